@@ -1,0 +1,172 @@
+/*
+ * texb_scatter.h -- C ABI of the B200 (sm_100a) segmented scatter-reduction library.
+ *
+ * The library replaces the native half of TorchEx's scatter operators
+ * (scatter_sum / scatter_mean / scatter_max over feats[N, C] grouped by
+ * unq_inv[N]).  Every entry point takes plain device pointers and sizes, an
+ * explicit CUDA stream (a cudaStream_t passed as void*; NULL = legacy default
+ * stream) and returns an int status.  Nothing here allocates device memory
+ * unless a comment says otherwise: scratch is a caller-provided workspace
+ * whose size comes from the matching *_workspace_bytes query.  Nothing calls
+ * exit() or throws.  All pointers refer to the CUDA device that is current on
+ * the calling thread.
+ *
+ * Vocabulary: a "point" is one row of feats; a "segment" is the set of points
+ * that share one id (one voxel / one pooled group); "sid" is the segment id of
+ * a point; "offsets" is TorchEx's preSum array (offsets[s] .. offsets[s+1] is
+ * the range of segment s in segment-sorted order); "perm" maps a position in
+ * segment-sorted order to the row of feats it came from.
+ */
+#ifndef TEXB_SCATTER_H_
+#define TEXB_SCATTER_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes --------------------------------------------------------- */
+#define TEXB_OK 0
+#define TEXB_ERR_INVALID_ARGUMENT 1 /* null pointer, negative size, bad enum   */
+#define TEXB_ERR_UNSUPPORTED 2      /* size beyond a documented limit           */
+#define TEXB_ERR_WORKSPACE 3        /* workspace smaller than *_workspace_bytes */
+#define TEXB_ERR_CUDA 4             /* a CUDA runtime call or launch failed     */
+
+/* reduce operators of texb_segment_reduce */
+#define TEXB_OP_SUM 0
+#define TEXB_OP_MEAN 1
+#define TEXB_OP_MAX 2
+
+/* Library version (major * 100 + minor). */
+int texb_version(void);
+
+/* Message for the last non-zero status returned on the calling thread.
+ * The pointer stays valid until the next failing call on that thread.
+ * TorchEx has no counterpart: its CHECK_CALL prints and calls exit(1)
+ * (torchex/src/utils/error.cuh:4-18) and the scatter launchers check nothing
+ * (torchex/src/scatter/scatter_kernel.cu:173-192). */
+const char* texb_last_error(void);
+
+/* Tuning knobs for experiments ("rows_per_cta", "compensated", "fixup_pdl").
+ * Process-wide; returns TEXB_ERR_INVALID_ARGUMENT for unknown keys or values
+ * out of range.  texb_tune_get returns the current value or -1. */
+int texb_tune_set(const char* key, int value);
+int texb_tune_get(const char* key);
+
+/* ---- segment-offset builder ------------------------------------------------
+ * Replaces ScatterData.__init__ / GetPreSumFunction
+ * (torchex/operator_py/scatter_op.py:7-21, 114-135) and getPreSum_launcher
+ * (torchex/src/scatter/scatter_kernel.cu:85-100, 173-175), and lifts their
+ * "ids must already be sorted and dense" requirement. */
+
+/* One pass over ids[n] (id_bytes = 4 for int32, 8 for int64).
+ * Writes stats_dev[0..3] (device int32): [0] 1 if ids are non-decreasing else
+ * 0, [1] minimum id, [2] maximum id, [3] number of distinct runs (equals the
+ * number of distinct ids when sorted).  n == 0 gives {1, INT32_MAX, -1, 0}. */
+int texb_ids_inspect(const void* ids, int id_bytes, int64_t n,
+                     int32_t* stats_dev, void* stream);
+
+/* Workspace for texb_plan_build. */
+size_t texb_plan_workspace_bytes(int64_t n, int64_t num_segments, int sorted);
+
+/* Builds the segment plan for ids[n] with ids in [0, num_segments).
+ *   sorted != 0: ids are non-decreasing.  sid_out receives the ids as int32,
+ *                perm_out is not touched (may be NULL), no sort runs.
+ *   sorted == 0: a stable LSD radix sort (per-digit histogram -> exclusive scan
+ *                -> scatter) orders the points by id; sid_out[p] is the id at
+ *                sorted position p and perm_out[p] the original row, rows of
+ *                one segment in increasing row order.
+ * offsets_out[num_segments + 1] is TorchEx's preSum.  plan_stats_dev[0..3]
+ * (device int32): [0] largest segment size, [1] number of empty segments,
+ * [2] number of ids outside [0, num_segments) (the plan is unusable if not 0),
+ * [3] reserved.  Limits: n < 2^31, num_segments < 2^31. */
+int texb_plan_build(const void* ids, int id_bytes, int64_t n,
+                    int64_t num_segments, int sorted, int32_t* sid_out,
+                    int32_t* perm_out, int32_t* offsets_out,
+                    int32_t* plan_stats_dev, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
+/* Drop-in for getPreSum_launcher(unq_inv, preSum, num_total)
+ * (torchex/src/scatter/scatter.cpp:18, scatter_kernel.cu:173-175): sorted
+ * int32 ids -> pre_sum[num_unq + 1].  Unlike the reference every entry is
+ * written (pre_sum need not be zero-filled) and skipped ids give empty
+ * segments instead of corrupt offsets. */
+int texb_get_pre_sum(const int32_t* unq_inv, int32_t* pre_sum,
+                     int64_t num_total, int64_t num_unq, void* stream);
+
+/* ---- forward reduce ----------------------------------------------------------
+ * Replaces scatter_sum_launcher / scatter_max_launcher
+ * (torchex/src/scatter/scatter.cpp:12-16, scatter_kernel.cu:102-171, 177-192)
+ * and the separate mean divide (torchex/operator_py/scatter_op.py:68-69). */
+
+/* Workspace for texb_segment_reduce (depends on the "rows_per_cta" knob). */
+size_t texb_reduce_workspace_bytes(int64_t n, int channel);
+
+/* out[s, :] = reduce over the rows of segment s of feats[N, channel] (fp32,
+ * row-major).  sid[n] is the segment id at each segment-sorted position;
+ * perm[n] the feats row at that position, or NULL when feats is already in
+ * segment order.  offsets may be NULL when has_empty == 0; otherwise the rows
+ * of empty segments are filled (0 for sum/mean; -FLT_MAX and -1 for max, what
+ * the reference kernel writes for an empty range).
+ *   TEXB_OP_SUM : fp32 sum, compensated (error-free transformation) so that
+ *                 long segments stay within 1e-6 + 1e-5*|x| of the exact sum.
+ *   TEXB_OP_MEAN: that sum divided (IEEE fp32 division) by the row count.
+ *   TEXB_OP_MAX : maximum and, in arg[num_segments, channel] (int32), the
+ *                 feats row holding it; ties go to the lowest row; NaN never
+ *                 wins (as in the reference, scatter_kernel.cu:146-151).
+ * No floating-point atomics: results are bit-reproducible run to run.
+ * Limits: n < 2^31, channel >= 1. */
+int texb_segment_reduce(int op, const float* feats, const int32_t* sid,
+                        const int32_t* perm, const int32_t* offsets,
+                        int has_empty, int64_t n, int channel,
+                        int64_t num_segments, float* out, int32_t* arg,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* Workspace for the two reference-shaped entry points below: room to expand
+ * pre_sum back into per-row segment ids plus texb_reduce_workspace_bytes. */
+size_t texb_scatter_compat_workspace_bytes(int64_t num_total, int channel);
+
+/* Drop-in for scatter_sum_launcher(feats, preSum, out, channel, num_unq,
+ * max_cnt) (torchex/src/scatter/scatter.cpp:12-13): feats in segment order.
+ * max_cnt is accepted and ignored (the reference sizes its thread blocks from
+ * it, scatter_kernel.cu:177-183).  num_total = feats rows, which the reference
+ * takes from the tensor. */
+int texb_scatter_sum(const float* feats, const int32_t* pre_sum, float* out,
+                     int channel, int num_unq, int max_cnt, int64_t num_total,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* Drop-in for scatter_max_launcher(feats, preSum, out, arg, channel, num_unq,
+ * max_cnt) (torchex/src/scatter/scatter.cpp:15-16). */
+int texb_scatter_max(const float* feats, const int32_t* pre_sum, float* out,
+                     int32_t* arg, int channel, int num_unq, int max_cnt,
+                     int64_t num_total, void* workspace,
+                     size_t workspace_bytes, void* stream);
+
+/* ---- backward -------------------------------------------------------------
+ * Replace the ATen expressions of the autograd Functions. */
+
+/* g_in[i, :] = g[unq_inv[i], :]
+ * (ScatterSumFunction.backward, torchex/operator_py/scatter_op.py:47-50). */
+int texb_scatter_sum_backward(const float* g, const int32_t* unq_inv,
+                              float* g_in, int64_t n, int channel,
+                              int64_t num_segments, void* stream);
+
+/* g_in[i, :] = g[unq_inv[i], :] / count(unq_inv[i]), count taken from offsets
+ * (ScatterMeanFunction.backward, torchex/operator_py/scatter_op.py:73-78). */
+int texb_scatter_mean_backward(const float* g, const int32_t* unq_inv,
+                               const int32_t* offsets, float* g_in, int64_t n,
+                               int channel, int64_t num_segments, void* stream);
+
+/* g_in[i, c] = (arg[unq_inv[i], c] == i) ? g[unq_inv[i], c] : 0, one fused
+ * pass instead of zeros + scatter_ (the intent of ScatterMaxFunction.backward,
+ * torchex/operator_py/scatter_op.py:105-111, which raises as shipped). */
+int texb_scatter_max_backward(const float* g, const int32_t* arg,
+                              const int32_t* unq_inv, float* g_in, int64_t n,
+                              int channel, int64_t num_segments, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TEXB_SCATTER_H_ */

@@ -1,0 +1,170 @@
+"""GPU parity of the CUDA path (through the C ABI) against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import scatter_oracle as O
+from torchex_b200 import ScatterData, _native, scatter_max, scatter_mean, scatter_sum, workloads as W
+from tests.gpu_util import ABS, DEV, REL, check_forward
+
+pytestmark = pytest.mark.gpu
+
+
+def _ids_from_sizes(sizes, seed, shuffled):
+    g = torch.Generator().manual_seed(seed)
+    m = sizes.numel()
+    ids = torch.repeat_interleave(torch.arange(m), sizes)
+    if shuffled:
+        ids = ids[torch.randperm(ids.numel(), generator=g)]
+    return ids
+
+
+@pytest.mark.parametrize("channel", [1, 3, 4, 5, 8, 16, 20, 32, 64, 128, 132, 256])
+@pytest.mark.parametrize("shuffled", [False, True])
+def test_small_shapes_all_channel_layouts(channel, shuffled):
+    g = torch.Generator().manual_seed(channel)
+    sizes = torch.randint(1, 40, (300,), generator=g)
+    sizes[7] = 700      # spans several CTAs at the smallest rows_per_cta
+    sizes[123] = 2500
+    ids = _ids_from_sizes(sizes, channel, shuffled)
+    feat = W.features(ids.numel(), channel, channel)
+    check_forward(feat, ids, sizes, label=f"C={channel} shuffled={shuffled}")
+
+
+@pytest.mark.parametrize("n,m", [(1, 1), (2, 1), (2, 2), (31, 1), (33, 3), (64, 64), (257, 2), (513, 1)])
+def test_tiny_exhaustive(n, m):
+    g = torch.Generator().manual_seed(n * 131 + m)
+    ids = torch.randint(0, m, (n,), generator=g)
+    ids[:m] = torch.arange(m)
+    cnt = torch.bincount(ids, minlength=m)
+    for channel in (1, 4, 16, 128):
+        feat = W.features(n, channel, n + channel)
+        check_forward(feat, ids, cnt, label=f"n={n} m={m} C={channel}")
+        srt = torch.sort(ids).values
+        check_forward(feat, srt, cnt, id_dtype=torch.int32, label=f"sorted n={n} m={m} C={channel}")
+
+
+@pytest.mark.parametrize("rows_per_cta", [64, 256, 512, 2048])
+def test_rows_per_cta_does_not_change_results(rows_per_cta):
+    old = _native.tune_get("rows_per_cta")
+    try:
+        _native.tune_set("rows_per_cta", rows_per_cta)
+        ids, cnt = W.skewed_ids(60_000, 3_000, seed=3, giant=9_000)
+        feat = W.features(60_000, 64, 3)
+        check_forward(feat, ids, cnt, label=f"rows_per_cta={rows_per_cta}")
+    finally:
+        _native.tune_set("rows_per_cta", old)
+
+
+def test_empty_segments_and_empty_input():
+    ids = torch.tensor([5, 5, 2, 9, 2, 5], dtype=torch.int64)
+    cnt = torch.bincount(ids, minlength=12)
+    feat = W.features(6, 8, 0)
+    data, s, mean, mx, arg = check_forward(feat, ids, cnt, label="gaps")
+    assert data.has_empty and not data.is_sorted
+    assert (s[cnt.numpy() == 0] == 0).all() and (arg[cnt.numpy() == 0] == -1).all()
+    # no points at all
+    data0 = ScatterData(torch.empty(0, dtype=torch.int64, device=DEV), torch.zeros(4, dtype=torch.int64, device=DEV))
+    out = scatter_sum(torch.empty((0, 16), device=DEV), data0)
+    assert out.shape == (4, 16) and (out == 0).all()
+
+
+def test_out_of_range_ids_are_rejected():
+    ids = torch.tensor([0, 1, 7], device=DEV)
+    with pytest.raises(ValueError):
+        ScatterData(ids, torch.ones(3, dtype=torch.int64, device=DEV))
+    with pytest.raises(ValueError):
+        ScatterData(torch.tensor([-1, 0], device=DEV), torch.ones(3, dtype=torch.int64, device=DEV))
+
+
+def test_plan_matches_stable_sort():
+    ids, cnt = W.voxel_frame(50_000, seed=5)
+    data = ScatterData(ids.to(DEV), cnt.to(DEV))
+    order = torch.argsort(ids, stable=True)
+    assert torch.equal(data.perm.cpu().long(), order)
+    assert torch.equal(data.sid.cpu().long(), ids[order])
+    pre = torch.zeros(cnt.numel() + 1, dtype=torch.int64)
+    pre[1:] = torch.cumsum(cnt, 0)
+    assert torch.equal(data.preSum.cpu().long(), pre)
+    assert data.max_cnt == int(cnt.max()) and data.num_unq == cnt.numel()
+    assert torch.equal(data.unq_inv.cpu().long(), ids)
+
+
+def test_config1_uniform_ids():
+    ids, cnt = W.uniform_ids(20_000, 2_000, seed=11)
+    check_forward(W.features(20_000, 16, 11), ids, cnt, label="c1")
+
+
+def test_config2_voxel_frame():
+    ids, cnt = W.voxel_frame(200_000, seed=12)
+    check_forward(W.features(200_000, 64, 12), ids, cnt, label="c2")
+
+
+@pytest.mark.parametrize("shuffled", [True, False])
+def test_config3_skewed_full_size(shuffled):
+    ids, cnt = W.skewed_ids(1_000_000, 50_000, seed=13, shuffled=shuffled)
+    check_forward(W.features(1_000_000, 128, 13), ids, cnt, label=f"c3 shuffled={shuffled}")
+
+
+def test_runs_are_bit_reproducible():
+    ids, cnt = W.skewed_ids(200_000, 10_000, seed=14, giant=30_000)
+    feat = W.features(200_000, 128, 14).to(DEV)
+    data = ScatterData(ids.to(DEV), cnt.to(DEV))
+    a = scatter_sum(feat, data)
+    b = scatter_sum(feat, ScatterData(ids.to(DEV), cnt.to(DEV)))
+    assert torch.equal(a, b)
+
+
+def test_config4_backward_with_ties():
+    ids, cnt, feat, grad = W.small_segments_with_ties(500_000, 128, seed=15)
+    m = cnt.numel()
+    data = ScatterData(ids.to(DEV), cnt.to(DEV))
+    x = feat.to(DEV).requires_grad_(True)
+    g = grad.to(DEV)
+    out, arg = scatter_max(x, data)
+    out.backward(g)
+    want_mx, want_arg = O.spec_scatter_max(feat, ids, m)
+    assert np.array_equal(out.detach().cpu().numpy(), want_mx)
+    assert np.array_equal(arg.cpu().numpy(), want_arg)
+    # ties exist and went to the lowest row
+    assert np.array_equal(x.grad.cpu().numpy(), O.spec_max_backward(grad, want_arg, ids.numel()))
+    x.grad = None
+    scatter_mean(x, data).backward(g)
+    assert np.array_equal(x.grad.cpu().numpy(), O.spec_mean_backward(grad, ids, cnt))
+    x.grad = None
+    scatter_sum(x, data).backward(g)
+    assert np.array_equal(x.grad.cpu().numpy(), O.spec_sum_backward(grad, ids))
+
+
+def test_backward_accepts_expanded_gradient():
+    ids, cnt = W.uniform_ids(5_000, 400, seed=16)
+    data = ScatterData(ids.to(DEV), cnt.to(DEV))
+    x = W.features(5_000, 32, 16).to(DEV).requires_grad_(True)
+    scatter_sum(x, data).sum().backward()
+    assert torch.equal(x.grad, torch.ones_like(x))
+    x.grad = None
+    scatter_mean(x, data).sum().backward()
+    want = (1.0 / cnt.float())[ids][:, None].expand(-1, 32)
+    assert torch.equal(x.grad.cpu(), want)
+
+
+def test_scatter_ext_module_keeps_reference_signatures():
+    from torchex_b200 import scatter_ext
+    ids, cnt = W.uniform_ids(6_000, 500, seed=17)
+    order, feat_s, ids_s = O.sort_for_reference(W.features(6_000, 16, 17), ids)
+    feat_d = feat_s.to(DEV)
+    pre = torch.zeros(501, dtype=torch.int32, device=DEV)
+    scatter_ext.getPreSum(ids_s.int().to(DEV), pre)
+    assert np.array_equal(pre.cpu().numpy(), O.ref_order_get_pre_sum(ids_s))
+    out = torch.zeros((500, 16), device=DEV)
+    scatter_ext.sum(feat_d, pre, out, int(cnt.max()))
+    s64, _ = O.spec_scatter_sum_f64(feat_s, ids_s, 500)
+    assert O.within_tolerance(out.cpu().numpy(), s64, REL, ABS).all()
+    arg = torch.zeros((500, 16), dtype=torch.int32, device=DEV)
+    scatter_ext.max(feat_d, pre, out, arg, int(cnt.max()))
+    want_mx, want_arg = O.spec_scatter_max(feat_s, ids_s, 500)
+    assert np.array_equal(out.cpu().numpy(), want_mx) and np.array_equal(arg.cpu().numpy(), want_arg)
+    with pytest.raises(RuntimeError):
+        scatter_ext.sum(feat_s, pre, out, 1)           # CPU tensor
+    with pytest.raises(RuntimeError):
+        scatter_ext.sum(feat_d.t(), pre, out, 1)       # not contiguous

@@ -1,0 +1,90 @@
+"""ctypes view of ``libtexb_scatter.so`` (the C ABI in ``include/texb_scatter.h``).
+
+There is no CPU fallback: if the library is missing, ``lib()`` raises.  Each
+wrapper passes raw device pointers, sizes and the current CUDA stream, and turns
+a non-zero status into ``RuntimeError`` carrying ``texb_last_error()``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+from . import build as _build
+
+_c = ctypes
+_lock = threading.Lock()
+_lib = None
+
+_SIGNATURES = {
+    # name: (restype, argtypes)
+    "texb_version": (_c.c_int, []),
+    "texb_last_error": (_c.c_char_p, []),
+    "texb_tune_set": (_c.c_int, [_c.c_char_p, _c.c_int]),
+    "texb_tune_get": (_c.c_int, [_c.c_char_p]),
+    "texb_ids_inspect": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p, _c.c_void_p]),
+    "texb_plan_workspace_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int64, _c.c_int]),
+    "texb_plan_build": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int,
+                                   _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                   _c.c_void_p, _c.c_size_t, _c.c_void_p]),
+    "texb_get_pre_sum": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p]),
+    "texb_reduce_workspace_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int]),
+    "texb_segment_reduce": (_c.c_int, [_c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                       _c.c_int, _c.c_int64, _c.c_int, _c.c_int64, _c.c_void_p,
+                                       _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
+    "texb_scatter_compat_workspace_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int]),
+    "texb_scatter_sum": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int,
+                                    _c.c_int, _c.c_int64, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
+    "texb_scatter_max": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int,
+                                    _c.c_int, _c.c_int, _c.c_int64, _c.c_void_p, _c.c_size_t,
+                                    _c.c_void_p]),
+    "texb_scatter_sum_backward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64,
+                                             _c.c_int, _c.c_int64, _c.c_void_p]),
+    "texb_scatter_mean_backward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                              _c.c_int64, _c.c_int, _c.c_int64, _c.c_void_p]),
+    "texb_scatter_max_backward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                             _c.c_int64, _c.c_int, _c.c_int64, _c.c_void_p]),
+}
+
+OP_SUM, OP_MEAN, OP_MAX = 0, 1, 2
+
+
+def exported_symbols():
+    """Names every build of the library must export."""
+    return sorted(_SIGNATURES)
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the library once; raises if it has not been built."""
+    global _lib
+    with _lock:
+        if _lib is None:
+            path = _build.LIB_PATH
+            if not os.path.exists(path):
+                raise RuntimeError(
+                    f"{path} is missing: build it with `python -m torchex_b200.build` "
+                    "(there is no CPU or PyTorch fallback for the scatter kernels)")
+            handle = ctypes.CDLL(path)
+            for name, (res, args) in _SIGNATURES.items():
+                fn = getattr(handle, name)
+                fn.restype = res
+                fn.argtypes = args
+            _lib = handle
+    return _lib
+
+
+def last_error() -> str:
+    return lib().texb_last_error().decode("utf-8", "replace")
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        raise RuntimeError(f"{what} failed with status {status}: {last_error()}")
+
+
+def tune_set(key: str, value: int) -> None:
+    check(lib().texb_tune_set(key.encode(), int(value)), f"texb_tune_set({key})")
+
+
+def tune_get(key: str) -> int:
+    return lib().texb_tune_get(key.encode())

@@ -1,0 +1,220 @@
+// extern "C" surface of the library (declared in include/texb_scatter.h):
+// argument plumbing, thread-local error text and the tuning knobs.
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace texb {
+
+// implemented in the kernel files
+int ids_inspect_impl(const void*, int, int64_t, int32_t*, cudaStream_t);
+size_t plan_workspace_bytes_impl(int64_t, int64_t, int);
+int plan_build_impl(const void*, int, int64_t, int64_t, int, int32_t*, int32_t*, int32_t*, int32_t*,
+                    void*, size_t, cudaStream_t);
+int get_pre_sum_impl(const int32_t*, int32_t*, int64_t, int64_t, cudaStream_t);
+size_t reduce_workspace_bytes_impl(int64_t, int);
+int segment_reduce_impl(int, const float*, const int32_t*, const int32_t*, const int32_t*, int,
+                        int64_t, int, int64_t, float*, int32_t*, void*, size_t, cudaStream_t);
+int expand_offsets_impl(const int32_t*, int32_t*, int64_t, int64_t, cudaStream_t);
+int sum_backward_impl(const float*, const int32_t*, float*, int64_t, int, int64_t, cudaStream_t);
+int mean_backward_impl(const float*, const int32_t*, const int32_t*, float*, int64_t, int, int64_t,
+                       cudaStream_t);
+int max_backward_impl(const float*, const int32_t*, const int32_t*, float*, int64_t, int, int64_t,
+                      cudaStream_t);
+
+namespace {
+thread_local char t_error[512] = "";
+
+std::mutex g_tuning_mutex;
+Tuning g_tuning = {512, 1, 0};
+bool g_tuning_env_read = false;
+
+int env_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  if (!v || !*v) return fallback;
+  return std::atoi(v);
+}
+
+bool set_knob(Tuning& t, const char* key, int value) {
+  if (!std::strcmp(key, "rows_per_cta")) {
+    if (value < 64 || value > (1 << 20)) return false;
+    t.rows_per_cta = value;
+    return true;
+  }
+  if (!std::strcmp(key, "compensated")) {
+    if (value != 0 && value != 1) return false;
+    t.compensated = value;
+    return true;
+  }
+  if (!std::strcmp(key, "fixup_pdl")) {
+    if (value != 0 && value != 1) return false;
+    t.fixup_pdl = value;
+    return true;
+  }
+  return false;
+}
+
+void read_env_locked() {
+  if (g_tuning_env_read) return;
+  g_tuning_env_read = true;
+  set_knob(g_tuning, "rows_per_cta", env_int("TEXB_ROWS_PER_CTA", g_tuning.rows_per_cta));
+  set_knob(g_tuning, "compensated", env_int("TEXB_COMPENSATED", g_tuning.compensated));
+  set_knob(g_tuning, "fixup_pdl", env_int("TEXB_FIXUP_PDL", g_tuning.fixup_pdl));
+}
+}  // namespace
+
+int fail(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  std::vsnprintf(t_error, sizeof(t_error), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return TEXB_OK;
+  return fail(TEXB_ERR_CUDA, "%s: %s (cuda error %d)", what, cudaGetErrorString(e), int(e));
+}
+
+Tuning tuning() {
+  std::lock_guard<std::mutex> lock(g_tuning_mutex);
+  read_env_locked();
+  return g_tuning;
+}
+
+}  // namespace texb
+
+using namespace texb;
+
+extern "C" {
+
+int texb_version(void) { return 100; }
+
+const char* texb_last_error(void) { return t_error; }
+
+int texb_tune_set(const char* key, int value) {
+  if (!key) return fail(TEXB_ERR_INVALID_ARGUMENT, "tune_set: NULL key");
+  std::lock_guard<std::mutex> lock(g_tuning_mutex);
+  read_env_locked();
+  if (!set_knob(g_tuning, key, value))
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "tune_set: unknown key or bad value: %s=%d", key, value);
+  return TEXB_OK;
+}
+
+int texb_tune_get(const char* key) {
+  if (!key) return -1;
+  Tuning t = tuning();
+  if (!std::strcmp(key, "rows_per_cta")) return t.rows_per_cta;
+  if (!std::strcmp(key, "compensated")) return t.compensated;
+  if (!std::strcmp(key, "fixup_pdl")) return t.fixup_pdl;
+  return -1;
+}
+
+int texb_ids_inspect(const void* ids, int id_bytes, int64_t n, int32_t* stats_dev, void* stream) {
+  return ids_inspect_impl(ids, id_bytes, n, stats_dev, static_cast<cudaStream_t>(stream));
+}
+
+size_t texb_plan_workspace_bytes(int64_t n, int64_t num_segments, int sorted) {
+  return plan_workspace_bytes_impl(n, num_segments, sorted);
+}
+
+int texb_plan_build(const void* ids, int id_bytes, int64_t n, int64_t num_segments, int sorted,
+                    int32_t* sid_out, int32_t* perm_out, int32_t* offsets_out,
+                    int32_t* plan_stats_dev, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+  return plan_build_impl(ids, id_bytes, n, num_segments, sorted, sid_out, perm_out, offsets_out,
+                         plan_stats_dev, workspace, workspace_bytes,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int texb_get_pre_sum(const int32_t* unq_inv, int32_t* pre_sum, int64_t num_total, int64_t num_unq,
+                     void* stream) {
+  return get_pre_sum_impl(unq_inv, pre_sum, num_total, num_unq, static_cast<cudaStream_t>(stream));
+}
+
+size_t texb_reduce_workspace_bytes(int64_t n, int channel) {
+  if (n < 0 || channel < 1) return 0;
+  return reduce_workspace_bytes_impl(n, channel);
+}
+
+int texb_segment_reduce(int op, const float* feats, const int32_t* sid, const int32_t* perm,
+                        const int32_t* offsets, int has_empty, int64_t n, int channel,
+                        int64_t num_segments, float* out, int32_t* arg, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+  return segment_reduce_impl(op, feats, sid, perm, offsets, has_empty, n, channel, num_segments,
+                             out, arg, workspace, workspace_bytes,
+                             static_cast<cudaStream_t>(stream));
+}
+
+size_t texb_scatter_compat_workspace_bytes(int64_t num_total, int channel) {
+  if (num_total < 0 || channel < 1) return 0;
+  return align_up(size_t(num_total) * sizeof(int32_t), 256) + 256 +
+         reduce_workspace_bytes_impl(num_total, channel);
+}
+
+static int compat_reduce(int op, const float* feats, const int32_t* pre_sum, float* out,
+                         int32_t* arg, int channel, int num_unq, int64_t num_total, void* workspace,
+                         size_t workspace_bytes, cudaStream_t stream) {
+  if (num_total < 0 || num_unq < 0 || channel < 1)
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "scatter: bad sizes");
+  if (!pre_sum) return fail(TEXB_ERR_INVALID_ARGUMENT, "scatter: preSum is NULL");
+  if (num_total >= (int64_t(1) << 31) - 65536)
+    return fail(TEXB_ERR_UNSUPPORTED, "scatter: num_total must be below 2^31 - 65536");
+  const size_t sid_bytes = align_up(size_t(num_total) * sizeof(int32_t), 256);
+  uintptr_t base = align_up(reinterpret_cast<uintptr_t>(workspace), 256);
+  const size_t pad = base - reinterpret_cast<uintptr_t>(workspace);
+  if (!workspace || workspace_bytes < pad + sid_bytes)
+    return fail(TEXB_ERR_WORKSPACE, "scatter workspace: need %zu bytes, got %zu",
+                texb_scatter_compat_workspace_bytes(num_total, channel), workspace_bytes);
+  int32_t* sid = reinterpret_cast<int32_t*>(base);
+  int st = expand_offsets_impl(pre_sum, sid, num_total, num_unq, stream);
+  if (st != TEXB_OK) return st;
+  // The reference kernels write every row, including those of empty ranges.
+  return segment_reduce_impl(op, feats, sid, nullptr, pre_sum, /*has_empty=*/1, num_total, channel,
+                             num_unq, out, arg, reinterpret_cast<void*>(base + sid_bytes),
+                             workspace_bytes - pad - sid_bytes, stream);
+}
+
+int texb_scatter_sum(const float* feats, const int32_t* pre_sum, float* out, int channel,
+                     int num_unq, int max_cnt, int64_t num_total, void* workspace,
+                     size_t workspace_bytes, void* stream) {
+  (void)max_cnt;
+  return compat_reduce(TEXB_OP_SUM, feats, pre_sum, out, nullptr, channel, num_unq, num_total,
+                       workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int texb_scatter_max(const float* feats, const int32_t* pre_sum, float* out, int32_t* arg,
+                     int channel, int num_unq, int max_cnt, int64_t num_total, void* workspace,
+                     size_t workspace_bytes, void* stream) {
+  (void)max_cnt;
+  return compat_reduce(TEXB_OP_MAX, feats, pre_sum, out, arg, channel, num_unq, num_total,
+                       workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int texb_scatter_sum_backward(const float* g, const int32_t* unq_inv, float* g_in, int64_t n,
+                              int channel, int64_t num_segments, void* stream) {
+  return sum_backward_impl(g, unq_inv, g_in, n, channel, num_segments,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int texb_scatter_mean_backward(const float* g, const int32_t* unq_inv, const int32_t* offsets,
+                               float* g_in, int64_t n, int channel, int64_t num_segments,
+                               void* stream) {
+  return mean_backward_impl(g, unq_inv, offsets, g_in, n, channel, num_segments,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int texb_scatter_max_backward(const float* g, const int32_t* arg, const int32_t* unq_inv,
+                              float* g_in, int64_t n, int channel, int64_t num_segments,
+                              void* stream) {
+  return max_backward_impl(g, arg, unq_inv, g_in, n, channel, num_segments,
+                           static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

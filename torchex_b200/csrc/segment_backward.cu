@@ -1,0 +1,172 @@
+// Backward of the scatter operators: one fused row-broadcast pass per call.
+//
+//   sum : g_in[i, :] = g[sid_i, :]
+//   mean: g_in[i, :] = g[sid_i, :] / count(sid_i)
+//   max : g_in[i, c] = (arg[sid_i, c] == i) ? g[sid_i, c] : 0
+//
+// Lanes run along the channel axis (128-bit accesses when the layout allows),
+// a group of lanes handles eight consecutive points per step, and g_in is
+// written with streaming stores so that g / arg (reused by every point of a
+// segment) stay resident in L2.  No memset, no atomics.
+//
+// Replaces the ATen expressions in ScatterSumFunction.backward,
+// ScatterMeanFunction.backward and ScatterMaxFunction.backward
+// (torchex/operator_py/scatter_op.py:47-50, 73-78, 105-111).
+
+#include "common.cuh"
+
+namespace texb {
+namespace {
+
+constexpr int kModeSum = 0, kModeMean = 1, kModeMax = 2;
+constexpr int kRowsPerStep = 8;
+
+template <int VEC>
+struct Pack { float v[VEC]; };
+
+template <int VEC>
+__device__ __forceinline__ Pack<VEC> load_f(const float* p) {
+  Pack<VEC> r;
+  if constexpr (VEC == 4) {
+    float4 t = __ldg(reinterpret_cast<const float4*>(p));
+    r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
+  } else {
+    r.v[0] = __ldg(p);
+  }
+  return r;
+}
+
+template <int VEC>
+struct PackI { int v[VEC]; };
+
+template <int VEC>
+__device__ __forceinline__ PackI<VEC> load_i(const int32_t* p) {
+  PackI<VEC> r;
+  if constexpr (VEC == 4) {
+    int4 t = __ldg(reinterpret_cast<const int4*>(p));
+    r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
+  } else {
+    r.v[0] = __ldg(p);
+  }
+  return r;
+}
+
+template <int VEC>
+__device__ __forceinline__ void store_stream(float* p, const Pack<VEC>& r) {
+  if constexpr (VEC == 4) {
+    __stcs(reinterpret_cast<float4*>(p), make_float4(r.v[0], r.v[1], r.v[2], r.v[3]));
+  } else {
+    __stcs(p, r.v[0]);
+  }
+}
+
+template <int MODE, int VEC, int LPR>
+__global__ void __launch_bounds__(kCtaThreads)
+broadcast_back_kernel(const float* __restrict__ g, const int32_t* __restrict__ arg,
+                      const int32_t* __restrict__ ids, const int32_t* __restrict__ offsets,
+                      float* __restrict__ g_in, int64_t n, int C, int64_t m) {
+  constexpr int GPC = kCtaThreads / LPR;
+  const int lane_g = threadIdx.x & (LPR - 1);
+  const int group = threadIdx.x / LPR;
+  const int64_t r0 = (int64_t(blockIdx.x) * GPC + group) * kRowsPerStep;
+  if (r0 >= n) return;
+
+  int s[kRowsPerStep];
+  float den[kRowsPerStep];
+#pragma unroll
+  for (int k = 0; k < kRowsPerStep; ++k) {
+    const int64_t i = r0 + k;
+    int v = (i < n) ? __ldg(ids + i) : -1;
+    s[k] = (v >= 0 && v < m) ? v : -1;  // ids outside the range get a zero row
+  }
+  if constexpr (MODE == kModeMean) {
+#pragma unroll
+    for (int k = 0; k < kRowsPerStep; ++k) {
+      den[k] = 1.f;
+      if (s[k] >= 0) den[k] = float(__ldg(offsets + s[k] + 1) - __ldg(offsets + s[k]));
+    }
+  }
+  for (int ch = lane_g * VEC; ch < C; ch += LPR * VEC) {
+    Pack<VEC> val[kRowsPerStep];
+#pragma unroll
+    for (int k = 0; k < kRowsPerStep; ++k) {
+      if (s[k] >= 0) {
+        val[k] = load_f<VEC>(g + int64_t(s[k]) * C + ch);
+        if constexpr (MODE == kModeMax) {
+          PackI<VEC> a = load_i<VEC>(arg + int64_t(s[k]) * C + ch);
+          const int64_t i = r0 + k;
+#pragma unroll
+          for (int q = 0; q < VEC; ++q)
+            if (int64_t(a.v[q]) != i) val[k].v[q] = 0.f;
+        }
+        if constexpr (MODE == kModeMean) {
+#pragma unroll
+          for (int q = 0; q < VEC; ++q) val[k].v[q] = __fdiv_rn(val[k].v[q], den[k]);
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) val[k].v[q] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kRowsPerStep; ++k) {
+      const int64_t i = r0 + k;
+      if (i < n) store_stream<VEC>(g_in + i * C + ch, val[k]);
+    }
+  }
+}
+
+template <int MODE, int VEC>
+int launch_lpr(int lpr, const float* g, const int32_t* arg, const int32_t* ids,
+               const int32_t* offsets, float* g_in, int64_t n, int C, int64_t m,
+               cudaStream_t stream) {
+  const int gpc = kCtaThreads / lpr;
+  const unsigned blocks = unsigned(ceil_div(n, int64_t(gpc) * kRowsPerStep));
+#define TEXB_LAUNCH(L)                                                                   \
+  broadcast_back_kernel<MODE, VEC, L><<<blocks, kCtaThreads, 0, stream>>>(g, arg, ids,   \
+                                                                         offsets, g_in, n, C, m)
+  switch (lpr) {
+    case 1: TEXB_LAUNCH(1); break;
+    case 2: TEXB_LAUNCH(2); break;
+    case 4: TEXB_LAUNCH(4); break;
+    case 8: TEXB_LAUNCH(8); break;
+    case 16: TEXB_LAUNCH(16); break;
+    default: TEXB_LAUNCH(32); break;
+  }
+#undef TEXB_LAUNCH
+  return check_launch("broadcast_back_kernel");
+}
+
+template <int MODE>
+int launch_back(const float* g, const int32_t* arg, const int32_t* ids, const int32_t* offsets,
+                float* g_in, int64_t n, int C, int64_t m, cudaStream_t stream) {
+  if (n < 0 || m < 0 || C < 1) return fail(TEXB_ERR_INVALID_ARGUMENT, "backward: bad sizes");
+  if (n == 0) return TEXB_OK;
+  if (!g_in || !ids || (m > 0 && !g) || (MODE == kModeMax && m > 0 && !arg) ||
+      (MODE == kModeMean && !offsets))
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "backward: NULL pointer");
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  const bool vec4 = (C % 4 == 0) && al(g) && al(g_in) && (MODE != kModeMax || al(arg));
+  const int vec = vec4 ? 4 : 1;
+  int lpr = 1;
+  while (lpr < C / vec && lpr < 32) lpr <<= 1;
+  if (vec4) return launch_lpr<MODE, 4>(lpr, g, arg, ids, offsets, g_in, n, C, m, stream);
+  return launch_lpr<MODE, 1>(lpr, g, arg, ids, offsets, g_in, n, C, m, stream);
+}
+
+}  // namespace
+
+int sum_backward_impl(const float* g, const int32_t* ids, float* g_in, int64_t n, int C, int64_t m,
+                      cudaStream_t stream) {
+  return launch_back<kModeSum>(g, nullptr, ids, nullptr, g_in, n, C, m, stream);
+}
+int mean_backward_impl(const float* g, const int32_t* ids, const int32_t* offsets, float* g_in,
+                       int64_t n, int C, int64_t m, cudaStream_t stream) {
+  return launch_back<kModeMean>(g, nullptr, ids, offsets, g_in, n, C, m, stream);
+}
+int max_backward_impl(const float* g, const int32_t* arg, const int32_t* ids, float* g_in,
+                      int64_t n, int C, int64_t m, cudaStream_t stream) {
+  return launch_back<kModeMax>(g, arg, ids, nullptr, g_in, n, C, m, stream);
+}
+
+}  // namespace texb

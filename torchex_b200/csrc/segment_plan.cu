@@ -1,0 +1,401 @@
+// Segment-offset builder: ids[n] -> (sid, perm, offsets) for the reduce kernels.
+//
+//   * texb_ids_inspect: one pass giving sortedness, id range and run count.
+//   * sorted ids: offsets come from neighbour comparison (each entry written
+//     exactly once, gaps in the id space become empty segments); no sort runs.
+//   * unsorted ids: a stable least-significant-digit radix sort on the id with
+//     the row index as payload.  Every digit pass is a per-tile histogram, an
+//     exclusive scan over (digit, tile) and a stable scatter, i.e. three plain
+//     launches with no inter-CTA waiting.  Rows of one segment therefore stay in
+//     increasing row order, which makes the reduce result independent of run
+//     order.
+//
+// Replaces ScatterData.__init__ / GetPreSumFunction
+// (torchex/operator_py/scatter_op.py:7-21, 114-135) and the getPreSum kernel
+// (torchex/src/scatter/scatter_kernel.cu:85-100), which only handle ids that
+// are already sorted and dense.
+
+#include <climits>
+
+#include "common.cuh"
+
+namespace texb {
+namespace {
+
+constexpr int kRadixBits = 8;
+constexpr int kRadix = 1 << kRadixBits;
+constexpr int kSortThreads = 256;
+constexpr int kSortItems = 16;
+constexpr int kSortTile = kSortThreads * kSortItems;    // keys per CTA
+constexpr int kWarpTile = 32 * kSortItems;              // keys per warp
+constexpr int kSortWarps = kSortThreads / 32;
+
+template <typename IdT>
+__device__ __forceinline__ int32_t clamp_id(IdT v) {
+  if (sizeof(IdT) == 8) {
+    if (v > IdT(INT_MAX)) return INT_MAX;
+    if (v < IdT(INT_MIN)) return INT_MIN;
+  }
+  return int32_t(v);
+}
+
+// ---- inspect --------------------------------------------------------------------
+
+__global__ void init_inspect_stats_kernel(int32_t* stats) {
+  if (threadIdx.x == 0) {
+    stats[0] = 1;
+    stats[1] = INT_MAX;
+    stats[2] = INT_MIN;
+    stats[3] = 0;
+  }
+}
+
+template <typename IdT>
+__global__ void inspect_ids_kernel(const IdT* __restrict__ ids, int64_t n, int32_t* stats) {
+  int unsorted = 0, runs = 0;
+  int32_t lo = INT_MAX, hi = INT_MIN;
+  for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < n;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    const IdT a = ids[i];
+    const int32_t a32 = clamp_id<IdT>(a);
+    lo = min(lo, a32);
+    hi = max(hi, a32);
+    if (i + 1 < n) {
+      const IdT b = ids[i + 1];
+      unsorted |= (a > b);
+      runs += (a != b);
+    } else {
+      runs += 1;  // the last run
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    unsorted |= __shfl_xor_sync(0xffffffffu, unsorted, o);
+    runs += __shfl_xor_sync(0xffffffffu, runs, o);
+    lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+    hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    if (unsorted) atomicAnd(&stats[0], 0);
+    if (lo != INT_MAX) atomicMin(&stats[1], lo);
+    if (hi != INT_MIN) atomicMax(&stats[2], hi);
+    if (runs) atomicAdd(&stats[3], runs);
+  }
+}
+
+// ---- offsets from sorted ids -----------------------------------------------------
+
+// Thread i in [0, n] owns the boundary before sorted position i and writes
+// offsets[s] = i for every s in (id[i-1], id[i]], with id[-1] = -1 and id[n] = m.
+template <typename IdT>
+__global__ void offsets_from_sorted_kernel(const IdT* __restrict__ ids, int32_t* __restrict__ sid_out,
+                                           int32_t* __restrict__ offsets, int n, int m,
+                                           int32_t* plan_stats) {
+  const int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
+  if (i > n) return;
+  int64_t a = (i == 0) ? -1 : int64_t(ids[i - 1]);
+  int64_t b = (i == n) ? int64_t(m) : int64_t(ids[i]);
+  if (i < n) {
+    if (plan_stats && (b < 0 || b >= m)) atomicAdd(&plan_stats[2], 1);
+    if (sid_out) sid_out[i] = clamp_id<IdT>(ids[i]);
+  }
+  if (a < -1) a = -1;
+  if (b > m) b = m;
+  for (int64_t s = a + 1; s <= b; ++s) offsets[s] = int32_t(i);
+}
+
+__global__ void plan_stats_kernel(const int32_t* __restrict__ offsets, int m, int32_t* plan_stats) {
+  int mx = 0, empty = 0;
+  for (int64_t s = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; s < m;
+       s += int64_t(gridDim.x) * blockDim.x) {
+    const int c = offsets[s + 1] - offsets[s];
+    mx = max(mx, c);
+    empty += (c == 0);
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    empty += __shfl_xor_sync(0xffffffffu, empty, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    if (mx) atomicMax(&plan_stats[0], mx);
+    if (empty) atomicAdd(&plan_stats[1], empty);
+  }
+}
+
+// ---- radix sort passes -------------------------------------------------------------
+
+template <typename IdT>
+__device__ __forceinline__ uint32_t load_key(const void* keys, int64_t idx) {
+  return uint32_t(clamp_id<IdT>(static_cast<const IdT*>(keys)[idx]));
+}
+
+// ghist[d * num_tiles + tile] = number of keys of this tile whose digit is d.
+template <typename IdT>
+__global__ void __launch_bounds__(kSortThreads)
+radix_histogram_kernel(const void* __restrict__ keys, int n, int shift, uint32_t* __restrict__ ghist,
+                       int num_tiles) {
+  __shared__ uint32_t s_hist[kRadix];
+  for (int d = threadIdx.x; d < kRadix; d += kSortThreads) s_hist[d] = 0u;
+  __syncthreads();
+  const int64_t tile0 = int64_t(blockIdx.x) * kSortTile;
+#pragma unroll 4
+  for (int k = 0; k < kSortItems; ++k) {
+    const int64_t idx = tile0 + k * kSortThreads + threadIdx.x;
+    if (idx < n) atomicAdd(&s_hist[(load_key<IdT>(keys, idx) >> shift) & (kRadix - 1)], 1u);
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < kRadix; d += kSortThreads)
+    ghist[int64_t(d) * num_tiles + blockIdx.x] = s_hist[d];
+}
+
+// In-place exclusive scan over `count` words by a single CTA of 1024 threads.
+__global__ void __launch_bounds__(1024) exclusive_scan_kernel(uint32_t* data, int64_t count) {
+  __shared__ uint32_t s_warp[32];
+  const int64_t per = (count + 1023) / 1024;
+  const int64_t i0 = min(int64_t(threadIdx.x) * per, count);
+  const int64_t i1 = min(i0 + per, count);
+  uint32_t sum = 0u;
+  for (int64_t i = i0; i < i1; ++i) sum += data[i];
+  // exclusive scan of the 1024 per-thread sums
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t incl = sum;
+  for (int o = 1; o < 32; o <<= 1) {
+    uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) s_warp[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t w = s_warp[lane];
+    uint32_t wi = w;
+    for (int o = 1; o < 32; o <<= 1) {
+      uint32_t t = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += t;
+    }
+    s_warp[lane] = wi - w;  // exclusive base of each warp
+  }
+  __syncthreads();
+  uint32_t run = s_warp[warp] + (incl - sum);
+  for (int64_t i = i0; i < i1; ++i) {
+    const uint32_t v = data[i];
+    data[i] = run;
+    run += v;
+  }
+}
+
+// Stable scatter of one digit pass.  Within a warp, item k of lane l is key
+// tile0 + warp * kWarpTile + k * 32 + l, so (warp, k, lane) order is key order.
+template <typename IdT, bool FIRST>
+__global__ void __launch_bounds__(kSortThreads)
+radix_scatter_kernel(const void* __restrict__ keys_in, const int32_t* __restrict__ vals_in,
+                     int32_t* __restrict__ keys_out, int32_t* __restrict__ vals_out, int n, int shift,
+                     const uint32_t* __restrict__ ghist, int num_tiles) {
+  __shared__ uint32_t s_wcount[kSortWarps][kRadix];
+  __shared__ uint32_t s_gbase[kRadix];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < kSortWarps * kRadix; i += kSortThreads) (&s_wcount[0][0])[i] = 0u;
+  __syncthreads();
+
+  const int64_t w0 = int64_t(blockIdx.x) * kSortTile + int64_t(warp) * kWarpTile;
+  uint32_t key[kSortItems];
+  uint32_t rank[kSortItems];
+  const uint32_t lt_mask = (1u << lane) - 1u;
+#pragma unroll
+  for (int k = 0; k < kSortItems; ++k) {
+    const int64_t idx = w0 + k * 32 + lane;
+    const bool valid = idx < n;
+    key[k] = valid ? load_key<IdT>(keys_in, idx) : 0u;
+    const uint32_t d = (key[k] >> shift) & (kRadix - 1);
+    const uint32_t tag = valid ? d : uint32_t(kRadix);  // out-of-range lanes group together
+    const uint32_t peers = __match_any_sync(0xffffffffu, tag);
+    const int leader = __ffs(peers) - 1;
+    uint32_t before = 0u;
+    if (valid && lane == leader) {
+      before = s_wcount[warp][d];
+      s_wcount[warp][d] = before + __popc(peers);
+    }
+    before = __shfl_sync(0xffffffffu, before, leader);
+    rank[k] = before + __popc(peers & lt_mask);
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < kRadix; d += kSortThreads) {
+    uint32_t run = 0u;
+#pragma unroll
+    for (int w = 0; w < kSortWarps; ++w) {
+      const uint32_t c = s_wcount[w][d];
+      s_wcount[w][d] = run;
+      run += c;
+    }
+    s_gbase[d] = ghist[int64_t(d) * num_tiles + blockIdx.x];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < kSortItems; ++k) {
+    const int64_t idx = w0 + k * 32 + lane;
+    if (idx < n) {
+      const uint32_t d = (key[k] >> shift) & (kRadix - 1);
+      const uint32_t pos = s_gbase[d] + s_wcount[warp][d] + rank[k];
+      keys_out[pos] = int32_t(key[k]);
+      vals_out[pos] = FIRST ? int32_t(idx) : vals_in[idx];
+    }
+  }
+}
+
+int bit_width(int64_t v) {
+  int b = 0;
+  while (v > 0) { ++b; v >>= 1; }
+  return b;
+}
+
+int num_sort_passes(int64_t m) {
+  int bits = bit_width(m > 1 ? m - 1 : 1);
+  return (bits + kRadixBits - 1) / kRadixBits;
+}
+
+struct SortWorkspace {
+  int32_t* tmp_keys;
+  int32_t* tmp_vals;
+  uint32_t* ghist;
+  size_t bytes;
+};
+
+SortWorkspace carve_sort_workspace(void* ws, int64_t n) {
+  SortWorkspace s;
+  const size_t arr = align_up(size_t(n) * sizeof(int32_t), 256);
+  const int64_t tiles = ceil_div(n, kSortTile);
+  const size_t hist = align_up(size_t(tiles) * kRadix * sizeof(uint32_t), 256);
+  uintptr_t base = align_up(reinterpret_cast<uintptr_t>(ws), 256);
+  s.tmp_keys = reinterpret_cast<int32_t*>(base);
+  s.tmp_vals = reinterpret_cast<int32_t*>(base + arr);
+  s.ghist = reinterpret_cast<uint32_t*>(base + 2 * arr);
+  s.bytes = 2 * arr + hist + 256;
+  return s;
+}
+
+template <typename IdT>
+int run_sort(const void* ids, int64_t n, int64_t m, int32_t* sid_out, int32_t* perm_out,
+             const SortWorkspace& sw, cudaStream_t stream) {
+  const int passes = num_sort_passes(m);
+  const int tiles = int(ceil_div(n, kSortTile));
+  const void* src_k = ids;
+  const int32_t* src_v = nullptr;
+  for (int p = 0; p < passes; ++p) {
+    const bool to_out = ((passes - 1 - p) % 2) == 0;
+    int32_t* dst_k = to_out ? sid_out : sw.tmp_keys;
+    int32_t* dst_v = to_out ? perm_out : sw.tmp_vals;
+    const int shift = p * kRadixBits;
+    if (p == 0) {
+      radix_histogram_kernel<IdT><<<tiles, kSortThreads, 0, stream>>>(src_k, int(n), shift, sw.ghist, tiles);
+    } else {
+      radix_histogram_kernel<int32_t><<<tiles, kSortThreads, 0, stream>>>(src_k, int(n), shift, sw.ghist, tiles);
+    }
+    exclusive_scan_kernel<<<1, 1024, 0, stream>>>(sw.ghist, int64_t(tiles) * kRadix);
+    if (p == 0) {
+      radix_scatter_kernel<IdT, true><<<tiles, kSortThreads, 0, stream>>>(
+          src_k, src_v, dst_k, dst_v, int(n), shift, sw.ghist, tiles);
+    } else {
+      radix_scatter_kernel<int32_t, false><<<tiles, kSortThreads, 0, stream>>>(
+          src_k, src_v, dst_k, dst_v, int(n), shift, sw.ghist, tiles);
+    }
+    int st = check_launch("radix sort pass");
+    if (st != TEXB_OK) return st;
+    src_k = dst_k;
+    src_v = dst_v;
+  }
+  return TEXB_OK;
+}
+
+template <typename IdT>
+int run_offsets(const void* sorted_ids, int32_t* sid_out, int32_t* offsets, int64_t n, int64_t m,
+                int32_t* plan_stats, cudaStream_t stream) {
+  const int64_t threads = n + 1;
+  offsets_from_sorted_kernel<IdT><<<unsigned(ceil_div(threads, 256)), 256, 0, stream>>>(
+      static_cast<const IdT*>(sorted_ids), sid_out, offsets, int(n), int(m), plan_stats);
+  int st = check_launch("offsets_from_sorted_kernel");
+  if (st != TEXB_OK) return st;
+  if (m > 0) {
+    int64_t blocks = ceil_div(m, 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    plan_stats_kernel<<<unsigned(blocks), 256, 0, stream>>>(offsets, int(m), plan_stats);
+    st = check_launch("plan_stats_kernel");
+  }
+  return st;
+}
+
+}  // namespace
+
+int ids_inspect_impl(const void* ids, int id_bytes, int64_t n, int32_t* stats_dev,
+                     cudaStream_t stream) {
+  if (id_bytes != 4 && id_bytes != 8)
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "id_bytes must be 4 or 8, got %d", id_bytes);
+  if (n < 0 || !stats_dev || (n > 0 && !ids))
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "ids_inspect: bad pointer or size");
+  init_inspect_stats_kernel<<<1, 32, 0, stream>>>(stats_dev);
+  if (n > 0) {
+    int64_t blocks = ceil_div(n, 256 * 4);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (id_bytes == 4)
+      inspect_ids_kernel<int32_t><<<unsigned(blocks), 256, 0, stream>>>(
+          static_cast<const int32_t*>(ids), n, stats_dev);
+    else
+      inspect_ids_kernel<int64_t><<<unsigned(blocks), 256, 0, stream>>>(
+          static_cast<const int64_t*>(ids), n, stats_dev);
+  }
+  return check_launch("inspect_ids_kernel");
+}
+
+size_t plan_workspace_bytes_impl(int64_t n, int64_t m, int sorted) {
+  (void)m;
+  if (sorted || n <= 0) return 256;
+  return carve_sort_workspace(nullptr, n).bytes;
+}
+
+int plan_build_impl(const void* ids, int id_bytes, int64_t n, int64_t m, int sorted,
+                    int32_t* sid_out, int32_t* perm_out, int32_t* offsets_out,
+                    int32_t* plan_stats_dev, void* workspace, size_t workspace_bytes,
+                    cudaStream_t stream) {
+  if (id_bytes != 4 && id_bytes != 8)
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "id_bytes must be 4 or 8, got %d", id_bytes);
+  if (n < 0 || m < 0) return fail(TEXB_ERR_INVALID_ARGUMENT, "plan_build: negative size");
+  if (n > INT_MAX - 65536 || m > INT_MAX - 65536)
+    return fail(TEXB_ERR_UNSUPPORTED, "plan_build: n and num_segments must be below 2^31 - 65536");
+  if (!offsets_out || !plan_stats_dev || (n > 0 && (!ids || !sid_out)))
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "plan_build: NULL pointer");
+  if (!sorted && n > 0 && !perm_out)
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "plan_build: perm_out is required for unsorted ids");
+  if (!sorted && n > 0 && static_cast<const void*>(sid_out) == ids)
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "plan_build: sid_out may not alias unsorted ids");
+  cudaError_t e = cudaMemsetAsync(plan_stats_dev, 0, 4 * sizeof(int32_t), stream);
+  if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+
+  if (sorted || n == 0) {
+    int32_t* sid_dst = (static_cast<const void*>(sid_out) == ids) ? nullptr : sid_out;
+    if (id_bytes == 4)
+      return run_offsets<int32_t>(ids, sid_dst, offsets_out, n, m, plan_stats_dev, stream);
+    return run_offsets<int64_t>(ids, sid_dst, offsets_out, n, m, plan_stats_dev, stream);
+  }
+
+  SortWorkspace sw = carve_sort_workspace(workspace, n);
+  const size_t pad = reinterpret_cast<uintptr_t>(sw.tmp_keys) - reinterpret_cast<uintptr_t>(workspace);
+  if (!workspace || workspace_bytes + 256 < sw.bytes + pad)
+    return fail(TEXB_ERR_WORKSPACE, "plan workspace: need %zu bytes, got %zu", sw.bytes,
+                workspace_bytes);
+  int st = (id_bytes == 4) ? run_sort<int32_t>(ids, n, m, sid_out, perm_out, sw, stream)
+                           : run_sort<int64_t>(ids, n, m, sid_out, perm_out, sw, stream);
+  if (st != TEXB_OK) return st;
+  // sid_out now holds the sorted ids; offsets come from their run boundaries.
+  return run_offsets<int32_t>(sid_out, nullptr, offsets_out, n, m, plan_stats_dev, stream);
+}
+
+int get_pre_sum_impl(const int32_t* unq_inv, int32_t* pre_sum, int64_t num_total, int64_t num_unq,
+                     cudaStream_t stream) {
+  if (num_total < 0 || num_unq < 0 || !pre_sum || (num_total > 0 && !unq_inv))
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "get_pre_sum: bad pointer or size");
+  if (num_total > INT_MAX - 65536 || num_unq > INT_MAX - 65536)
+    return fail(TEXB_ERR_UNSUPPORTED, "get_pre_sum: sizes must be below 2^31 - 65536");
+  offsets_from_sorted_kernel<int32_t><<<unsigned(ceil_div(num_total + 1, 256)), 256, 0, stream>>>(
+      unq_inv, nullptr, pre_sum, int(num_total), int(num_unq), nullptr);
+  return check_launch("offsets_from_sorted_kernel");
+}
+
+}  // namespace texb

@@ -1,0 +1,249 @@
+"""Segmented scatter reduction with TorchEx's Python interface.
+
+Mirrors the public names and call signatures of
+torchex/operator_py/scatter_op.py (``ScatterData`` :7-21, the autograd
+Functions :24-135 and the aliases :138-141) so code written against TorchEx
+runs unchanged, while every device-side step goes through the C ABI in
+``include/texb_scatter.h``.
+
+Differences a caller can observe:
+  * ``unq_inv`` need not be sorted (a stable sort plan is built once and
+    cached in ``ScatterData``); ids that skip a value give empty segments.
+  * ``scatter_max`` backward works (the reference raises AttributeError at
+    scatter_op.py:107-109); ties send the gradient to the lowest row.
+  * ``arg`` holds the row of ``feats`` as passed by the caller.
+  * ids outside ``[0, num_unq)`` raise ``ValueError`` instead of corrupting
+    memory.
+"""
+from __future__ import annotations
+
+import torch
+from torch.autograd import Function
+
+from .. import _native
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _scratch(nbytes: int, device) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=device)
+
+
+def _as_feats(feats: torch.Tensor) -> torch.Tensor:
+    if not feats.is_cuda:
+        raise RuntimeError("feats must be a CUDAtensor")
+    if feats.dtype != torch.float32:
+        raise RuntimeError(f"feats must be float32, got {feats.dtype}")
+    if feats.ndim != 2:
+        raise RuntimeError(f"feats must be [num_total, channel], got {tuple(feats.shape)}")
+    return feats.contiguous()
+
+
+class ScatterData:
+    """Segment plan shared by every reduction over the same ``unq_inv``.
+
+    Same constructor and public attributes as the reference class
+    (scatter_op.py:7-21): ``unq_inv`` (int32 [num_total], caller order),
+    ``unq_cnts`` ([num_unq, 1], caller dtype), ``preSum`` (int32 [num_unq + 1]),
+    ``max_cnt`` (int) and ``num_unq`` (int).  Added: ``sid`` (segment id at each
+    segment-sorted position), ``perm`` (row of ``feats`` at that position, or
+    ``None`` when the ids arrive sorted), ``is_sorted`` and ``has_empty``.
+
+    ``num_unq`` is ``len(unq_cnts)``; the reference derives it from the last id
+    with a device-to-host copy (scatter_op.py:125-126).  Construction
+    synchronises with the device twice (id statistics, plan statistics).
+    """
+
+    def __init__(self, unq_inv: torch.Tensor, unq_cnts: torch.Tensor) -> None:
+        assert unq_inv.ndim in (1, 2), \
+            f"unq_inv in ScatterData should be 1 or 2-dims, but got {unq_inv.ndim}-dims"
+        assert unq_cnts.ndim in (1, 2), \
+            f"unq_cnts in ScatterData should be 1 or 2-dims, but got {unq_cnts.ndim}-dims"
+        if not unq_inv.is_cuda:
+            raise RuntimeError("unq_inv must be a CUDAtensor")
+        ids = unq_inv.reshape(-1)
+        if ids.dtype not in (torch.int32, torch.int64):
+            ids = ids.long()
+        ids = ids.contiguous()
+        self.unq_cnts = unq_cnts.unsqueeze(-1) if unq_cnts.ndim == 1 else unq_cnts
+        n = ids.numel()
+        m = int(self.unq_cnts.shape[0])
+        dev = ids.device
+        lib = _native.lib()
+        id_bytes = ids.element_size()
+
+        with torch.cuda.device(dev):
+            stats = torch.empty(4, dtype=torch.int32, device=dev)
+            _native.check(lib.texb_ids_inspect(ids.data_ptr(), id_bytes, n, stats.data_ptr(), _stream()),
+                          "texb_ids_inspect")
+            is_sorted, id_min, id_max, _runs = (int(v) for v in stats.cpu())
+            if n > 0 and (id_min < 0 or id_max >= m):
+                raise ValueError(f"unq_inv holds ids in [{id_min}, {id_max}] but unq_cnts "
+                                 f"describes {m} segments")
+            self.is_sorted = bool(is_sorted)
+            self.preSum = torch.empty(m + 1, dtype=torch.int32, device=dev)
+            plan_stats = torch.empty(4, dtype=torch.int32, device=dev)
+            if self.is_sorted:
+                self.perm = None
+                self.sid = ids if ids.dtype == torch.int32 else torch.empty(n, dtype=torch.int32, device=dev)
+                ws = _scratch(lib.texb_plan_workspace_bytes(n, m, 1), dev)
+                perm_ptr = None
+            else:
+                self.sid = torch.empty(n, dtype=torch.int32, device=dev)
+                self.perm = torch.empty(n, dtype=torch.int32, device=dev)
+                ws = _scratch(lib.texb_plan_workspace_bytes(n, m, 0), dev)
+                perm_ptr = self.perm.data_ptr()
+            _native.check(lib.texb_plan_build(ids.data_ptr(), id_bytes, n, m, int(self.is_sorted),
+                                              self.sid.data_ptr(), perm_ptr, self.preSum.data_ptr(),
+                                              plan_stats.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
+                          "texb_plan_build")
+            if ids.dtype == torch.int32:
+                self.unq_inv = ids
+            elif self.is_sorted:
+                self.unq_inv = self.sid
+            else:
+                self.unq_inv = ids.int()
+            max_cnt, num_empty, bad_ids, _ = (int(v) for v in plan_stats.cpu())
+        if bad_ids:
+            raise ValueError(f"{bad_ids} ids of unq_inv lie outside [0, {m})")
+        self.max_cnt = max_cnt
+        self.has_empty = num_empty > 0
+        self.num_unq = m
+
+
+def _reduce(op: int, feats: torch.Tensor, data: ScatterData, want_arg: bool):
+    feats = _as_feats(feats)
+    n, c = feats.shape
+    if n != data.unq_inv.numel():
+        raise RuntimeError(f"feats has {n} rows but ScatterData was built for {data.unq_inv.numel()}")
+    if feats.device != data.sid.device:
+        raise RuntimeError("feats and ScatterData live on different devices")
+    if c < 1:
+        raise RuntimeError("feats needs at least one channel")
+    lib = _native.lib()
+    m = data.num_unq
+    out = feats.new_empty((m, c))
+    arg = torch.empty((m, c), dtype=torch.int32, device=feats.device) if want_arg else None
+    with torch.cuda.device(feats.device):
+        ws = _scratch(lib.texb_reduce_workspace_bytes(n, c), feats.device)
+        _native.check(
+            lib.texb_segment_reduce(op, feats.data_ptr(), data.sid.data_ptr(),
+                                    None if data.perm is None else data.perm.data_ptr(),
+                                    data.preSum.data_ptr(), int(data.has_empty or n == 0), n, c, m,
+                                    out.data_ptr(), None if arg is None else arg.data_ptr(),
+                                    ws.data_ptr(), ws.numel(), _stream()),
+            "texb_segment_reduce")
+    return out, arg
+
+
+def _grad(g: torch.Tensor) -> torch.Tensor:
+    # Autograd may hand over an expanded or strided gradient; the C ABI wants rows.
+    return g.contiguous() if g.dtype == torch.float32 else g.float().contiguous()
+
+
+class ScatterSumFunction(Function):
+
+    @staticmethod
+    def forward(ctx, feats: torch.Tensor, data: ScatterData):
+        """out[s] = sum of the rows of feats whose id is s.
+
+        feats: float32 [num_total, channel]; data: ScatterData of the same
+        num_total.  Returns float32 [num_unq, channel].
+        """
+        out, _ = _reduce(_native.OP_SUM, feats, data, want_arg=False)
+        ctx.save_for_backward(data.unq_inv)
+        ctx.num_unq = data.num_unq
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (unq_inv,) = ctx.saved_tensors
+        g = _grad(g)
+        n, c = unq_inv.numel(), g.shape[1]
+        g_input = g.new_empty((n, c))
+        with torch.cuda.device(g.device):
+            _native.check(_native.lib().texb_scatter_sum_backward(
+                g.data_ptr(), unq_inv.data_ptr(), g_input.data_ptr(), n, c, ctx.num_unq, _stream()),
+                "texb_scatter_sum_backward")
+        return g_input, None
+
+
+class ScatterMeanFunction(Function):
+
+    @staticmethod
+    def forward(ctx, feats: torch.Tensor, data: ScatterData):
+        """out[s] = mean of the rows of feats whose id is s (one fused kernel;
+        the divisor is the number of rows actually reduced)."""
+        out, _ = _reduce(_native.OP_MEAN, feats, data, want_arg=False)
+        ctx.save_for_backward(data.unq_inv, data.preSum)
+        ctx.num_unq = data.num_unq
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        unq_inv, pre_sum = ctx.saved_tensors
+        g = _grad(g)
+        n, c = unq_inv.numel(), g.shape[1]
+        g_input = g.new_empty((n, c))
+        with torch.cuda.device(g.device):
+            _native.check(_native.lib().texb_scatter_mean_backward(
+                g.data_ptr(), unq_inv.data_ptr(), pre_sum.data_ptr(), g_input.data_ptr(), n, c,
+                ctx.num_unq, _stream()), "texb_scatter_mean_backward")
+        return g_input, None
+
+
+class ScatterMaxFunction(Function):
+
+    @staticmethod
+    def forward(ctx, feats: torch.Tensor, data: ScatterData):
+        """(out, arg): per-segment maximum and the row of feats that holds it
+        (int32, lowest row on ties).  arg is not differentiable."""
+        out, arg = _reduce(_native.OP_MAX, feats, data, want_arg=True)
+        ctx.save_for_backward(arg, data.unq_inv)
+        ctx.mark_non_differentiable(arg)
+        ctx.num_unq = data.num_unq
+        return out, arg
+
+    @staticmethod
+    def backward(ctx, g_out, g_arg):
+        arg, unq_inv = ctx.saved_tensors
+        g = _grad(g_out)
+        n, c = unq_inv.numel(), g.shape[1]
+        g_input = g.new_empty((n, c))
+        with torch.cuda.device(g.device):
+            _native.check(_native.lib().texb_scatter_max_backward(
+                g.data_ptr(), arg.data_ptr(), unq_inv.data_ptr(), g_input.data_ptr(), n, c,
+                ctx.num_unq, _stream()), "texb_scatter_max_backward")
+        return g_input, None
+
+
+class GetPreSumFunction(Function):
+
+    @staticmethod
+    def forward(ctx, unq_inv: torch.Tensor):
+        """Offsets of sorted ids: preSum[s] .. preSum[s + 1] is the range of
+        segment s.  As in the reference (scatter_op.py:117-131) the number of
+        segments is the last id + 1, which costs one device-to-host copy."""
+        if unq_inv.dtype != torch.int32:
+            unq_inv = unq_inv.int()
+        unq_inv = unq_inv.contiguous()
+        num_unq = int(unq_inv[-1]) + 1 if unq_inv.numel() else 0
+        pre_sum = unq_inv.new_empty(num_unq + 1)
+        with torch.cuda.device(unq_inv.device):
+            _native.check(_native.lib().texb_get_pre_sum(unq_inv.data_ptr(), pre_sum.data_ptr(),
+                                                         unq_inv.numel(), num_unq, _stream()),
+                          "texb_get_pre_sum")
+        ctx.mark_non_differentiable(pre_sum)
+        return pre_sum
+
+    @staticmethod
+    def backward(ctx, g):
+        return None
+
+
+scatter_sum = ScatterSumFunction.apply
+scatter_mean = ScatterMeanFunction.apply
+scatter_max = ScatterMaxFunction.apply
+getPreSum = GetPreSumFunction.apply
