@@ -49,7 +49,16 @@ int texb_version(void);
  * (torchex/src/scatter/scatter_kernel.cu:173-192). */
 const char* texb_last_error(void);
 
-/* Tuning knobs for experiments ("rows_per_cta", "compensated", "fixup_pdl").
+/* Number of bounded device-side waits that expired since the library was
+ * loaded on the current device (0 in a healthy process).  The reduce kernels
+ * wait for their bulk copies with an iteration limit; when it runs out they
+ * count the event here and return instead of hanging.  Synchronises with the
+ * device.  No counterpart in the reference. */
+int texb_device_status(int* wait_timeouts);
+
+/* Tuning knobs for experiments: "rows_per_cta" (0 = one wave of CTAs),
+ * "staged" (0 register kernel, 1 cp.async ring, 2 bulk-copy ring),
+ * "compensated" (1 = error-free sums), "fixup_pdl".
  * Process-wide; returns TEXB_ERR_INVALID_ARGUMENT for unknown keys or values
  * out of range.  texb_tune_get returns the current value or -1. */
 int texb_tune_set(const char* key, int value);
@@ -64,7 +73,7 @@ int texb_tune_get(const char* key);
 /* One pass over ids[n] (id_bytes = 4 for int32, 8 for int64).
  * Writes stats_dev[0..3] (device int32): [0] 1 if ids are non-decreasing else
  * 0, [1] minimum id, [2] maximum id, [3] number of distinct runs (equals the
- * number of distinct ids when sorted).  n == 0 gives {1, INT32_MAX, -1, 0}. */
+ * number of distinct ids when sorted).  n == 0 gives {1, INT32_MAX, INT32_MIN, 0}. */
 int texb_ids_inspect(const void* ids, int id_bytes, int64_t n,
                      int32_t* stats_dev, void* stream);
 
@@ -88,6 +97,18 @@ int texb_plan_build(const void* ids, int id_bytes, int64_t n,
                     int32_t* plan_stats_dev, void* workspace,
                     size_t workspace_bytes, void* stream);
 
+/* Optional part of the plan: balance_out[balance_len] (balance_len = K + 1,
+ * K >= 1) receives increasing positions, balance_out[0] = 0 and
+ * balance_out[K] = n, that cut the segment-sorted rows sid[n] into K pieces of
+ * equal estimated cost (a row costs 1, closing a segment costs the
+ * "end_cost_x4" knob / 4).  texb_segment_reduce hands each group of lanes a
+ * run of consecutive pieces, so regions full of tiny segments do not finish
+ * later than regions inside one huge segment.  K around 50 times the number
+ * of groups in flight (131072 is plenty for a B200) keeps the cut fine enough.
+ * No counterpart in the reference, whose grid is one block per segment. */
+int texb_plan_balance(const int32_t* sid, int64_t n, int32_t* balance_out,
+                      int balance_len, void* stream);
+
 /* Drop-in for getPreSum_launcher(unq_inv, preSum, num_total)
  * (torchex/src/scatter/scatter.cpp:18, scatter_kernel.cu:173-175): sorted
  * int32 ids -> pre_sum[num_unq + 1].  Unlike the reference every entry is
@@ -107,7 +128,10 @@ size_t texb_reduce_workspace_bytes(int64_t n, int channel);
 /* out[s, :] = reduce over the rows of segment s of feats[N, channel] (fp32,
  * row-major).  sid[n] is the segment id at each segment-sorted position;
  * perm[n] the feats row at that position, or NULL when feats is already in
- * segment order.  offsets may be NULL when has_empty == 0; otherwise the rows
+ * segment order; it must list the rows of one segment in increasing order
+ * (texb_plan_build does) for the lowest-row tie rule of TEXB_OP_MAX to hold.
+ * balance / balance_len: the table of texb_plan_balance, or NULL / 0 for an
+ * even split of the rows.  offsets may be NULL when has_empty == 0; otherwise the rows
  * of empty segments are filled (0 for sum/mean; -FLT_MAX and -1 for max, what
  * the reference kernel writes for an empty range).
  *   TEXB_OP_SUM : fp32 sum, compensated (error-free transformation) so that
@@ -120,9 +144,10 @@ size_t texb_reduce_workspace_bytes(int64_t n, int channel);
  * Limits: n < 2^31, channel >= 1. */
 int texb_segment_reduce(int op, const float* feats, const int32_t* sid,
                         const int32_t* perm, const int32_t* offsets,
-                        int has_empty, int64_t n, int channel,
-                        int64_t num_segments, float* out, int32_t* arg,
-                        void* workspace, size_t workspace_bytes, void* stream);
+                        int has_empty, const int32_t* balance, int balance_len,
+                        int64_t n, int channel, int64_t num_segments,
+                        float* out, int32_t* arg, void* workspace,
+                        size_t workspace_bytes, void* stream);
 
 /* Workspace for the two reference-shaped entry points below: room to expand
  * pre_sum back into per-row segment ids plus texb_reduce_workspace_bytes. */

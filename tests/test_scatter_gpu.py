@@ -44,16 +44,26 @@ def test_tiny_exhaustive(n, m):
         check_forward(feat, srt, cnt, id_dtype=torch.int32, label=f"sorted n={n} m={m} C={channel}")
 
 
-@pytest.mark.parametrize("rows_per_cta", [64, 256, 512, 2048])
-def test_rows_per_cta_does_not_change_results(rows_per_cta):
-    old = _native.tune_get("rows_per_cta")
+@pytest.mark.parametrize("staged", [0, 1, 2])
+@pytest.mark.parametrize("rows_per_cta", [0, 64, 256, 2048])
+def test_every_walker_and_split_gives_the_same_results(staged, rows_per_cta):
+    """Register, cp.async and bulk-copy walkers, with and without the dependent
+    launch of the fix-up kernel, at several CTA sizes."""
+    old = {k: _native.tune_get(k) for k in ("rows_per_cta", "staged", "fixup_pdl")}
     try:
         _native.tune_set("rows_per_cta", rows_per_cta)
-        ids, cnt = W.skewed_ids(60_000, 3_000, seed=3, giant=9_000)
-        feat = W.features(60_000, 64, 3)
-        check_forward(feat, ids, cnt, label=f"rows_per_cta={rows_per_cta}")
+        _native.tune_set("staged", staged)
+        for pdl in (0, 1):
+            _native.tune_set("fixup_pdl", pdl)
+            for channel in (64, 128, 136):
+                ids, cnt = W.skewed_ids(60_000, 3_000, seed=3, giant=9_000)
+                feat = W.features(60_000, channel, 3)
+                check_forward(feat, ids, cnt, label=f"staged={staged} rows_per_cta={rows_per_cta} pdl={pdl} C={channel}")
+                check_forward(feat, torch.sort(ids).values, cnt, label=f"sorted staged={staged} rows_per_cta={rows_per_cta}")
+        assert _native.device_wait_timeouts() == 0
     finally:
-        _native.tune_set("rows_per_cta", old)
+        for k, v in old.items():
+            _native.tune_set(k, v)
 
 
 def test_empty_segments_and_empty_input():

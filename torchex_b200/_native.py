@@ -20,6 +20,7 @@ _SIGNATURES = {
     # name: (restype, argtypes)
     "texb_version": (_c.c_int, []),
     "texb_last_error": (_c.c_char_p, []),
+    "texb_device_status": (_c.c_int, [_c.POINTER(_c.c_int)]),
     "texb_tune_set": (_c.c_int, [_c.c_char_p, _c.c_int]),
     "texb_tune_get": (_c.c_int, [_c.c_char_p]),
     "texb_ids_inspect": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p, _c.c_void_p]),
@@ -29,9 +30,10 @@ _SIGNATURES = {
                                    _c.c_void_p, _c.c_size_t, _c.c_void_p]),
     "texb_get_pre_sum": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p]),
     "texb_reduce_workspace_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int]),
+    "texb_plan_balance": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_int, _c.c_void_p]),
     "texb_segment_reduce": (_c.c_int, [_c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
-                                       _c.c_int, _c.c_int64, _c.c_int, _c.c_int64, _c.c_void_p,
-                                       _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
+                                       _c.c_int, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int, _c.c_int64,
+                                       _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
     "texb_scatter_compat_workspace_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int]),
     "texb_scatter_sum": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int,
                                     _c.c_int, _c.c_int64, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
@@ -47,6 +49,7 @@ _SIGNATURES = {
 }
 
 OP_SUM, OP_MEAN, OP_MAX = 0, 1, 2
+BALANCE_PIECES = 131072  # pieces of the plan's balance table (see texb_plan_balance)
 
 
 def exported_symbols():
@@ -80,6 +83,13 @@ def last_error() -> str:
 def check(status: int, what: str) -> None:
     if status != 0:
         raise RuntimeError(f"{what} failed with status {status}: {last_error()}")
+
+
+def device_wait_timeouts() -> int:
+    """Bounded device-side waits that expired on the current device (0 when healthy)."""
+    v = _c.c_int(0)
+    check(lib().texb_device_status(_c.byref(v)), "texb_device_status")
+    return v.value
 
 
 def tune_set(key: str, value: int) -> None:

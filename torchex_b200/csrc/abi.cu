@@ -19,7 +19,10 @@ int plan_build_impl(const void*, int, int64_t, int64_t, int, int32_t*, int32_t*,
 int get_pre_sum_impl(const int32_t*, int32_t*, int64_t, int64_t, cudaStream_t);
 size_t reduce_workspace_bytes_impl(int64_t, int);
 int segment_reduce_impl(int, const float*, const int32_t*, const int32_t*, const int32_t*, int,
-                        int64_t, int, int64_t, float*, int32_t*, void*, size_t, cudaStream_t);
+                        const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, void*, size_t,
+                        cudaStream_t);
+int plan_balance_impl(const int32_t*, int64_t, int32_t*, int, cudaStream_t);
+int device_status_impl(int*);
 int expand_offsets_impl(const int32_t*, int32_t*, int64_t, int64_t, cudaStream_t);
 int sum_backward_impl(const float*, const int32_t*, float*, int64_t, int, int64_t, cudaStream_t);
 int mean_backward_impl(const float*, const int32_t*, const int32_t*, float*, int64_t, int, int64_t,
@@ -31,7 +34,7 @@ namespace {
 thread_local char t_error[512] = "";
 
 std::mutex g_tuning_mutex;
-Tuning g_tuning = {512, 1, 0};
+Tuning g_tuning = {0, 2, 1, 1, 1, 8};
 bool g_tuning_env_read = false;
 
 int env_int(const char* name, int fallback) {
@@ -42,8 +45,13 @@ int env_int(const char* name, int fallback) {
 
 bool set_knob(Tuning& t, const char* key, int value) {
   if (!std::strcmp(key, "rows_per_cta")) {
-    if (value < 64 || value > (1 << 20)) return false;
+    if (value != 0 && (value < 64 || value > (1 << 20))) return false;
     t.rows_per_cta = value;
+    return true;
+  }
+  if (!std::strcmp(key, "staged")) {
+    if (value < 0 || value > 2) return false;
+    t.staged = value;
     return true;
   }
   if (!std::strcmp(key, "compensated")) {
@@ -56,6 +64,16 @@ bool set_knob(Tuning& t, const char* key, int value) {
     t.fixup_pdl = value;
     return true;
   }
+  if (!std::strcmp(key, "balanced")) {
+    if (value != 0 && value != 1) return false;
+    t.balanced = value;
+    return true;
+  }
+  if (!std::strcmp(key, "end_cost_x4")) {
+    if (value < 0 || value > 1024) return false;
+    t.end_cost_x4 = value;
+    return true;
+  }
   return false;
 }
 
@@ -63,8 +81,11 @@ void read_env_locked() {
   if (g_tuning_env_read) return;
   g_tuning_env_read = true;
   set_knob(g_tuning, "rows_per_cta", env_int("TEXB_ROWS_PER_CTA", g_tuning.rows_per_cta));
+  set_knob(g_tuning, "staged", env_int("TEXB_STAGED", g_tuning.staged));
   set_knob(g_tuning, "compensated", env_int("TEXB_COMPENSATED", g_tuning.compensated));
   set_knob(g_tuning, "fixup_pdl", env_int("TEXB_FIXUP_PDL", g_tuning.fixup_pdl));
+  set_knob(g_tuning, "balanced", env_int("TEXB_BALANCED", g_tuning.balanced));
+  set_knob(g_tuning, "end_cost_x4", env_int("TEXB_END_COST_X4", g_tuning.end_cost_x4));
 }
 }  // namespace
 
@@ -111,10 +132,15 @@ int texb_tune_get(const char* key) {
   if (!key) return -1;
   Tuning t = tuning();
   if (!std::strcmp(key, "rows_per_cta")) return t.rows_per_cta;
+  if (!std::strcmp(key, "staged")) return t.staged;
   if (!std::strcmp(key, "compensated")) return t.compensated;
   if (!std::strcmp(key, "fixup_pdl")) return t.fixup_pdl;
+  if (!std::strcmp(key, "balanced")) return t.balanced;
+  if (!std::strcmp(key, "end_cost_x4")) return t.end_cost_x4;
   return -1;
 }
+
+int texb_device_status(int* wait_timeouts) { return device_status_impl(wait_timeouts); }
 
 int texb_ids_inspect(const void* ids, int id_bytes, int64_t n, int32_t* stats_dev, void* stream) {
   return ids_inspect_impl(ids, id_bytes, n, stats_dev, static_cast<cudaStream_t>(stream));
@@ -143,12 +169,17 @@ size_t texb_reduce_workspace_bytes(int64_t n, int channel) {
   return reduce_workspace_bytes_impl(n, channel);
 }
 
+int texb_plan_balance(const int32_t* sid, int64_t n, int32_t* balance_out, int balance_len,
+                      void* stream) {
+  return plan_balance_impl(sid, n, balance_out, balance_len, static_cast<cudaStream_t>(stream));
+}
+
 int texb_segment_reduce(int op, const float* feats, const int32_t* sid, const int32_t* perm,
-                        const int32_t* offsets, int has_empty, int64_t n, int channel,
-                        int64_t num_segments, float* out, int32_t* arg, void* workspace,
-                        size_t workspace_bytes, void* stream) {
-  return segment_reduce_impl(op, feats, sid, perm, offsets, has_empty, n, channel, num_segments,
-                             out, arg, workspace, workspace_bytes,
+                        const int32_t* offsets, int has_empty, const int32_t* balance,
+                        int balance_len, int64_t n, int channel, int64_t num_segments, float* out,
+                        int32_t* arg, void* workspace, size_t workspace_bytes, void* stream) {
+  return segment_reduce_impl(op, feats, sid, perm, offsets, has_empty, balance, balance_len, n,
+                             channel, num_segments, out, arg, workspace, workspace_bytes,
                              static_cast<cudaStream_t>(stream));
 }
 
@@ -176,7 +207,7 @@ static int compat_reduce(int op, const float* feats, const int32_t* pre_sum, flo
   int st = expand_offsets_impl(pre_sum, sid, num_total, num_unq, stream);
   if (st != TEXB_OK) return st;
   // The reference kernels write every row, including those of empty ranges.
-  return segment_reduce_impl(op, feats, sid, nullptr, pre_sum, /*has_empty=*/1, num_total, channel,
+  return segment_reduce_impl(op, feats, sid, nullptr, pre_sum, /*has_empty=*/1, nullptr, 0, num_total, channel,
                              num_unq, out, arg, reinterpret_cast<void*>(base + sid_bytes),
                              workspace_bytes - pad - sid_bytes, stream);
 }

@@ -18,9 +18,12 @@ int check_launch(const char* what);
 
 // Tuning knobs (see texb_tune_set).
 struct Tuning {
-  int rows_per_cta;  // rows of the segment-sorted order handled by one CTA
+  int rows_per_cta;  // rows of the segment-sorted order handled by one CTA; 0 = one wave
+  int staged;        // row staging where the layout allows: 0 registers, 1 cp.async ring, 2 bulk-copy ring
   int compensated;   // 1: error-free (two-sum) accumulation in sum / mean
   int fixup_pdl;     // 1: launch the fix-up kernel with programmatic dependent launch
+  int balanced;      // 1: use the plan's balance table to cut the rows by estimated cost
+  int end_cost_x4;   // cost of closing a segment, in quarter rows, for that table
 };
 Tuning tuning();
 

@@ -121,6 +121,31 @@ __global__ void plan_stats_kernel(const int32_t* __restrict__ offsets, int m, in
   }
 }
 
+// ---- balance table ------------------------------------------------------------------
+// cost(p) = 4 p + end_cost_x4 * (number of segments that end before p), taken
+// as sid[p] - sid[0] (exact for dense ids, an over-estimate across gaps, always
+// non-decreasing).  table[k] is the first position whose cost reaches k / K of
+// the total, so consecutive entries cut the rows into K pieces of equal cost.
+__global__ void balance_table_kernel(const int32_t* __restrict__ sid, int n, int end_cost_x4,
+                                     int32_t* __restrict__ table, int K) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k > K) return;
+  if (k == 0) { table[0] = 0; return; }
+  if (k == K) { table[K] = n; return; }
+  const long long first = sid[0];
+  const long long total = 4LL * n + (long long)end_cost_x4 * (sid[n - 1] - first + 1);
+  // smallest target that piece k must reach, without overflow: total < 2^34 * 1024
+  const long long target = (long long)(((__int128)total * k) / K);
+  int lo = 0, hi = n;  // cost(lo) < target <= cost(hi), with cost(n) = total
+  if (4LL * 0 + (long long)end_cost_x4 * 0 >= target) { table[k] = 0; return; }
+  while (hi - lo > 1) {
+    const int mid = lo + ((hi - lo) >> 1);
+    const long long c = 4LL * mid + (long long)end_cost_x4 * (__ldg(sid + mid) - first);
+    if (c < target) lo = mid; else hi = mid;
+  }
+  table[k] = hi;
+}
+
 // ---- radix sort passes -------------------------------------------------------------
 
 template <typename IdT>
@@ -385,6 +410,21 @@ int plan_build_impl(const void* ids, int id_bytes, int64_t n, int64_t m, int sor
   if (st != TEXB_OK) return st;
   // sid_out now holds the sorted ids; offsets come from their run boundaries.
   return run_offsets<int32_t>(sid_out, nullptr, offsets_out, n, m, plan_stats_dev, stream);
+}
+
+int plan_balance_impl(const int32_t* sid, int64_t n, int32_t* table, int table_len, cudaStream_t stream) {
+  if (n < 0 || !table || table_len < 2 || (n > 0 && !sid))
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "plan_balance: bad pointer or size");
+  if (n > INT_MAX - 65536) return fail(TEXB_ERR_UNSUPPORTED, "plan_balance: n must be below 2^31 - 65536");
+  const int K = table_len - 1;
+  if (n == 0) {
+    cudaError_t e = cudaMemsetAsync(table, 0, size_t(table_len) * sizeof(int32_t), stream);
+    if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    return TEXB_OK;
+  }
+  balance_table_kernel<<<unsigned(ceil_div(table_len, 256)), 256, 0, stream>>>(
+      sid, int(n), tuning().end_cost_x4, table, K);
+  return check_launch("balance_table_kernel");
 }
 
 int get_pre_sum_impl(const int32_t* unq_inv, int32_t* pre_sum, int64_t num_total, int64_t num_unq,

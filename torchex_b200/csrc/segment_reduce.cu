@@ -3,17 +3,25 @@
 // Work is split by ROWS of the segment-sorted order, never by segments, so a
 // 100 000-row segment and 100 000 one-row segments cost the same:
 //
-//   * a CTA owns `rows_per_cta` consecutive sorted positions; inside it every
-//     "group" of LPR lanes (LPR * VEC channels wide, one 128-bit load per lane
-//     when VEC == 4) owns a consecutive sub-range and walks it row by row with
-//     several row loads in flight, keeping one running accumulator per channel;
+//   * a CTA owns `rows_per_cta` consecutive sorted positions (by default the
+//     rows are divided evenly over exactly one resident wave of CTAs); inside it
+//     every "group" of LPR lanes (LPR * VEC channels wide, one 128-bit access per
+//     lane when VEC == 4) owns a consecutive sub-range and walks it row by row,
+//     keeping one running accumulator per channel;
 //   * a segment that starts and ends inside a group's sub-range is written
-//     straight to `out`; a run that touches the edge of the sub-range is left
-//     in shared memory, and one group then stitches the CTA's edge runs in
-//     position order (segments that live inside one CTA finish here);
+//     straight to `out`; a run that touches the edge of the sub-range is kept,
+//     and one group then stitches the CTA's edge runs in position order
+//     (segments that live inside one CTA finish here);
 //   * runs that cross a CTA edge go to a small workspace (two records per CTA)
 //     and the fix-up kernel stitches those chains, again in position order.
 //
+// Two walkers share that skeleton.  The staged kernel (rows of 64..128 channels
+// per slab) streams rows with cp.async into a per-lane ring in shared memory,
+// two batches ahead of the batch being reduced; the register kernel (every other
+// layout) keeps eight row loads in flight in registers.
+//
+// Sums carry an error-free compensation term (TwoSum) through every add and
+// every merge, so a 175 000-row segment stays within a few ulp of the exact sum.
 // The combination order depends only on the geometry, so results are
 // bit-reproducible, and no floating-point atomic is used anywhere.
 //
@@ -34,102 +42,136 @@ constexpr unsigned kValid = 1u;
 constexpr unsigned kOpenLeft = 2u;   // segment began before this range
 constexpr unsigned kOpenRight = 4u;  // segment continues after this range
 
-template <int VEC>
-struct Acc {
-  float a[VEC];     // running sum, or running maximum
-  uint32_t b[VEC];  // bits of the compensation term, or row index of the maximum
-};
-
 // ---- operators --------------------------------------------------------------
+// State<VEC> lives in registers; pack / unpack move it through two arrays of
+// VEC 32-bit words (shared memory or the workspace).
 
-struct OpSumComp {  // sum with an error-free two-sum; value = a + b
+struct OpSumComp {  // fp32 sum + error-free two-sum: (s, c) with s + c the exact running sum
   static constexpr bool kIsMax = false;
+  template <int VEC> struct State { float s[VEC]; float c[VEC]; };
   template <int VEC>
-  static __device__ __forceinline__ void init(Acc<VEC>& x) {
+  static __device__ __forceinline__ void init(State<VEC>& x) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) { x.a[k] = 0.f; x.b[k] = 0u; }
+    for (int k = 0; k < VEC; ++k) { x.s[k] = 0.f; x.c[k] = 0.f; }
   }
+  // Knuth's TwoSum: t + e == s + v exactly, whatever the magnitudes.
   static __device__ __forceinline__ void two_sum(float s, float v, float& t, float& e) {
     t = s + v;
-    float bp = t - s;
+    const float bp = t - s;
     e = (s - (t - bp)) + (v - bp);
   }
   template <int VEC>
-  static __device__ __forceinline__ void add(Acc<VEC>& x, const float (&v)[VEC], int) {
+  static __device__ __forceinline__ void add(State<VEC>& x, const float (&v)[VEC], int) {
 #pragma unroll
     for (int k = 0; k < VEC; ++k) {
       float t, e;
-      two_sum(x.a[k], v[k], t, e);
-      x.b[k] = __float_as_uint(__uint_as_float(x.b[k]) + e);
-      x.a[k] = t;
+      two_sum(x.s[k], v[k], t, e);
+      x.c[k] += e;
+      x.s[k] = t;
     }
   }
   template <int VEC>
-  static __device__ __forceinline__ void merge(Acc<VEC>& x, const Acc<VEC>& y) {
+  static __device__ __forceinline__ void merge(State<VEC>& x, const State<VEC>& y) {
 #pragma unroll
     for (int k = 0; k < VEC; ++k) {
       float t, e;
-      two_sum(x.a[k], y.a[k], t, e);
-      x.b[k] = __float_as_uint((__uint_as_float(x.b[k]) + __uint_as_float(y.b[k])) + e);
-      x.a[k] = t;
+      two_sum(x.s[k], y.s[k], t, e);
+      x.c[k] = (x.c[k] + y.c[k]) + e;
+      x.s[k] = t;
     }
   }
   template <int VEC>
-  static __device__ __forceinline__ float value(const Acc<VEC>& x, int k) {
-    return x.a[k] + __uint_as_float(x.b[k]);
+  static __device__ __forceinline__ void pack(const State<VEC>& x, uint32_t (&wa)[VEC], uint32_t (&wb)[VEC]) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) { wa[k] = __float_as_uint(x.s[k]); wb[k] = __float_as_uint(x.c[k]); }
   }
+  template <int VEC>
+  static __device__ __forceinline__ void unpack(State<VEC>& x, const uint32_t (&wa)[VEC], const uint32_t (&wb)[VEC]) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) { x.s[k] = __uint_as_float(wa[k]); x.c[k] = __uint_as_float(wb[k]); }
+  }
+  template <int VEC>
+  static __device__ __forceinline__ float value(const State<VEC>& x, int k) { return x.s[k] + x.c[k]; }
+  template <int VEC>
+  static __device__ __forceinline__ int index(const State<VEC>&, int) { return 0; }
 };
 
-struct OpSumPlain {  // plain fp32 running sum
+struct OpSumPlain {  // plain fp32 running sum (the "compensated" knob set to 0)
   static constexpr bool kIsMax = false;
+  template <int VEC> struct State { float s[VEC]; };
   template <int VEC>
-  static __device__ __forceinline__ void init(Acc<VEC>& x) {
+  static __device__ __forceinline__ void init(State<VEC>& x) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) { x.a[k] = 0.f; x.b[k] = 0u; }
+    for (int k = 0; k < VEC; ++k) x.s[k] = 0.f;
   }
   template <int VEC>
-  static __device__ __forceinline__ void add(Acc<VEC>& x, const float (&v)[VEC], int) {
+  static __device__ __forceinline__ void add(State<VEC>& x, const float (&v)[VEC], int) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) x.a[k] += v[k];
+    for (int k = 0; k < VEC; ++k) x.s[k] += v[k];
   }
   template <int VEC>
-  static __device__ __forceinline__ void merge(Acc<VEC>& x, const Acc<VEC>& y) {
+  static __device__ __forceinline__ void merge(State<VEC>& x, const State<VEC>& y) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) x.a[k] += y.a[k];
+    for (int k = 0; k < VEC; ++k) x.s[k] += y.s[k];
   }
   template <int VEC>
-  static __device__ __forceinline__ float value(const Acc<VEC>& x, int k) {
-    return x.a[k];
+  static __device__ __forceinline__ void pack(const State<VEC>& x, uint32_t (&wa)[VEC], uint32_t (&wb)[VEC]) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) { wa[k] = __float_as_uint(x.s[k]); wb[k] = 0u; }
   }
+  template <int VEC>
+  static __device__ __forceinline__ void unpack(State<VEC>& x, const uint32_t (&wa)[VEC], const uint32_t (&)[VEC]) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) x.s[k] = __uint_as_float(wa[k]);
+  }
+  template <int VEC>
+  static __device__ __forceinline__ float value(const State<VEC>& x, int k) { return x.s[k]; }
+  template <int VEC>
+  static __device__ __forceinline__ int index(const State<VEC>&, int) { return 0; }
 };
 
-struct OpMax {  // maximum + row index; ties -> lowest row; NaN never wins
+// Maximum + row.  Rows reach `add` and pieces reach `merge` in increasing row
+// order within a segment (the plan's permutation is stable), so a strict ">"
+// keeps the lowest row on ties.  The running value starts at -inf so that a row
+// equal to -FLT_MAX still records its index, like the reference's ">=" against
+// its -FLT_MAX start (scatter_kernel.cu:139-151); a channel no row claimed
+// reports -FLT_MAX / -1, the reference's untouched state.  NaN and -inf never win.
+struct OpMax {
   static constexpr bool kIsMax = true;
+  template <int VEC> struct State { float v[VEC]; int i[VEC]; };
   template <int VEC>
-  static __device__ __forceinline__ void init(Acc<VEC>& x) {
+  static __device__ __forceinline__ void init(State<VEC>& x) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) { x.a[k] = -FLT_MAX; x.b[k] = 0xffffffffu; }
+    for (int k = 0; k < VEC; ++k) { x.v[k] = -INFINITY; x.i[k] = -1; }
   }
   template <int VEC>
-  static __device__ __forceinline__ void add(Acc<VEC>& x, const float (&v)[VEC], int row) {
+  static __device__ __forceinline__ void add(State<VEC>& x, const float (&v)[VEC], int row) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-      bool take = (v[k] > x.a[k]) || (v[k] == x.a[k] && uint32_t(row) < x.b[k]);
-      if (take) { x.a[k] = v[k]; x.b[k] = uint32_t(row); }
-    }
+    for (int k = 0; k < VEC; ++k)
+      if (v[k] > x.v[k]) { x.v[k] = v[k]; x.i[k] = row; }
   }
   template <int VEC>
-  static __device__ __forceinline__ void merge(Acc<VEC>& x, const Acc<VEC>& y) {
+  static __device__ __forceinline__ void merge(State<VEC>& x, const State<VEC>& y) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-      bool take = (y.a[k] > x.a[k]) || (y.a[k] == x.a[k] && y.b[k] < x.b[k]);
-      if (take) { x.a[k] = y.a[k]; x.b[k] = y.b[k]; }
-    }
+    for (int k = 0; k < VEC; ++k)
+      if (y.v[k] > x.v[k]) { x.v[k] = y.v[k]; x.i[k] = y.i[k]; }
   }
   template <int VEC>
-  static __device__ __forceinline__ float value(const Acc<VEC>& x, int k) {
-    return x.a[k];
+  static __device__ __forceinline__ void pack(const State<VEC>& x, uint32_t (&wa)[VEC], uint32_t (&wb)[VEC]) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) { wa[k] = __float_as_uint(x.v[k]); wb[k] = uint32_t(x.i[k]); }
   }
+  template <int VEC>
+  static __device__ __forceinline__ void unpack(State<VEC>& x, const uint32_t (&wa)[VEC], const uint32_t (&wb)[VEC]) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) { x.v[k] = __uint_as_float(wa[k]); x.i[k] = int(wb[k]); }
+  }
+  template <int VEC>
+  static __device__ __forceinline__ float value(const State<VEC>& x, int k) {
+    return x.i[k] < 0 ? -FLT_MAX : x.v[k];
+  }
+  template <int VEC>
+  static __device__ __forceinline__ int index(const State<VEC>& x, int k) { return x.i[k]; }
 };
 
 // ---- small device helpers -----------------------------------------------------
@@ -166,40 +208,39 @@ __device__ __forceinline__ void load_words(const uint32_t* p, uint32_t (&v)[VEC]
   }
 }
 
-// Accumulator <-> two arrays of VEC 32-bit words (shared or global memory).
-template <int VEC>
-__device__ __forceinline__ void store_acc(uint32_t* pa, uint32_t* pb, const Acc<VEC>& x) {
-  uint32_t wa[VEC];
-#pragma unroll
-  for (int k = 0; k < VEC; ++k) wa[k] = __float_as_uint(x.a[k]);
+template <class Op, int VEC>
+__device__ __forceinline__ void store_state(uint32_t* pa, uint32_t* pb,
+                                            const typename Op::template State<VEC>& x) {
+  uint32_t wa[VEC], wb[VEC];
+  Op::template pack<VEC>(x, wa, wb);
   store_words<VEC>(pa, wa);
-  store_words<VEC>(pb, x.b);
+  store_words<VEC>(pb, wb);
 }
 
-template <int VEC>
-__device__ __forceinline__ void load_acc(const uint32_t* pa, const uint32_t* pb, Acc<VEC>& x) {
-  uint32_t wa[VEC];
+template <class Op, int VEC>
+__device__ __forceinline__ void load_state(const uint32_t* pa, const uint32_t* pb,
+                                           typename Op::template State<VEC>& x) {
+  uint32_t wa[VEC], wb[VEC];
   load_words<VEC>(pa, wa);
-  load_words<VEC>(pb, x.b);
-#pragma unroll
-  for (int k = 0; k < VEC; ++k) x.a[k] = __uint_as_float(wa[k]);
+  load_words<VEC>(pb, wb);
+  Op::template unpack<VEC>(x, wa, wb);
 }
 
 // Writes one finished segment row.  `ch` is this lane's first channel.
 template <class Op, int VEC>
 __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __restrict__ arg,
-                                          int64_t seg, int C, int ch, bool lane_on,
-                                          const Acc<VEC>& x, int cnt, bool mean) {
+                                       int seg, int C, int ch, bool lane_on,
+                                       const typename Op::template State<VEC>& x, int cnt, bool mean) {
   if (!lane_on) return;
   float r[VEC];
 #pragma unroll
   for (int k = 0; k < VEC; ++k) r[k] = Op::template value<VEC>(x, k);
   if (!Op::kIsMax && mean) {
-    float c = float(cnt);
+    const float c = float(cnt);
 #pragma unroll
     for (int k = 0; k < VEC; ++k) r[k] = __fdiv_rn(r[k], c);
   }
-  float* po = out + seg * C + ch;
+  float* po = out + int64_t(seg) * C + ch;
   if constexpr (VEC == 4) {
     *reinterpret_cast<float4*>(po) = make_float4(r[0], r[1], r[2], r[3]);
   } else {
@@ -207,12 +248,13 @@ __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __re
     for (int k = 0; k < VEC; ++k) po[k] = r[k];
   }
   if constexpr (Op::kIsMax) {
-    int32_t* pa = arg + seg * C + ch;
+    int32_t* pa = arg + int64_t(seg) * C + ch;
     if constexpr (VEC == 4) {
-      *reinterpret_cast<int4*>(pa) = make_int4(int(x.b[0]), int(x.b[1]), int(x.b[2]), int(x.b[3]));
+      *reinterpret_cast<int4*>(pa) = make_int4(Op::template index<VEC>(x, 0), Op::template index<VEC>(x, 1),
+                                               Op::template index<VEC>(x, 2), Op::template index<VEC>(x, 3));
     } else {
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) pa[k] = int(x.b[k]);
+      for (int k = 0; k < VEC; ++k) pa[k] = Op::template index<VEC>(x, k);
     }
   }
 }
@@ -226,14 +268,97 @@ struct Workspace {
   int4* meta;     // [num_slabs * num_ctas * 2]
 };
 
-// ---- main kernel --------------------------------------------------------------
+// Stitches the edge runs a CTA left in shared memory, in position order (group
+// 0 only).  Segments that live inside the CTA are written to `out`; a run open
+// at the CTA's left or right edge becomes the CTA's head or tail record.
+template <class Op, int VEC, int LPR>
+__device__ __forceinline__ void stitch_cta(const uint32_t* s_vec, const int* s_sid, const int* s_cnt,
+                                           const unsigned* s_flag, float* __restrict__ out,
+                                           int32_t* __restrict__ arg, Workspace ws, int C, int ch,
+                                           bool lane_on, int lane_g, int group, bool mean) {
+  using State = typename Op::template State<VEC>;
+  constexpr int GPC = kCtaThreads / LPR;
+  constexpr int CPS = LPR * VEC;
+  constexpr int SLOTS = 2 * GPC;
+  if (group != 0) return;
+  const int64_t rec = (int64_t(blockIdx.y) * gridDim.x + blockIdx.x) * 2;
+  bool have = false, cur_open_left = false;
+  int cur_sid = 0, cur_cnt = 0;
+  unsigned head_flag = 0u;
+  State cur;
+  Op::template init<VEC>(cur);
+  for (int slot = 0; slot < SLOTS; ++slot) {
+    const unsigned f = s_flag[slot];
+    if (!(f & kValid)) continue;
+    State x;
+    const uint32_t* pa = s_vec + slot * 2 * CPS + lane_g * VEC;
+    load_state<Op, VEC>(pa, pa + CPS, x);
+    if (!have) {
+      cur = x;
+      cur_sid = s_sid[slot];
+      cur_cnt = s_cnt[slot];
+      cur_open_left = (f & kOpenLeft) != 0u;
+      have = true;
+    } else {
+      Op::template merge<VEC>(cur, x);
+      cur_cnt += s_cnt[slot];
+    }
+    if (!(f & kOpenRight)) {
+      if (!cur_open_left) {
+        store_out<Op, VEC>(out, arg, cur_sid, C, ch, lane_on, cur, cur_cnt, mean);
+      } else {
+        uint32_t* ga = ws.vec + rec * 2 * CPS + lane_g * VEC;
+        store_state<Op, VEC>(ga, ga + CPS, cur);
+        head_flag = kValid | kOpenLeft;
+        if (lane_g == 0) ws.meta[rec] = make_int4(cur_sid, cur_cnt, int(head_flag), 0);
+      }
+      have = false;
+    }
+  }
+  if (head_flag == 0u && lane_g == 0) ws.meta[rec] = make_int4(0, 0, 0, 0);
+  if (have) {
+    uint32_t* ga = ws.vec + (rec + 1) * 2 * CPS + lane_g * VEC;
+    store_state<Op, VEC>(ga, ga + CPS, cur);
+    const unsigned f = kValid | kOpenRight | (cur_open_left ? kOpenLeft : 0u);
+    if (lane_g == 0) ws.meta[rec + 1] = make_int4(cur_sid, cur_cnt, int(f), 0);
+  } else if (lane_g == 0) {
+    ws.meta[rec + 1] = make_int4(0, 0, 0, 0);
+  }
+}
+
+// Range of sorted positions walked by one group.  With a balance table (K + 1
+// increasing positions that cut the rows into K pieces of equal estimated cost,
+// built with the plan) group gi of G takes pieces [gi K / G, (gi + 1) K / G);
+// without one the rows are cut evenly: rows_per_cta per CTA, rows_per_group per group.
+struct Split {
+  const int32_t* balance;  // NULL: even split
+  int balance_k;
+  int rows_per_cta, rows_per_group, num_ctas;
+};
+
+__device__ __forceinline__ void group_range(const Split& sp, int n, int group, int gpc, int& g0, int& g1) {
+  if (sp.balance) {
+    const long long gi = (long long)blockIdx.x * gpc + group;
+    const long long G = (long long)gridDim.x * gpc;
+    g0 = __ldg(sp.balance + int(gi * sp.balance_k / G));
+    g1 = __ldg(sp.balance + int((gi + 1) * sp.balance_k / G));
+  } else {
+    const int c0 = blockIdx.x * sp.rows_per_cta;
+    const int c1 = min(c0 + sp.rows_per_cta, n);
+    g0 = min(c0 + group * sp.rows_per_group, c1);
+    g1 = min(g0 + sp.rows_per_group, c1);
+  }
+}
+
+// ---- register kernel ------------------------------------------------------------
 
 template <class Op, int VEC, int LPR, bool HAS_PERM>
 __global__ void __launch_bounds__(kCtaThreads)
 segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict__ sid,
                       const int32_t* __restrict__ perm, float* __restrict__ out,
                       int32_t* __restrict__ arg, Workspace ws, int n, int C,
-                      int rows_per_cta, int rows_per_group, bool mean) {
+                      Split sp, bool mean) {
+  using State = typename Op::template State<VEC>;
   constexpr int GPC = kCtaThreads / LPR;           // groups per CTA
   constexpr int CPS = LPR * VEC;                   // channels per slab
   constexpr int U = (LPR >= 8) ? 8 : LPR;          // row loads in flight per group
@@ -252,10 +377,8 @@ segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict
   const int ch = blockIdx.y * CPS + lane_g * VEC;  // first channel of this lane
   const bool lane_on = ch < C;                     // VEC == 4 implies C % 4 == 0
 
-  const int c0 = blockIdx.x * rows_per_cta;
-  const int c1 = min(c0 + rows_per_cta, n);
-  const int g0 = c0 + group * rows_per_group;
-  const int g1 = min(g0 + rows_per_group, c1);
+  int g0, g1;
+  group_range(sp, n, group, GPC, g0, g1);
 
   if (lane_g == 0) {
     s_flag[2 * group] = 0u;
@@ -267,7 +390,7 @@ segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict
     const bool first_open_left = (g0 > 0) && (__ldg(sid + g0 - 1) == cur_sid);
     bool is_first = true;
     int cnt = 0;
-    Acc<VEC> acc;
+    State acc;
     Op::template init<VEC>(acc);
 
     // Ends the current run.  open_right is only ever true for the last run.
@@ -278,7 +401,7 @@ segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict
       } else {
         const int slot = 2 * group + (open_right ? 1 : 0);
         uint32_t* pa = s_vec + slot * 2 * CPS + lane_g * VEC;
-        store_acc<VEC>(pa, pa + CPS, acc);
+        store_state<Op, VEC>(pa, pa + CPS, acc);
         if (lane_g == 0) {
           s_sid[slot] = cur_sid;
           s_cnt[slot] = cnt;
@@ -330,53 +453,331 @@ segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict
     close_run(open_right);
   }
   __syncthreads();
+  stitch_cta<Op, VEC, LPR>(s_vec, s_sid, s_cnt, s_flag, out, arg, ws, C, ch, lane_on, lane_g,
+                           group, mean);
+}
 
-  // Stitch the edge runs of this CTA in position order (group 0 only).
-  if (group == 0) {
-    const int64_t rec = (int64_t(blockIdx.y) * gridDim.x + blockIdx.x) * 2;
-    bool have = false, cur_open_left = false;
-    int cur_sid = 0, cur_cnt = 0;
-    unsigned head_flag = 0u;
-    Acc<VEC> cur;
-    Op::template init<VEC>(cur);
-    for (int slot = 0; slot < SLOTS; ++slot) {
-      const unsigned f = s_flag[slot];
-      if (!(f & kValid)) continue;
-      Acc<VEC> x;
-      const uint32_t* pa = s_vec + slot * 2 * CPS + lane_g * VEC;
-      load_acc<VEC>(pa, pa + CPS, x);
-      if (!have) {
-        cur = x;
-        cur_sid = s_sid[slot];
-        cur_cnt = s_cnt[slot];
-        cur_open_left = (f & kOpenLeft) != 0u;
-        have = true;
-      } else {
-        Op::template merge<VEC>(cur, x);
-        cur_cnt += s_cnt[slot];
+// ---- staged kernel --------------------------------------------------------------
+// Rows of 64..128 fp32 channels per slab (LPR 16 or 32, 128-bit lanes).  Rows are
+// not loaded into registers: every lane streams its own 16 bytes of each row into
+// a private ring in shared memory with cp.async (L2 -> shared, bypassing L1 and
+// the register file), two batches of eight rows ahead of the batch being reduced.
+// A lane only ever reads back bytes it copied itself, so the ring needs no
+// barrier: cp.async.wait_group on the lane's own copy groups is the only
+// synchronisation.  Run ends come from one ballot per 32-position tile; a batch
+// without a run end takes a branch-free path of eight shared-memory loads and
+// accumulations.
+
+__device__ __forceinline__ void cp_async_16(unsigned smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Bulk (TMA) copy of one row slab, global -> this CTA's shared memory, signalling
+// an mbarrier with the byte count.  Never multicast; the source is always this
+// GPU's own memory.  Source, destination and size are multiples of 16 bytes.
+__device__ __forceinline__ void bulk_copy_g2s(unsigned smem_dst, const void* gmem_src, unsigned bytes,
+                                              unsigned bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_dst), "l"(gmem_src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0u;
+}
+
+// Number of bounded waits that gave up (sticky; read with texb_device_status).
+__device__ int g_wait_timeouts = 0;
+
+// Waits for a phase of an mbarrier, at most kWaitSpins polls (each poll itself
+// blocks for a bounded, hardware-defined time).  On expiry the event is counted
+// and the caller carries on with whatever the ring holds: the result is wrong
+// but the kernel returns and the context stays usable.
+constexpr int kWaitSpins = 1 << 20;
+__device__ __forceinline__ void mbar_wait_bounded(unsigned bar, unsigned parity) {
+  for (int it = 0; it < kWaitSpins; ++it)
+    if (mbar_try_wait(bar, parity)) return;
+  atomicAdd(&g_wait_timeouts, 1);
+}
+
+constexpr int kStageBatch = 8;    // rows per copy batch
+constexpr int kStageDepth = 3;    // groups in the ring: two in flight, one being reduced
+constexpr int kStageTile = 32;    // positions per metadata tile
+constexpr int kStageSlotBytes = kCtaThreads * 16;  // one row slot for the whole CTA
+constexpr int kStageRingBytes = kStageBatch * kStageDepth * kStageSlotBytes;
+
+template <class Op, int LPR, bool HAS_PERM, bool BULK>
+__global__ void __launch_bounds__(kCtaThreads, 2)
+segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __restrict__ sid,
+                             const int32_t* __restrict__ perm, float* __restrict__ out,
+                             int32_t* __restrict__ arg, Workspace ws, int n, int C,
+                             Split sp, bool mean) {
+  constexpr int VEC = 4;
+  using State = typename Op::template State<VEC>;
+  constexpr int GPC = kCtaThreads / LPR;
+  constexpr int CPS = LPR * VEC;
+  constexpr int SLOTS = 2 * GPC;
+  constexpr int B = kStageBatch, S = kStageDepth, T = kStageTile;
+  constexpr int NREG = T / LPR;  // tile positions held per lane
+  static_assert(LPR == 16 || LPR == 32, "staged kernel handles 16 or 32 lanes per row");
+  static_assert((S - 1) * B <= T && T % B == 0 && LPR % B == 0, "the copy front must stay within two tiles");
+
+  extern __shared__ __align__(16) unsigned char s_dyn[];
+  uint32_t* s_vec = reinterpret_cast<uint32_t*>(s_dyn);  // the ring, reused after the walk
+  __shared__ int s_sid[SLOTS];
+  __shared__ int s_cnt[SLOTS];
+  __shared__ unsigned s_flag[SLOTS];
+  __shared__ __align__(8) unsigned long long s_bar[BULK ? GPC * S : 1];  // one mbarrier per (group, stage)
+
+  const int lane_g = threadIdx.x & (LPR - 1);
+  const int group = threadIdx.x / LPR;
+  const int lane_base = (threadIdx.x & 31) & ~(LPR - 1);  // first lane of the group
+  const unsigned gmask = (LPR == 32) ? 0xffffffffu : (((1u << LPR) - 1u) << lane_base);
+  const int ch = blockIdx.y * CPS + lane_g * VEC;
+  const bool lane_on = ch < C;
+
+  int g0, g1;
+  group_range(sp, n, group, GPC, g0, g1);
+
+  if (lane_g == 0) {
+    s_flag[2 * group] = 0u;
+    s_flag[2 * group + 1] = 0u;
+  }
+  if constexpr (BULK) {
+    if (lane_g == 0) {
+#pragma unroll
+      for (int st = 0; st < S; ++st)
+        mbar_init(unsigned(__cvta_generic_to_shared(&s_bar[group * S + st])), 1u);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+  }
+
+  // Edge runs are parked in registers until the ring can be reused.
+  State head_acc, tail_acc;
+  int head_sid = 0, head_cnt = 0, tail_sid = 0, tail_cnt = 0;
+  unsigned head_flag = 0u, tail_flag = 0u;
+  Op::template init<VEC>(head_acc);
+  Op::template init<VEC>(tail_acc);
+
+  if (g0 < g1) {
+    const int L = g1 - g0;
+    const int nb = (L + B - 1) / B;
+    // Inactive lanes (channel tail of the last slab) copy channel 0 instead of
+    // branching around every access; their results are never stored.
+    const float* lane_src = feats + (lane_on ? ch : 0);
+    // cp.async layout: slot s of the CTA at s * kStageSlotBytes, lane t at + 16 t.
+    // Bulk layout: each group owns S * B consecutive row slabs of kRowBytes.
+    constexpr int kRowBytes = CPS * 4;
+    constexpr int kSlotFloat4 = BULK ? LPR : kCtaThreads;  // float4 stride between slots
+    const int row_bytes = min(CPS, C - blockIdx.y * CPS) * 4;  // the last slab may be narrower
+    const unsigned ring_addr = BULK
+        ? unsigned(__cvta_generic_to_shared(s_dyn)) + unsigned(group * S * B) * kRowBytes
+        : unsigned(__cvta_generic_to_shared(s_dyn)) + threadIdx.x * 16;
+    const float4* ring = BULK
+        ? reinterpret_cast<const float4*>(s_dyn) + group * S * B * LPR + lane_g
+        : reinterpret_cast<const float4*>(s_dyn) + threadIdx.x;
+    const unsigned bar0 = unsigned(__cvta_generic_to_shared(&s_bar[BULK ? group * S : 0]));
+    const float* slab_src = feats + blockIdx.y * CPS;
+
+    // Tile metadata: lane_g holds positions t * T + r * LPR + lane_g (r < NREG).
+    int cur_sid_r[NREG], cur_row_r[NREG], nxt_sid_r[NREG], nxt_row_r[NREG];
+    unsigned cur_mask = 0u, nxt_mask = 0u;  // bit j: position j of the tile ends a run
+    auto load_tile = [&](int t, int (&m_sid)[NREG], int (&m_row)[NREG], unsigned& m_mask) {
+      m_mask = 0u;
+#pragma unroll
+      for (int r = 0; r < NREG; ++r) {
+        const int p = g0 + t * T + r * LPR + lane_g;
+        const bool in = p < g1;
+        m_sid[r] = in ? __ldg(sid + p) : -1;
+        const int nxt = (in && p + 1 < n) ? __ldg(sid + p + 1) : -2;
+        m_row[r] = HAS_PERM ? (in ? __ldg(perm + p) : 0) : p;
+        const unsigned bal = __ballot_sync(gmask, in && (m_sid[r] != nxt));
+        m_mask |= ((bal >> lane_base) & ((LPR == 32) ? 0xffffffffu : ((1u << LPR) - 1u))) << (r * LPR);
       }
-      if (!(f & kOpenRight)) {
-        if (!cur_open_left) {
-          store_out<Op, VEC>(out, arg, cur_sid, C, ch, lane_on, cur, cur_cnt, mean);
-        } else {
-          uint32_t* ga = ws.vec + rec * 2 * CPS + lane_g * VEC;
-          store_acc<VEC>(ga, ga + CPS, cur);
-          head_flag = kValid | kOpenLeft;
-          if (lane_g == 0) ws.meta[rec] = make_int4(cur_sid, cur_cnt, int(head_flag), 0);
+    };
+    // Register of a tile array that holds positions j0 .. j0 + B - 1 (B divides LPR).
+    auto tile_reg = [&](const int (&m)[NREG], int j0) {
+      int v = m[0];
+#pragma unroll
+      for (int r = 1; r < NREG; ++r)
+        if (j0 / LPR == r) v = m[r];
+      return v;
+    };
+    int cur_t = 0;
+    load_tile(0, cur_sid_r, cur_row_r, cur_mask);
+    load_tile(1, nxt_sid_r, nxt_row_r, nxt_mask);
+
+    // Copies batch bb (rows bb*B .. bb*B+B-1 of this group's range) into ring stage `stage`.
+    auto issue = [&](int bb, int stage) {
+      if constexpr (BULK) {
+        // Lanes j0 .. j0 + nv - 1 of the tile hold the rows of this batch: each
+        // issues the copy of its own row; all copies report to the stage's mbarrier.
+        if (bb < nb) {
+          const int q0 = bb * B;
+          const int j0 = q0 & (T - 1);
+          const int nv = min(B, L - q0);
+          const int k = lane_g - (j0 & (LPR - 1));
+          __syncwarp(gmask);  // every lane has finished reading the stage being refilled
+          if (k >= 0 && k < nv) {
+            int row = g0 + q0 + k;
+            if constexpr (HAS_PERM) row = (q0 / T == cur_t) ? tile_reg(cur_row_r, j0) : tile_reg(nxt_row_r, j0);
+            const unsigned bar = bar0 + stage * 8;
+            if (k == 0) mbar_arrive_expect_tx(bar, unsigned(nv * row_bytes));
+            bulk_copy_g2s(ring_addr + unsigned(stage * B + k) * kRowBytes, slab_src + int64_t(row) * C,
+                          unsigned(row_bytes), bar);
+          }
         }
-        have = false;
+      } else {
+        if (bb < nb) {
+          const int q0 = bb * B;
+          const int j0 = q0 & (T - 1);
+          const unsigned dst = ring_addr + unsigned(stage * B) * kStageSlotBytes;
+          int rows_reg = 0;
+          if constexpr (HAS_PERM) rows_reg = (q0 / T == cur_t) ? tile_reg(cur_row_r, j0) : tile_reg(nxt_row_r, j0);
+          if (q0 + B <= L) {
+#pragma unroll
+            for (int k = 0; k < B; ++k) {
+              int row = g0 + q0 + k;
+              if constexpr (HAS_PERM) row = __shfl_sync(gmask, rows_reg, (j0 & (LPR - 1)) + k, LPR);
+              cp_async_16(dst + k * kStageSlotBytes, lane_src + int64_t(row) * C);
+            }
+          } else {
+#pragma unroll
+            for (int k = 0; k < B; ++k) {
+              if (q0 + k < L) {
+                int row = g0 + q0 + k;
+                if constexpr (HAS_PERM) row = __shfl_sync(gmask, rows_reg, (j0 & (LPR - 1)) + k, LPR);
+                cp_async_16(dst + k * kStageSlotBytes, lane_src + int64_t(row) * C);
+              }
+            }
+          }
+        }
+        cp_async_commit();
+      }
+    };
+
+    const bool first_open_left = (g0 > 0) && (__ldg(sid + g0 - 1) == __ldg(sid + g0));
+    bool is_first = true;
+    int run_start = 0;  // first row (index in this group's range) of the current run
+    State acc;
+    Op::template init<VEC>(acc);
+
+    auto close_run = [&](int sid_now, int cnt, bool open_right) {
+      const bool open_left = is_first && first_open_left;
+      if (!open_left && !open_right) {
+        store_out<Op, VEC>(out, arg, sid_now, C, ch, lane_on, acc, cnt, mean);
+      } else if (!open_right) {
+        head_acc = acc; head_sid = sid_now; head_cnt = cnt; head_flag = kValid | kOpenLeft;
+      } else {
+        tail_acc = acc; tail_sid = sid_now; tail_cnt = cnt;
+        tail_flag = kValid | kOpenRight | (open_left ? kOpenLeft : 0u);
+      }
+    };
+
+#pragma unroll
+    for (int bb = 0; bb < S - 1; ++bb) issue(bb, bb);
+    int stage_c = 0;        // ring stage of the batch being reduced
+    int stage_p = S - 1;    // ring stage the next copy batch goes to
+
+#pragma unroll 1
+    for (int b = 0; b < nb; ++b) {
+      const int q0 = b * B;
+      const int j0 = q0 & (T - 1);
+      if (b > 0 && j0 == 0) {  // the reduce front enters the next tile
+        ++cur_t;
+#pragma unroll
+        for (int r = 0; r < NREG; ++r) { cur_sid_r[r] = nxt_sid_r[r]; cur_row_r[r] = nxt_row_r[r]; }
+        cur_mask = nxt_mask;
+        load_tile(cur_t + 1, nxt_sid_r, nxt_row_r, nxt_mask);
+      }
+      issue(b + S - 1, stage_p);
+      stage_p = (stage_p + 1 == S) ? 0 : stage_p + 1;
+      if constexpr (BULK) {
+        mbar_wait_bounded(bar0 + stage_c * 8, unsigned(b / S) & 1u);  // batch b has landed
+      } else {
+        cp_async_wait<S - 1>();  // batch b has landed (groups complete in order)
+      }
+
+      const float4* src = ring + stage_c * B * kSlotFloat4;
+      stage_c = (stage_c + 1 == S) ? 0 : stage_c + 1;
+      const unsigned ends = (cur_mask >> j0) & ((1u << B) - 1u);
+      int rows_reg = 0;
+      if constexpr (Op::kIsMax && HAS_PERM) rows_reg = tile_reg(cur_row_r, j0);
+
+      if (ends == 0u && q0 + B <= L) {
+        // eight rows of one run: no bookkeeping
+#pragma unroll
+        for (int k = 0; k < B; ++k) {
+          const float4 t4 = src[k * kSlotFloat4];
+          const float v[VEC] = {t4.x, t4.y, t4.z, t4.w};
+          int row = g0 + q0 + k;
+          if constexpr (Op::kIsMax && HAS_PERM) row = __shfl_sync(gmask, rows_reg, (j0 & (LPR - 1)) + k, LPR);
+          Op::template add<VEC>(acc, v, row);
+        }
+      } else {
+        // a batch with run ends (or the ragged last batch): same loads, then a
+        // per-row check; the rows are already in registers when a run is closed
+        const int nv = min(B, L - q0);
+        const int sids_reg = tile_reg(cur_sid_r, j0);
+        float4 t4[B];
+#pragma unroll
+        for (int k = 0; k < B; ++k) t4[k] = src[(k < nv ? k : 0) * kSlotFloat4];
+#pragma unroll
+        for (int k = 0; k < B; ++k) {
+          if (k < nv) {
+            const float v[VEC] = {t4[k].x, t4[k].y, t4[k].z, t4[k].w};
+            int row = g0 + q0 + k;
+            if constexpr (Op::kIsMax && HAS_PERM) row = __shfl_sync(gmask, rows_reg, (j0 & (LPR - 1)) + k, LPR);
+            Op::template add<VEC>(acc, v, row);
+            if ((ends >> k) & 1u) {  // last row of its segment
+              const int sid_now = __shfl_sync(gmask, sids_reg, (j0 & (LPR - 1)) + k, LPR);
+              close_run(sid_now, q0 + k - run_start + 1, false);
+              is_first = false;
+              run_start = q0 + k + 1;
+              Op::template init<VEC>(acc);
+            }
+          }
+        }
       }
     }
-    if (head_flag == 0u && lane_g == 0) ws.meta[rec] = make_int4(0, 0, 0, 0);
-    if (have) {
-      uint32_t* ga = ws.vec + (rec + 1) * 2 * CPS + lane_g * VEC;
-      store_acc<VEC>(ga, ga + CPS, cur);
-      const unsigned f = kValid | kOpenRight | (cur_open_left ? kOpenLeft : 0u);
-      if (lane_g == 0) ws.meta[rec + 1] = make_int4(cur_sid, cur_cnt, int(f), 0);
-    } else if (lane_g == 0) {
-      ws.meta[rec + 1] = make_int4(0, 0, 0, 0);
+    if (run_start < L) {  // the last run continues past this range
+      const int jl = (L - 1) & (T - 1);
+      const int sid_now = __shfl_sync(gmask, tile_reg(cur_sid_r, jl & ~(B - 1)), jl & (LPR - 1), LPR);
+      close_run(sid_now, L - run_start, true);
     }
   }
+  if constexpr (!BULK) cp_async_wait<0>();
+  __syncthreads();  // every copy has been waited for and every lane is done with the ring
+
+  if (head_flag) {
+    uint32_t* pa = s_vec + (2 * group) * 2 * CPS + lane_g * VEC;
+    store_state<Op, VEC>(pa, pa + CPS, head_acc);
+    if (lane_g == 0) { s_sid[2 * group] = head_sid; s_cnt[2 * group] = head_cnt; s_flag[2 * group] = head_flag; }
+  }
+  if (tail_flag) {
+    uint32_t* pa = s_vec + (2 * group + 1) * 2 * CPS + lane_g * VEC;
+    store_state<Op, VEC>(pa, pa + CPS, tail_acc);
+    if (lane_g == 0) { s_sid[2 * group + 1] = tail_sid; s_cnt[2 * group + 1] = tail_cnt; s_flag[2 * group + 1] = tail_flag; }
+  }
+  __syncthreads();
+  stitch_cta<Op, VEC, LPR>(s_vec, s_sid, s_cnt, s_flag, out, arg, ws, C, ch, lane_on, lane_g,
+                           group, mean);
 }
 
 // ---- fix-up kernel --------------------------------------------------------------
@@ -389,6 +790,7 @@ template <class Op, int VEC, int LPR>
 __global__ void __launch_bounds__(kCtaThreads)
 segment_fixup_kernel(Workspace ws, float* __restrict__ out, int32_t* __restrict__ arg,
                      int num_ctas, int C, bool mean) {
+  using State = typename Op::template State<VEC>;
   constexpr int GPC = kCtaThreads / LPR;
   constexpr int CPS = LPR * VEC;
 
@@ -434,27 +836,27 @@ segment_fixup_kernel(Workspace ws, float* __restrict__ out, int32_t* __restrict_
   const int per = (K + GPC - 1) / GPC;
   const int i0 = min(group * per, K);
   const int i1 = min(i0 + per, K);
-  Acc<VEC> acc;
+  State acc;
   Op::template init<VEC>(acc);
   int cnt = 0;
   for (int i = i0; i < i1; ++i) {
     const int64_t rec = (rec_base + b + i) * 2 + ((i == K - 1) ? 0 : 1);
-    Acc<VEC> x;
+    State x;
     const uint32_t* ga = ws.vec + rec * 2 * CPS + lane_g * VEC;
-    load_acc<VEC>(ga, ga + CPS, x);
+    load_state<Op, VEC>(ga, ga + CPS, x);
     if (i == i0) acc = x; else Op::template merge<VEC>(acc, x);
     cnt += ws.meta[rec].y;
   }
   uint32_t* pa = s_vec + group * 2 * CPS + lane_g * VEC;
-  store_acc<VEC>(pa, pa + CPS, acc);
+  store_state<Op, VEC>(pa, pa + CPS, acc);
   if (lane_g == 0) s_cnt[group] = cnt;
   __syncthreads();
   if (group == 0) {
     const int used = (K + per - 1) / per;  // groups that held at least one piece
     for (int g = 1; g < used; ++g) {
-      Acc<VEC> x;
+      State x;
       const uint32_t* qa = s_vec + g * 2 * CPS + lane_g * VEC;
-      load_acc<VEC>(qa, qa + CPS, x);
+      load_state<Op, VEC>(qa, qa + CPS, x);
       Op::template merge<VEC>(acc, x);
       cnt += s_cnt[g];
     }
@@ -493,14 +895,22 @@ __global__ void expand_offsets_kernel(const int32_t* __restrict__ offsets, int32
 
 // ---- host side ----------------------------------------------------------------
 
-struct Geometry {
-  int vec, lpr, cps, num_slabs, gpc, rows_per_cta, rows_per_group, num_ctas;
+struct Layout {
+  int vec, lpr, cps, num_slabs, gpc;
+  int staged;  // 0: register kernel, 1: cp.async ring, 2: bulk-copy (TMA) ring; 128-bit lanes, 16 or 32 lanes per row
 };
+
+int sm_count() {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess)
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms > 0 ? sms : 148;
+}
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-Geometry make_geometry(int64_t n, int C, bool allow_vec4) {
-  Geometry g;
+Layout make_layout(int C, bool allow_vec4) {
+  Layout g;
   g.vec = (allow_vec4 && C % 4 == 0) ? 4 : 1;
   const int lanes = C / g.vec;
   int lpr = 1;
@@ -510,145 +920,217 @@ Geometry make_geometry(int64_t n, int C, bool allow_vec4) {
   g.cps = g.lpr * g.vec;
   g.num_slabs = (C + g.cps - 1) / g.cps;
   g.gpc = kCtaThreads / g.lpr;
-  int rows = tuning().rows_per_cta;
-  rows = int(ceil_div(rows, g.gpc)) * g.gpc;
-  g.rows_per_cta = rows;
-  g.rows_per_group = rows / g.gpc;
-  g.num_ctas = int(ceil_div(n, rows));
+  g.staged = (g.vec == 4 && g.lpr >= 16) ? tuning().staged : 0;
   return g;
 }
 
+// rows_per_cta == 0 (default): the rows are divided evenly over one wave of
+// CTAs, `ctas_per_sm` per SM (what the kernel's occupancy allows), so that no
+// SM is left with a partial second wave; at least 16 rows per group.
+Split make_split(int64_t n, const Layout& g, int ctas_per_sm) {
+  Split s;
+  s.balance = nullptr;
+  s.balance_k = 0;
+  int64_t rows = tuning().rows_per_cta;
+  if (rows <= 0) {
+    const int64_t resident = int64_t(sm_count()) * ctas_per_sm;
+    rows = ceil_div(n > 0 ? n : 1, resident);
+    if (rows < 16 * g.gpc) rows = 16 * g.gpc;
+  }
+  rows = ceil_div(rows, g.gpc) * g.gpc;
+  s.rows_per_cta = int(rows);
+  s.rows_per_group = int(rows / g.gpc);
+  s.num_ctas = int(ceil_div(n, rows));
+  return s;
+}
+
+constexpr int kMaxCtasPerSm = 8;  // 256-thread CTAs: the hardware limit of 2048 threads per SM
+
+size_t records_vec_bytes(const Layout& g, int num_ctas) {
+  return align_up(size_t(g.num_slabs) * num_ctas * 2 * 2 * g.cps * sizeof(uint32_t), 256);
+}
+size_t records_meta_bytes(const Layout& g, int num_ctas) {
+  return size_t(g.num_slabs) * num_ctas * 2 * sizeof(int4);
+}
+
+// Upper bound over both lane layouts (a caller may pass unaligned pointers) and
+// over every occupancy the launch may find.
 size_t reduce_workspace_bytes(int64_t n, int C) {
-  // Sized for the scalar layout too (a caller may pass unaligned pointers).
   size_t best = 0;
   for (int v = 0; v < 2; ++v) {
-    Geometry g = make_geometry(n, C, v == 1);
-    size_t recs = size_t(g.num_slabs) * g.num_ctas * 2;
-    size_t bytes = align_up(recs * 2 * g.cps * sizeof(uint32_t), 256) + recs * sizeof(int4);
+    const Layout g = make_layout(C, v == 1);
+    const Split s = make_split(n, g, kMaxCtasPerSm);
+    const size_t bytes = records_vec_bytes(g, s.num_ctas) + records_meta_bytes(g, s.num_ctas);
     if (bytes > best) best = bytes;
   }
-  return best + 256;
+  return best + 512;
+}
+
+struct Call {
+  const float* feats;
+  const int32_t* sid;
+  const int32_t* perm;
+  float* out;
+  int32_t* arg;
+  void* workspace;
+  size_t workspace_bytes;
+  int n, C;
+  bool mean;
+  cudaStream_t stream;
+  const int32_t* balance;
+  int balance_k;
+};
+
+// Resident CTAs per SM of one kernel instantiation (asked once per process).
+template <class Kernel>
+int resident_ctas(Kernel kernel, size_t dyn_smem) {
+  int blocks = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, kCtaThreads, dyn_smem) != cudaSuccess ||
+      blocks < 1) {
+    (void)cudaGetLastError();
+    blocks = 1;
+  }
+  return blocks < kMaxCtasPerSm ? blocks : kMaxCtasPerSm;
+}
+
+template <class Op, int VEC, int LPR, class Kernel>
+int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g, const Call& c) {
+  Split s = make_split(c.n, g, ctas_per_sm);
+  if (c.balance && c.balance_k > 0 && tuning().balanced) {
+    s.balance = c.balance;
+    s.balance_k = c.balance_k;
+  }
+  const size_t vec_bytes = records_vec_bytes(g, s.num_ctas);
+  const size_t need = vec_bytes + records_meta_bytes(g, s.num_ctas);
+  const uintptr_t base = align_up(reinterpret_cast<uintptr_t>(c.workspace), 256);
+  const size_t pad = base - reinterpret_cast<uintptr_t>(c.workspace);
+  if (!c.workspace || c.workspace_bytes < need + pad)
+    return fail(TEXB_ERR_WORKSPACE, "reduce workspace: need %zu bytes, got %zu", need + pad,
+                c.workspace_bytes);
+  Workspace ws;
+  ws.vec = reinterpret_cast<uint32_t*>(base);
+  ws.meta = reinterpret_cast<int4*>(base + vec_bytes);
+
+  const dim3 grid(s.num_ctas, g.num_slabs);
+  kernel<<<grid, kCtaThreads, dyn_smem, c.stream>>>(c.feats, c.sid, c.perm, c.out, c.arg, ws, c.n, c.C,
+                                                    s, c.mean);
+  int st = check_launch("segment reduce kernel");
+  if (st != TEXB_OK || s.num_ctas <= 1) return st;
+
+  if (tuning().fixup_pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kCtaThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = c.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, segment_fixup_kernel<Op, VEC, LPR>, ws, c.out, c.arg,
+                                       s.num_ctas, c.C, c.mean);
+    if (e != cudaSuccess)
+      return fail(TEXB_ERR_CUDA, "segment_fixup_kernel launch: %s", cudaGetErrorString(e));
+  } else {
+    segment_fixup_kernel<Op, VEC, LPR><<<grid, kCtaThreads, 0, c.stream>>>(ws, c.out, c.arg, s.num_ctas,
+                                                                           c.C, c.mean);
+  }
+  return check_launch("segment_fixup_kernel");
+}
+
+template <class Op, int VEC, int LPR, bool HAS_PERM>
+int launch_reduce(const Layout& g, const Call& c) {
+  if constexpr (VEC == 4 && (LPR == 16 || LPR == 32)) {
+    if (g.staged) {
+      // The shared-memory attribute is per device: set it on every call (a host-side table write).
+      auto staged_launch = [&](auto kernel, int* resident) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kStageRingBytes);
+        if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        if (*resident == 0) *resident = resident_ctas(kernel, kStageRingBytes);
+        return launch_pair<Op, VEC, LPR>(kernel, kStageRingBytes, *resident, g, c);
+      };
+      if (g.staged == 2) {
+        static int resident = 0;
+        return staged_launch(segment_reduce_staged_kernel<Op, LPR, HAS_PERM, true>, &resident);
+      }
+      static int resident = 0;
+      return staged_launch(segment_reduce_staged_kernel<Op, LPR, HAS_PERM, false>, &resident);
+    }
+  }
+  auto kernel = segment_reduce_kernel<Op, VEC, LPR, HAS_PERM>;
+  static const int resident = resident_ctas(kernel, 0);
+  return launch_pair<Op, VEC, LPR>(kernel, 0, resident, g, c);
 }
 
 template <class Op, int VEC, int LPR>
-int launch_reduce(const Geometry& g, const float* feats, const int32_t* sid, const int32_t* perm,
-                  float* out, int32_t* arg, Workspace ws, int n, int C, bool mean,
-                  cudaStream_t stream) {
-  dim3 grid(g.num_ctas, g.num_slabs);
-  if (perm) {
-    segment_reduce_kernel<Op, VEC, LPR, true><<<grid, kCtaThreads, 0, stream>>>(
-        feats, sid, perm, out, arg, ws, n, C, g.rows_per_cta, g.rows_per_group, mean);
-  } else {
-    segment_reduce_kernel<Op, VEC, LPR, false><<<grid, kCtaThreads, 0, stream>>>(
-        feats, sid, perm, out, arg, ws, n, C, g.rows_per_cta, g.rows_per_group, mean);
-  }
-  int st = check_launch("segment_reduce_kernel");
-  if (st != TEXB_OK) return st;
-  if (g.num_ctas > 1) {
-    if (tuning().fixup_pdl) {
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = grid;
-      cfg.blockDim = dim3(kCtaThreads);
-      cfg.dynamicSmemBytes = 0;
-      cfg.stream = stream;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-      attr[0].val.programmaticStreamSerializationAllowed = 1;
-      cfg.attrs = attr;
-      cfg.numAttrs = 1;
-      cudaError_t e = cudaLaunchKernelEx(&cfg, segment_fixup_kernel<Op, VEC, LPR>, ws, out, arg,
-                                         g.num_ctas, C, mean);
-      if (e != cudaSuccess)
-        return fail(TEXB_ERR_CUDA, "segment_fixup_kernel launch: %s", cudaGetErrorString(e));
-    } else {
-      segment_fixup_kernel<Op, VEC, LPR><<<grid, kCtaThreads, 0, stream>>>(ws, out, arg,
-                                                                           g.num_ctas, C, mean);
-    }
-    st = check_launch("segment_fixup_kernel");
-  }
-  return st;
+int dispatch_perm(const Layout& g, const Call& c) {
+  if (c.perm) return launch_reduce<Op, VEC, LPR, true>(g, c);
+  return launch_reduce<Op, VEC, LPR, false>(g, c);
 }
 
-template <class Op, int VEC>
-int dispatch_lpr(const Geometry& g, const float* feats, const int32_t* sid, const int32_t* perm,
-                 float* out, int32_t* arg, Workspace ws, int n, int C, bool mean,
-                 cudaStream_t stream) {
-  switch (g.lpr) {
-    case 1: return launch_reduce<Op, VEC, 1>(g, feats, sid, perm, out, arg, ws, n, C, mean, stream);
-    case 4: return launch_reduce<Op, VEC, 4>(g, feats, sid, perm, out, arg, ws, n, C, mean, stream);
-    case 32: return launch_reduce<Op, VEC, 32>(g, feats, sid, perm, out, arg, ws, n, C, mean, stream);
-    default: break;
-  }
-  if constexpr (VEC == 4) {
+template <class Op>
+int dispatch_layout(const Layout& g, const Call& c) {
+  if (g.vec == 4) {
     switch (g.lpr) {
-      case 2: return launch_reduce<Op, 4, 2>(g, feats, sid, perm, out, arg, ws, n, C, mean, stream);
-      case 8: return launch_reduce<Op, 4, 8>(g, feats, sid, perm, out, arg, ws, n, C, mean, stream);
-      case 16: return launch_reduce<Op, 4, 16>(g, feats, sid, perm, out, arg, ws, n, C, mean, stream);
+      case 1: return dispatch_perm<Op, 4, 1>(g, c);
+      case 2: return dispatch_perm<Op, 4, 2>(g, c);
+      case 4: return dispatch_perm<Op, 4, 4>(g, c);
+      case 8: return dispatch_perm<Op, 4, 8>(g, c);
+      case 16: return dispatch_perm<Op, 4, 16>(g, c);
+      case 32: return dispatch_perm<Op, 4, 32>(g, c);
+      default: break;
+    }
+  } else {
+    switch (g.lpr) {
+      case 1: return dispatch_perm<Op, 1, 1>(g, c);
+      case 4: return dispatch_perm<Op, 1, 4>(g, c);
+      case 32: return dispatch_perm<Op, 1, 32>(g, c);
       default: break;
     }
   }
   return fail(TEXB_ERR_UNSUPPORTED, "no kernel for %d lanes per row", g.lpr);
 }
 
-template <class Op>
-int dispatch_vec(const Geometry& g, const float* feats, const int32_t* sid, const int32_t* perm,
-                 float* out, int32_t* arg, Workspace ws, int n, int C, bool mean,
-                 cudaStream_t stream) {
-  if (g.vec == 4) return dispatch_lpr<Op, 4>(g, feats, sid, perm, out, arg, ws, n, C, mean, stream);
-  return dispatch_lpr<Op, 1>(g, feats, sid, perm, out, arg, ws, n, C, mean, stream);
-}
-
 }  // namespace
 
 int segment_reduce_impl(int op, const float* feats, const int32_t* sid, const int32_t* perm,
-                        const int32_t* offsets, int has_empty, int64_t n, int C, int64_t m,
-                        float* out, int32_t* arg, void* workspace, size_t workspace_bytes,
-                        cudaStream_t stream) {
+                        const int32_t* offsets, int has_empty, const int32_t* balance,
+                        int balance_len, int64_t n, int C, int64_t m, float* out, int32_t* arg,
+                        void* workspace, size_t workspace_bytes, cudaStream_t stream) {
   if (op != TEXB_OP_SUM && op != TEXB_OP_MEAN && op != TEXB_OP_MAX)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "unknown reduce op %d", op);
   if (n < 0 || m < 0 || C < 1)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "bad sizes n=%lld channel=%d num_segments=%lld",
                 (long long)n, C, (long long)m);
-  if (n >= (int64_t(1) << 31) || m >= (int64_t(1) << 31))
-    return fail(TEXB_ERR_UNSUPPORTED, "n and num_segments must be below 2^31");
+  if (n >= (int64_t(1) << 31) - 65536 || m >= (int64_t(1) << 31) - 65536)
+    return fail(TEXB_ERR_UNSUPPORTED, "n and num_segments must be below 2^31 - 65536");
   if (m > 0 && !out) return fail(TEXB_ERR_INVALID_ARGUMENT, "out is NULL");
   if (m > 0 && op == TEXB_OP_MAX && !arg) return fail(TEXB_ERR_INVALID_ARGUMENT, "arg is NULL");
   if (n > 0 && (!feats || !sid)) return fail(TEXB_ERR_INVALID_ARGUMENT, "feats or sid is NULL");
-  if (has_empty && !offsets)
-    return fail(TEXB_ERR_INVALID_ARGUMENT, "offsets is required when has_empty is set");
+  if ((has_empty || n == 0) && m > 0 && !offsets)
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "offsets is required when has_empty is set or n == 0");
   if (m == 0) return TEXB_OK;
 
   if (has_empty || n == 0) {
-    int64_t total = m * C;
-    int blocks = int(ceil_div(total, 256) < 148 * 16 ? ceil_div(total, 256) : 148 * 16);
-    if (n == 0 && !offsets) {
-      return fail(TEXB_ERR_INVALID_ARGUMENT, "offsets is required when n == 0");
-    }
+    const int64_t total = m * C;
+    const int64_t want = ceil_div(total, 256);
+    const int blocks = int(want < 148 * 16 ? want : 148 * 16);
     fill_empty_kernel<<<blocks, 256, 0, stream>>>(offsets, out, arg, m, C, op == TEXB_OP_MAX);
     int st = check_launch("fill_empty_kernel");
     if (st != TEXB_OK || n == 0) return st;
   }
 
   const bool vec_ok = aligned16(feats) && aligned16(out) && (op != TEXB_OP_MAX || aligned16(arg));
-  Geometry g = make_geometry(n, C, vec_ok);
-  const size_t recs = size_t(g.num_slabs) * g.num_ctas * 2;
-  const size_t vec_bytes = align_up(recs * 2 * g.cps * sizeof(uint32_t), 256);
-  const size_t need = vec_bytes + recs * sizeof(int4);
-  uintptr_t base = align_up(reinterpret_cast<uintptr_t>(workspace), 256);
-  size_t pad = base - reinterpret_cast<uintptr_t>(workspace);
-  if (!workspace || workspace_bytes < need + pad)
-    return fail(TEXB_ERR_WORKSPACE, "reduce workspace: need %zu bytes, got %zu", need + pad,
-                workspace_bytes);
-  Workspace ws;
-  ws.vec = reinterpret_cast<uint32_t*>(base);
-  ws.meta = reinterpret_cast<int4*>(base + vec_bytes);
-
-  const bool mean = (op == TEXB_OP_MEAN);
-  if (op == TEXB_OP_MAX)
-    return dispatch_vec<OpMax>(g, feats, sid, perm, out, arg, ws, int(n), C, false, stream);
-  if (tuning().compensated)
-    return dispatch_vec<OpSumComp>(g, feats, sid, perm, out, arg, ws, int(n), C, mean, stream);
-  return dispatch_vec<OpSumPlain>(g, feats, sid, perm, out, arg, ws, int(n), C, mean, stream);
+  const Layout g = make_layout(C, vec_ok);
+  if (balance && balance_len < 2)
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "balance table needs at least 2 entries");
+  Call c = {feats, sid, perm, out, arg, workspace, workspace_bytes, int(n), C, op == TEXB_OP_MEAN, stream,
+            balance, balance ? balance_len - 1 : 0};
+  if (op == TEXB_OP_MAX) return dispatch_layout<OpMax>(g, c);
+  if (tuning().compensated) return dispatch_layout<OpSumComp>(g, c);
+  return dispatch_layout<OpSumPlain>(g, c);
 }
 
 int expand_offsets_impl(const int32_t* offsets, int32_t* sid, int64_t n, int64_t m,
@@ -659,5 +1141,13 @@ int expand_offsets_impl(const int32_t* offsets, int32_t* sid, int64_t n, int64_t
 }
 
 size_t reduce_workspace_bytes_impl(int64_t n, int C) { return reduce_workspace_bytes(n, C); }
+
+int device_status_impl(int* wait_timeouts) {
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_wait_timeouts, sizeof(int));
+  if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "cudaMemcpyFromSymbol: %s", cudaGetErrorString(e));
+  if (wait_timeouts) *wait_timeouts = v;
+  return TEXB_OK;
+}
 
 }  // namespace texb

@@ -49,7 +49,8 @@ class ScatterData:
     ``unq_cnts`` ([num_unq, 1], caller dtype), ``preSum`` (int32 [num_unq + 1]),
     ``max_cnt`` (int) and ``num_unq`` (int).  Added: ``sid`` (segment id at each
     segment-sorted position), ``perm`` (row of ``feats`` at that position, or
-    ``None`` when the ids arrive sorted), ``is_sorted`` and ``has_empty``.
+    ``None`` when the ids arrive sorted), ``balance`` (cost-balanced cut points of
+    the sorted rows), ``is_sorted`` and ``has_empty``.
 
     ``num_unq`` is ``len(unq_cnts)``; the reference derives it from the last id
     with a device-to-host copy (scatter_op.py:125-126).  Construction
@@ -99,6 +100,9 @@ class ScatterData:
                                               self.sid.data_ptr(), perm_ptr, self.preSum.data_ptr(),
                                               plan_stats.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
                           "texb_plan_build")
+            self.balance = torch.empty(_native.BALANCE_PIECES + 1, dtype=torch.int32, device=dev)
+            _native.check(lib.texb_plan_balance(self.sid.data_ptr(), n, self.balance.data_ptr(),
+                                                self.balance.numel(), _stream()), "texb_plan_balance")
             if ids.dtype == torch.int32:
                 self.unq_inv = ids
             elif self.is_sorted:
@@ -131,7 +135,8 @@ def _reduce(op: int, feats: torch.Tensor, data: ScatterData, want_arg: bool):
         _native.check(
             lib.texb_segment_reduce(op, feats.data_ptr(), data.sid.data_ptr(),
                                     None if data.perm is None else data.perm.data_ptr(),
-                                    data.preSum.data_ptr(), int(data.has_empty or n == 0), n, c, m,
+                                    data.preSum.data_ptr(), int(data.has_empty or n == 0),
+                                    data.balance.data_ptr(), data.balance.numel(), n, c, m,
                                     out.data_ptr(), None if arg is None else arg.data_ptr(),
                                     ws.data_ptr(), ws.numel(), _stream()),
             "texb_segment_reduce")
