@@ -1,0 +1,442 @@
+"""Benchmark of the segmented scatter-reduction forward path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one forward pass of the hot path over one batch: scatter_sum,
+scatter_mean and scatter_max of feat[N, C] with a prebuilt segment plan (the
+reference's own test also builds ScatterData outside its timed loop,
+test/test_scatter.py:24, 38-44).  The workload is the skewed configuration the
+headline metric is quoted on: N = 1 000 000 points, C = 128 fp32 channels,
+M = 50 000 segments with Zipf(1.2) sizes plus one 100 000-point segment, ids
+randomly permuted.  With N > 1 (launched by torchrun, one rank per GPU) every
+rank reduces its own frame of that shape, nothing is exchanged (frames are
+independent), and the value is the sum over ranks: weak scaling.
+
+The line printed by rank 0 carries the device-resident throughput (`value`),
+the same metric through the public operators with host buffers (`e2e`), the
+roofline of the reduce kernel, the host-CPU baseline, sampled clocks, and the
+multi-frame batch (16 frames x 200 000 points) in Mpoints/s.
+
+`--impl reference` times the CPU statement of the operators
+(torch.Tensor.scatter_reduce_ with all host threads; TorchEx ships no CPU
+kernel) on the same workload, on rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+N_POINTS, CHANNELS, N_SEGMENTS = 1_000_000, 128, 50_000
+SEED = 2024
+HBM_NOMINAL_GBS = 8000.0          # the target's denominator
+HBM_FALLBACK_GBS = 6650.0         # earlier copy measurement on this pool, used only without MEASURED_PEAKS.json
+# DRAM bytes of one reduce launch on this workload (dram__bytes_read.sum +
+# dram__bytes_write.sum of one ncu capture of this script; summary in
+# profiles/reduce_kernel_skewed_1m_c128.txt).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def algorithmic_bytes(n, c, m):
+    """Bytes one launch must move: features, one int32 per point, one offset per
+    segment, the output rows (max also writes the int32 argmax rows)."""
+    b_sum = 4 * n * c + 4 * n + 4 * (m + 1) + 4 * m * c
+    return {"sum": b_sum, "mean": b_sum, "max": b_sum + 4 * m * c}
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return HBM_FALLBACK_GBS, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Polls SM clock and clock-event reasons through NVML while the timed
+    region runs (read-only queries)."""
+
+    def __init__(self, index, period_s=0.004):
+        super().__init__(daemon=True)
+        self.period = period_s
+        self.samples, self.reasons = [], set()
+        self.sm_max = None
+        self._halt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        names = {"hw_slowdown": "nvmlClocksEventReasonHwSlowdown",
+                 "hw_thermal_slowdown": "nvmlClocksEventReasonHwThermalSlowdown",
+                 "sw_thermal_slowdown": "nvmlClocksEventReasonSwThermalSlowdown",
+                 "sw_power_cap": "nvmlClocksEventReasonSwPowerCap"}
+        bits = {k: getattr(self.nv, v, None) for k, v in names.items()}
+        while not self._halt.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                mask = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for k, b in bits.items():
+                    if b is not None and mask & b:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def stop(self):
+        self._halt.set()
+        if self.ok:
+            self.join(timeout=1.0)
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+# ---------------------------------------------------------------------------- ours
+
+def run_ours(args):
+    import torch.distributed as dist
+    from torchex_b200 import ScatterData, _native, scatter_max, scatter_mean, scatter_sum, workloads as W
+
+    rank, local_rank, world = dist_env()
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _native.lib()
+    n, c, m = N_POINTS, CHANNELS, N_SEGMENTS
+    bytes_op = algorithmic_bytes(n, c, m)
+    bytes_step = sum(bytes_op.values())
+
+    # ---- inputs resident in HBM: this rank's frame
+    ids, cnt = W.skewed_ids(n, m, seed=SEED + rank)
+    feat = W.features(n, c, SEED + rank, device=dev)
+    data = ScatterData(ids.to(dev), cnt.to(dev))
+    outs = {k: torch.empty((m, c), device=dev) for k in ("sum", "mean", "max")}
+    arg = torch.empty((m, c), dtype=torch.int32, device=dev)
+    ws = torch.empty(lib.texb_reduce_workspace_bytes(n, c), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    perm_ptr = None if data.perm is None else data.perm.data_ptr()
+    ops = {"sum": _native.OP_SUM, "mean": _native.OP_MEAN, "max": _native.OP_MAX}
+
+    def reduce(name):
+        st = lib.texb_segment_reduce(ops[name], feat.data_ptr(), data.sid.data_ptr(), perm_ptr,
+                                     data.preSum.data_ptr(), 0, data.balance.data_ptr(), data.balance.numel(),
+                                     n, c, m, outs[name].data_ptr(), arg.data_ptr(), ws.data_ptr(), ws.numel(),
+                                     stream)
+        if st != 0:
+            raise RuntimeError(_native.last_error())
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    for _ in range(max(args.warmup, 3)):
+        for name in ops:
+            reduce(name)
+    torch.cuda.synchronize()
+
+    # ---- timed region: K steps, device timed, per-step events around the sum launch pair
+    k = args.steps
+    ev_sum = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(k)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    t0.record()
+    for i in range(k):
+        ev_sum[i][0].record()
+        reduce("sum")
+        ev_sum[i][1].record()
+        reduce("mean")
+        reduce("max")
+    t1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    barrier()
+    elapsed_ms = t0.elapsed_time(t1)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / k
+    value = world * bytes_step / (ms_per_step * 1e-3) / 1e9
+    sum_ms = statistics.mean(a.elapsed_time(b) for a, b in ev_sum)
+    timeouts = _native.device_wait_timeouts()
+
+    # ---- per-op device time (same buffers, right after the timed region)
+    per_op = {}
+    for name in ops:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 50
+        a.record()
+        for _ in range(reps):
+            reduce(name)
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) / reps * 1e3
+        gbs = bytes_op[name] / us / 1e3
+        per_op[name] = {"us": round(us, 2), "GBps": round(gbs, 1), "Mpoints_per_s": round(n / us, 1),
+                        "frac_of_8000": round(gbs / HBM_NOMINAL_GBS, 4)}
+
+    peak, peak_kind = measured_peak_gbs()
+    achieved = bytes_op["sum"] / (sum_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "segment_reduce_staged_kernel<sum> + segment_fixup_kernel (one launch pair)",
+                "achieved": round(achieved, 1), "peak": peak, "peak_source": f"hbm_gbs of {peak_kind} copy",
+                "unit": "GB/s", "frac": round(achieved / peak, 4), "frac_of_nominal_8000": round(achieved / HBM_NOMINAL_GBS, 4),
+                "algorithmic_bytes_per_launch": bytes_op["sum"], "us_per_launch": round(sum_ms * 1e3, 2),
+                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH}
+
+    # ---- end to end through the public operators, host buffers in pinned memory
+    e2e = None
+    if not args.no_e2e:
+        h_feat = feat.cpu().pin_memory()
+        h_ids = ids.pin_memory()
+        h_cnt = cnt.pin_memory()
+        h_out = {kk: torch.empty((m, c), dtype=torch.float32).pin_memory() for kk in ("sum", "mean", "max")}
+        h_arg = torch.empty((m, c), dtype=torch.int32).pin_memory()
+        steps_e2e = max(2, min(k, args.e2e_steps))
+
+        def e2e_step():
+            d_feat = h_feat.to(dev, non_blocking=True)
+            d = ScatterData(h_ids.to(dev, non_blocking=True), h_cnt.to(dev, non_blocking=True))
+            h_out["sum"].copy_(scatter_sum(d_feat, d), non_blocking=True)
+            h_out["mean"].copy_(scatter_mean(d_feat, d), non_blocking=True)
+            mx, ag = scatter_max(d_feat, d)
+            h_out["max"].copy_(mx, non_blocking=True)
+            h_arg.copy_(ag, non_blocking=True)
+
+        e2e_step()
+        torch.cuda.synchronize()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps_e2e):
+            e2e_step()
+        b.record()
+        torch.cuda.synchronize()
+        e_ms = a.elapsed_time(b) / steps_e2e
+        if world > 1:
+            t = torch.tensor([e_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e_ms = float(t.item())
+        e2e = {"value": round(world * bytes_step / (e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
+               "ms_per_step": round(e_ms, 3), "steps": steps_e2e,
+               "h2d_bytes_per_step": h_feat.numel() * 4 + h_ids.numel() * 8 + h_cnt.numel() * 8,
+               "d2h_bytes_per_step": 3 * m * c * 4 + m * c * 4 + 32,
+               "includes": "H2D of feat, ids and counts from pinned memory, segment plan build, sum/mean/max "
+                           "through torchex_b200.scatter_*, D2H of the three results and argmax"}
+        del h_feat
+
+    # ---- multi-frame batch: 16 frames x 200 000 points, C = 128, frames sharded over the ranks
+    multi = None
+    if not args.no_multi_frame:
+        multi = multi_frame_bench(args, rank, world, dev, barrier)
+
+    # ---- host CPU baseline (rank 0, single-GPU run only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(feat.cpu(), ids, m, bytes_step, reps=3)
+
+    if rank == 0:
+        line = {
+            "metric": "scatter_fwd_GBps", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
+            "steps": k, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "skewed segments: N=1,000,000 points, C=128 fp32, M=50,000 segments "
+                                   "(Zipf 1.2 sizes + one 100,000-point segment), ids randomly permuted; "
+                                   "step = scatter_sum + scatter_mean + scatter_max forward with a prebuilt plan",
+                       "points_per_gpu": n, "channels": c, "segments": m, "frames": world,
+                       "sharding": "one frame per GPU, no collective", "l2": "inputs_exceed_l2 (512 MB of features per step op)",
+                       "seed": SEED},
+            "Mpoints_per_s": round(world * 3 * n / (ms_per_step * 1e-3) / 1e6, 1),
+            "pct_of_hbm_8000": round(100 * value / world / HBM_NOMINAL_GBS, 2),
+            "per_op": per_op,
+            "roofline": roofline,
+            "cpu_baseline": cpu,
+            "e2e": e2e,
+            "gpu_launches": 6 * k,
+            "clocks": clocks,
+            "multi_frame": multi,
+            "device_wait_timeouts": timeouts,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def multi_frame_bench(args, rank, world, dev, barrier):
+    """Strong scaling of the 16-frame batch: frames sharded over the ranks;
+    Mpoints/s with the outputs left sharded and with an NCCL all-gather."""
+    import torch.distributed as dist
+    from torchex_b200 import frames as F, workloads as W
+    frames, per_frame, c = 16, 200_000, CHANNELS
+    lo, hi = F.frame_blocks(frames, world)[rank]
+    mine = [W.voxel_frame(per_frame, SEED + 100 + f) for f in range(lo, hi)]
+    seg_local = torch.zeros(frames, dtype=torch.int64, device=dev)
+    for i, (_, cnt) in enumerate(mine):
+        seg_local[lo + i] = cnt.numel()
+    if world > 1:
+        dist.all_reduce(seg_local)
+    frame_segments = [int(v) for v in seg_local.cpu()]
+    layout = F.shard_layout(frame_segments, [per_frame] * frames, rank, world)
+    shard = F.FrameShard([i for i, _ in mine], [cn for _, cn in mine], layout, dev)
+    feats = W.features(layout.row_count, c, SEED + 200 + rank, device=dev)
+    res = {"frames": frames, "points": frames * per_frame, "channels": c, "segments": layout.seg_total}
+    for mode, replicated in (("sharded", False), ("replicated", True)):
+        def step():
+            shard.scatter("sum", feats, replicated)
+            shard.scatter("mean", feats, replicated)
+            shard.scatter("max", feats, replicated)
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        a.record()
+        for _ in range(reps):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / reps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        res[f"Mpoints_per_s_{mode}"] = round(3 * frames * per_frame / (ms * 1e-3) / 1e6, 1)
+        res[f"ms_per_step_{mode}"] = round(ms, 4)
+    res["note"] = ("step = sum + mean + max over all 16 frames through the operator API; sharded = outputs stay on the "
+                   "GPU that owns the frames, replicated = NCCL all-gather of every result to every GPU")
+    return res
+
+
+# ---------------------------------------------------------------------------- CPU
+
+def cpu_baseline(feat_cpu, ids, m, bytes_step, reps):
+    from oracle import scatter_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    index = ids[:, None].expand(-1, feat_cpu.shape[1])
+    O.cpu_forward_step(feat_cpu, index, m)
+    best = None
+    for _ in range(reps):
+        t = time.perf_counter()
+        O.cpu_forward_step(feat_cpu, index, m)
+        dt = time.perf_counter() - t
+        best = dt if best is None else min(best, dt)
+    return {"value": round(bytes_step / best / 1e9, 3), "unit": "GB/s", "cores": torch.get_num_threads(),
+            "kind": "port", "ms_per_step": round(best * 1e3, 2),
+            "sample": f"the full step (sum + mean + amax over all {feat_cpu.shape[0]:,} points) with "
+                      f"torch.Tensor.scatter_reduce_ on the host, best of {reps}"}
+
+
+def run_reference(args):
+    """CPU statement of the operators on the same workload (rank 0 only)."""
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    from oracle import scatter_oracle as O
+    from torchex_b200 import workloads as W
+    torch.set_num_threads(os.cpu_count() or 1)
+    n, c, m = N_POINTS, CHANNELS, N_SEGMENTS
+    ids, _ = W.skewed_ids(n, m, seed=SEED)
+    feat = W.features(n, c, SEED, device="cpu")
+    # bounded sample: a prefix of the (randomly permuted) points, sized so that the
+    # whole run stays within about two minutes
+    index_full = ids[:, None].expand(-1, c)
+    t = time.perf_counter()
+    O.cpu_forward_step(feat, index_full, m)
+    t_full = time.perf_counter() - t
+    total_steps = args.steps + max(args.warmup, 1)
+    budget = 120.0 / total_steps
+    frac = min(1.0, budget / t_full)
+    n_s = max(1000, int(n * frac))
+    f_s, i_s = feat[:n_s].contiguous(), ids[:n_s, None].expand(-1, c)
+    m_s = m
+    b = algorithmic_bytes(n_s, c, m_s)
+    bytes_step = sum(b.values())
+    for _ in range(max(args.warmup, 1)):
+        O.cpu_forward_step(f_s, i_s, m_s)
+    t = time.perf_counter()
+    for _ in range(args.steps):
+        O.cpu_forward_step(f_s, i_s, m_s)
+    dt = (time.perf_counter() - t) / args.steps
+    value = bytes_step / dt / 1e9
+    sample = (f"first {n_s:,} of {n:,} points of the workload ({100 * n_s / n:.1f} %), all {m:,} output rows, "
+              f"torch.Tensor.scatter_reduce_ sum + mean + amax per step")
+    line = {
+        "impl": "reference", "metric": "scatter_fwd_GBps", "value": round(value, 3), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": round(dt * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "skewed segments: N=1,000,000 points, C=128 fp32, M=50,000 segments "
+                               "(Zipf 1.2 sizes + one 100,000-point segment), ids randomly permuted; "
+                               "step = scatter_sum + scatter_mean + scatter_max forward",
+                   "note": "TorchEx has no CPU kernel for this path (its binding rejects non-CUDA tensors); "
+                           "this arm is the CPU statement of the operators, torch.Tensor.scatter_reduce_, on the host cores"},
+        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "Mpoints_per_s": round(3 * n_s / dt / 1e6, 2),
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-multi-frame", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -215,3 +215,19 @@ def within_tolerance(got, want, rel: float = 1e-5, abs_: float = 1e-6, slack=Non
     if slack is not None:
         bound = bound + np.asarray(slack, dtype=np.float64)
     return np.abs(got - want) <= bound
+
+
+# ---- timed CPU baseline ------------------------------------------------------------------
+
+def cpu_forward_step(feat_cpu: torch.Tensor, index_cpu: torch.Tensor, m: int):
+    """One forward pass of the path on the host: sum, mean and max of
+    ``feat_cpu[N, C]`` by ``index_cpu`` (int64 ``[N, C]``, the ids expanded along
+    the channels) with ``torch.Tensor.scatter_reduce_``, the CPU statement of the
+    operators (TorchEx itself has no CPU kernel, torchex/src/scatter/scatter.cpp:4-5).
+    Uses however many threads torch is configured with."""
+    c = feat_cpu.shape[1]
+    outs = []
+    for mode in ("sum", "mean", "amax"):
+        outs.append(torch.zeros((m, c), dtype=torch.float32).scatter_reduce_(
+            0, index_cpu, feat_cpu, mode, include_self=False))
+    return outs

@@ -1,0 +1,147 @@
+"""Multi-frame batches sharded over the GPUs of one box (one process per GPU).
+
+Frames are independent: each owns a disjoint, contiguous range of global
+segment ids (frame f's local ids are offset by the number of segments of the
+frames before it), so no reduction crosses a frame and no exchange is needed
+for correctness.  Each rank takes a contiguous block of frames, builds one
+``ScatterData`` over its frames' points with ids rebased to start at zero, and
+runs the single-GPU path on its shard.  Only a caller that wants the full
+``[M, C]`` result on every GPU pays for a collective: a variable-size
+all-gather of the shard outputs over NCCL, landing in each GPU's own memory.
+
+The reference has no multi-GPU code at all (every test pins ``cuda:0``,
+test/test_scatter.py:9); this module is the driver the single-GPU operators
+need to serve a batch of frames on an 8-GPU box.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def frame_blocks(num_frames: int, world_size: int) -> List[Tuple[int, int]]:
+    """Contiguous [start, stop) block of frames per rank; sizes differ by at most one."""
+    if num_frames < 0 or world_size < 1:
+        raise ValueError("num_frames must be >= 0 and world_size >= 1")
+    base, extra = divmod(num_frames, world_size)
+    blocks, start = [], 0
+    for r in range(world_size):
+        stop = start + base + (1 if r < extra else 0)
+        blocks.append((start, stop))
+        start = stop
+    return blocks
+
+
+def exclusive_offsets(sizes: Sequence[int]) -> List[int]:
+    """[0, s0, s0 + s1, ...] with one more entry than ``sizes``."""
+    out = [0]
+    for s in sizes:
+        out.append(out[-1] + int(s))
+    return out
+
+
+@dataclass
+class ShardLayout:
+    """Where one rank's shard sits in the global batch."""
+    rank: int
+    world_size: int
+    frames: Tuple[int, int]          # block of frames owned by this rank
+    seg_base: int                    # first global segment id of the shard
+    seg_count: int                   # segments in the shard
+    row_base: int                    # first global row (point) of the shard
+    row_count: int                   # points in the shard
+    seg_counts_all: List[int]        # segments per rank, for the gather
+    seg_total: int
+
+
+def shard_layout(frame_segments: Sequence[int], frame_points: Sequence[int], rank: int,
+                 world_size: int) -> ShardLayout:
+    """Layout of ``rank``'s shard from the per-frame segment and point counts
+    (every rank knows these small host-side lists)."""
+    if len(frame_segments) != len(frame_points):
+        raise ValueError("frame_segments and frame_points differ in length")
+    if not 0 <= rank < world_size:
+        raise ValueError(f"rank {rank} outside world of {world_size}")
+    blocks = frame_blocks(len(frame_segments), world_size)
+    seg_off = exclusive_offsets(frame_segments)
+    row_off = exclusive_offsets(frame_points)
+    lo, hi = blocks[rank]
+    per_rank = [seg_off[b] - seg_off[a] for a, b in blocks]
+    return ShardLayout(rank, world_size, (lo, hi), seg_off[lo], seg_off[hi] - seg_off[lo], row_off[lo],
+                       row_off[hi] - row_off[lo], per_rank, seg_off[-1])
+
+
+def concat_local_ids(frame_ids: Sequence[torch.Tensor], frame_segments: Sequence[int]) -> torch.Tensor:
+    """Ids of a block of frames, each frame's local ids offset by the segments of
+    the frames before it inside the block (so they start at zero for the shard)."""
+    off = exclusive_offsets(frame_segments)
+    return torch.cat([ids + off[i] for i, ids in enumerate(frame_ids)]) if len(frame_ids) else \
+        torch.empty(0, dtype=torch.int64)
+
+
+def gather_shards(local: torch.Tensor, layout: ShardLayout, group=None) -> torch.Tensor:
+    """Replicated ``[seg_total, C]`` tensor from every rank's ``[seg_count, C]``
+    shard.  Shards are padded to the largest one so a single equal-size
+    all-gather (``all_gather_into_tensor``: NCCL over NVLink on GPUs, gloo on
+    CPU) moves them; the padding is dropped while the rows are put in place."""
+    world = layout.world_size
+    if world == 1:
+        return local
+    biggest = max(layout.seg_counts_all)
+    c = local.shape[1]
+    padded = local.new_zeros((biggest, c))
+    padded[: local.shape[0]] = local
+    gathered = local.new_empty((world * biggest, c))
+    dist.all_gather_into_tensor(gathered, padded, group=group)
+    out = local.new_empty((layout.seg_total, c))
+    start = 0
+    for r, cnt in enumerate(layout.seg_counts_all):
+        out[start:start + cnt] = gathered[r * biggest: r * biggest + cnt]
+        start += cnt
+    return out
+
+
+class FrameShard:
+    """One rank's share of a multi-frame batch.
+
+    ``reduce`` is a callable ``(op, feats, data) -> tensor or (tensor, arg)``;
+    the default runs the CUDA operators of this package.  Tests on CPU ranks
+    pass a stand-in so the bookkeeping is exercised without a GPU.
+    """
+
+    def __init__(self, frame_ids: Sequence[torch.Tensor], frame_cnts: Sequence[torch.Tensor],
+                 layout: ShardLayout, device, make_data: Optional[Callable] = None,
+                 reduce: Optional[Callable] = None):
+        self.layout = layout
+        self.device = device
+        segs = [int(c.numel()) for c in frame_cnts]
+        ids = concat_local_ids(list(frame_ids), segs).to(device)
+        cnts = (torch.cat(list(frame_cnts)) if len(frame_cnts) else torch.empty(0, dtype=torch.int64)).to(device)
+        if ids.numel() != layout.row_count or cnts.numel() != layout.seg_count:
+            raise ValueError("frames handed to FrameShard do not match its layout")
+        if make_data is None:
+            from .operator_py import ScatterData
+            make_data = ScatterData
+        self.data = make_data(ids, cnts)
+        self._reduce = reduce or _cuda_reduce
+
+    def scatter(self, op: str, feats: torch.Tensor, replicated: bool = False, group=None):
+        """Reduces this rank's points.  Returns the shard's ``[seg_count, C]``
+        result (for ``max`` also ``arg`` holding GLOBAL row numbers), or with
+        ``replicated=True`` the full ``[seg_total, C]`` tensors on every rank."""
+        res = self._reduce(op, feats, self.data)
+        if op == "max":
+            out, arg = res
+            arg = torch.where(arg >= 0, arg + self.layout.row_base, arg)
+            if replicated:
+                return gather_shards(out, self.layout, group), gather_shards(arg, self.layout, group)
+            return out, arg
+        return gather_shards(res, self.layout, group) if replicated else res
+
+
+def _cuda_reduce(op: str, feats: torch.Tensor, data):
+    from .operator_py import scatter_max, scatter_mean, scatter_sum
+    return {"sum": scatter_sum, "mean": scatter_mean, "max": scatter_max}[op](feats, data)
