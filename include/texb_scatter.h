@@ -149,6 +149,42 @@ int texb_segment_reduce(int op, const float* feats, const int32_t* sid,
                         float* out, int32_t* arg, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/* texb_segment_reduce for callers that cannot allocate device memory.
+ * No counterpart in the reference.
+ *
+ * Who needs it: code that is not allowed to call cudaMalloc (or any allocating
+ * library routine) once it is running -- a real-time perception loop whose
+ * buffers are all sized at start-up, a plugin that lives inside a host
+ * application's fixed memory pool, code placed between stream-ordered work
+ * where an allocation would stall the device.  Such a caller owns feats, the
+ * plan arrays and the outputs, but has nowhere to get the reduce workspace.
+ *
+ * Here the workspace is an array inside the library image,
+ * texb_static_scratch_bytes() = 4 MiB, held by every GPU that loads the
+ * library until the process exits.  The call allocates nothing: no cudaMalloc,
+ * no cudaFree, no allocating library call.  Arguments and results are those of
+ * texb_segment_reduce without the workspace pair.
+ *
+ * Limits and rules:
+ *   - a shape whose records do not fit in the 4 MiB (only possible with a very
+ *     small "rows_per_cta" knob or thousands of channels) is rejected with
+ *     TEXB_ERR_UNSUPPORTED and a message; nothing is launched;
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and loads the kernels;
+ *     make that first call before any stream capture begins;
+ *   - all calls on one GPU share the one array and it keeps the previous
+ *     call's contents (the kernels rewrite every word they later read, so
+ *     nothing needs clearing); two calls that overlap on the GPU, e.g. on
+ *     different streams, race on it -- keep them on one stream or order them
+ *     with events. */
+size_t texb_static_scratch_bytes(void);
+int texb_segment_reduce_static(int op, const float* feats, const int32_t* sid,
+                               const int32_t* perm, const int32_t* offsets,
+                               int has_empty, const int32_t* balance,
+                               int balance_len, int64_t n, int channel,
+                               int64_t num_segments, float* out, int32_t* arg,
+                               void* stream);
+
 /* Workspace for the two reference-shaped entry points below: room to expand
  * pre_sum back into per-row segment ids plus texb_reduce_workspace_bytes. */
 size_t texb_scatter_compat_workspace_bytes(int64_t num_total, int channel);

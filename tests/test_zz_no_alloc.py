@@ -1,0 +1,83 @@
+"""The allocation-free entry point against the ordinary one.
+
+``texb_segment_reduce_static`` serves callers that may not allocate device
+memory while they run (a real-time loop with all buffers sized at start-up, a
+plugin inside a fixed memory pool): its scratch is a 4 MiB array inside the
+library instead of a caller workspace.  Both entry points are called through
+the C ABI on the same inputs, twice in a row, and must agree: sum and mean
+within the tolerance of the other parity tests, max and argmax exactly.  The
+second call runs on what the first left in the shared array.
+
+The file name sorts last so that, in a run that stops at the first failure,
+every other test has already run.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import scatter_oracle as O
+from torchex_b200 import ScatterData, _native, workloads as W
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+REL, ABS = 1e-5, 1e-6  # same tolerance as tests/gpu_util.py
+
+
+def _call(static, op, feat, data, m, out, arg, ws):
+    lib = _native.lib()
+    n, c = feat.shape
+    stream = torch.cuda.current_stream().cuda_stream
+    perm = None if data.perm is None else data.perm.data_ptr()
+    head = (op, feat.data_ptr(), data.sid.data_ptr(), perm, data.preSum.data_ptr(), int(data.has_empty),
+            data.balance.data_ptr(), data.balance.numel(), n, c, m, out.data_ptr(), arg.data_ptr())
+    if static:
+        status = lib.texb_segment_reduce_static(*head, stream)
+    else:
+        status = lib.texb_segment_reduce(*head, ws.data_ptr(), ws.numel(), stream)
+    assert status == 0, _native.last_error()
+
+
+@pytest.mark.parametrize("shuffled", [True, False])
+def test_static_scratch_entry_matches_workspace_entry(shuffled):
+    lib = _native.lib()
+    n, c, m = 120_000, 128, 6_000
+    ids, cnt = W.skewed_ids(n, m, seed=31, giant=20_000, shuffled=shuffled)
+    with torch.cuda.device(DEV):
+        feat = W.features(n, c, 31, device=DEV)
+        data = ScatterData(ids.to(DEV), cnt.to(DEV))
+        ws = torch.empty(lib.texb_reduce_workspace_bytes(n, c), dtype=torch.uint8, device=DEV)
+        assert lib.texb_static_scratch_bytes() == 4 << 20
+        want, want_arg = {}, None
+        for op in (_native.OP_SUM, _native.OP_MEAN, _native.OP_MAX):
+            out = torch.empty((m, c), device=DEV)
+            arg = torch.empty((m, c), dtype=torch.int32, device=DEV)
+            _call(False, op, feat, data, m, out, arg, ws)
+            want[op] = out.cpu().numpy()
+            if op == _native.OP_MAX:
+                want_arg = arg.cpu().numpy()
+        for round_ in range(2):  # two calls in a row share the built-in scratch
+            for op in (_native.OP_SUM, _native.OP_MEAN, _native.OP_MAX):
+                out = torch.full((m, c), float("nan"), device=DEV)
+                arg = torch.full((m, c), -7, dtype=torch.int32, device=DEV)
+                _call(True, op, feat, data, m, out, arg, None)
+                torch.cuda.synchronize()
+                got = out.cpu().numpy()
+                if op == _native.OP_MAX:
+                    assert np.array_equal(got, want[op]), f"max differs (call {round_})"
+                    assert np.array_equal(arg.cpu().numpy(), want_arg), f"argmax differs (call {round_})"
+                else:
+                    assert O.within_tolerance(got, want[op], REL, ABS).all(), f"op {op} differs (call {round_})"
+
+
+def test_static_scratch_entry_rejects_oversized_shapes():
+    lib = _native.lib()
+    old = _native.tune_get("rows_per_cta")
+    try:
+        _native.tune_set("rows_per_cta", 64)  # 2 records per 64 rows: far beyond 4 MiB at this size
+        n, c = 4_000_000, 128
+        status = lib.texb_segment_reduce_static(_native.OP_SUM, 1, 1, None, None, 0, None, 0, n, c, 10, 1, None, None)
+        assert status == 2  # TEXB_ERR_UNSUPPORTED, reported before any pointer is touched
+        assert "scratch" in _native.last_error()
+    finally:
+        _native.tune_set("rows_per_cta", old)

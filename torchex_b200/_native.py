@@ -34,6 +34,10 @@ _SIGNATURES = {
     "texb_segment_reduce": (_c.c_int, [_c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                        _c.c_int, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int, _c.c_int64,
                                        _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
+    "texb_static_scratch_bytes": (_c.c_size_t, []),
+    "texb_segment_reduce_static": (_c.c_int, [_c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                              _c.c_int, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int, _c.c_int64,
+                                              _c.c_void_p, _c.c_void_p, _c.c_void_p]),
     "texb_scatter_compat_workspace_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int]),
     "texb_scatter_sum": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int,
                                     _c.c_int, _c.c_int64, _c.c_void_p, _c.c_size_t, _c.c_void_p]),

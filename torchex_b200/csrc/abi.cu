@@ -22,6 +22,9 @@ int segment_reduce_impl(int, const float*, const int32_t*, const int32_t*, const
                         const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, void*, size_t,
                         cudaStream_t);
 int plan_balance_impl(const int32_t*, int64_t, int32_t*, int, cudaStream_t);
+int segment_reduce_static_impl(int, const float*, const int32_t*, const int32_t*, const int32_t*, int,
+                               const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, cudaStream_t);
+size_t static_scratch_bytes_impl();
 int device_status_impl(int*);
 int expand_offsets_impl(const int32_t*, int32_t*, int64_t, int64_t, cudaStream_t);
 int sum_backward_impl(const float*, const int32_t*, float*, int64_t, int, int64_t, cudaStream_t);
@@ -181,6 +184,16 @@ int texb_segment_reduce(int op, const float* feats, const int32_t* sid, const in
   return segment_reduce_impl(op, feats, sid, perm, offsets, has_empty, balance, balance_len, n,
                              channel, num_segments, out, arg, workspace, workspace_bytes,
                              static_cast<cudaStream_t>(stream));
+}
+
+size_t texb_static_scratch_bytes(void) { return static_scratch_bytes_impl(); }
+
+int texb_segment_reduce_static(int op, const float* feats, const int32_t* sid, const int32_t* perm,
+                               const int32_t* offsets, int has_empty, const int32_t* balance,
+                               int balance_len, int64_t n, int channel, int64_t num_segments,
+                               float* out, int32_t* arg, void* stream) {
+  return segment_reduce_static_impl(op, feats, sid, perm, offsets, has_empty, balance, balance_len, n,
+                                    channel, num_segments, out, arg, static_cast<cudaStream_t>(stream));
 }
 
 size_t texb_scatter_compat_workspace_bytes(int64_t num_total, int channel) {

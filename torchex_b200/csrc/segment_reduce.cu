@@ -32,6 +32,7 @@
 
 #include <cfloat>
 #include <cstdio>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -1141,6 +1142,55 @@ int expand_offsets_impl(const int32_t* offsets, int32_t* sid, int64_t n, int64_t
 }
 
 size_t reduce_workspace_bytes_impl(int64_t n, int C) { return reduce_workspace_bytes(n, C); }
+
+// ---- reduce without a caller workspace -------------------------------------------------
+// Some callers may not allocate device memory at all once they are running: a
+// perception loop that sizes every buffer at start-up and forbids cudaMalloc
+// afterwards, a plugin living inside a host application's fixed memory pool, or
+// code between stream-ordered work where an allocation would stall the device.
+// For them the records of the reduce kernels live in this array, which is part of
+// the library image: every GPU that loads the library holds these 4 MiB until the
+// process exits.
+constexpr size_t kStaticScratchBytes = size_t(4) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+size_t static_scratch_bytes_impl() { return kStaticScratchBytes; }
+
+int segment_reduce_static_impl(int op, const float* feats, const int32_t* sid, const int32_t* perm,
+                               const int32_t* offsets, int has_empty, const int32_t* balance,
+                               int balance_len, int64_t n, int C, int64_t m, float* out, int32_t* arg,
+                               cudaStream_t stream) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static void* device_ptr[kMaxDevices] = {};
+  if (n < 0 || C < 1) return fail(TEXB_ERR_INVALID_ARGUMENT, "bad sizes n=%lld channel=%d", (long long)n, C);
+  const size_t need = reduce_workspace_bytes(n, C);
+  if (need > kStaticScratchBytes)
+    return fail(TEXB_ERR_UNSUPPORTED,
+                "this shape needs %zu bytes of scratch but the built-in scratch holds %zu; "
+                "use texb_segment_reduce with a caller workspace (or a larger rows_per_cta)",
+                need, kStaticScratchBytes);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(TEXB_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!device_ptr[dev]) {
+      // In host code the array's name is only a handle: ask the runtime for the
+      // address the array has on the current device, once per device.
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess || !p)
+        return fail(TEXB_ERR_CUDA, "cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
+      device_ptr[dev] = p;
+    }
+    scratch = device_ptr[dev];
+  }
+  return segment_reduce_impl(op, feats, sid, perm, offsets, has_empty, balance, balance_len, n, C, m, out,
+                             arg, scratch, kStaticScratchBytes, stream);
+}
 
 int device_status_impl(int* wait_timeouts) {
   int v = 0;
