@@ -178,3 +178,22 @@ def test_scatter_ext_module_keeps_reference_signatures():
         scatter_ext.sum(feat_s, pre, out, 1)           # CPU tensor
     with pytest.raises(RuntimeError):
         scatter_ext.sum(feat_d.t(), pre, out, 1)       # not contiguous
+
+
+def test_golden_hand_checkable_cases():
+    import os
+    d = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "spec_small.npz"))
+    for name in ("ints", "gap_ties", "extremes"):
+        feat = torch.from_numpy(d[f"{name}.feat"]).to(DEV)
+        ids = torch.from_numpy(d[f"{name}.ids"]).to(DEV)
+        m = int(d[f"{name}.m"])
+        cnt = torch.bincount(ids, minlength=m)
+        data = ScatterData(ids, cnt)
+        mx, arg = scatter_max(feat, data)
+        want_max = d[f"{name}.max"]
+        assert np.array_equal(mx.cpu().numpy(), want_max), name
+        assert np.array_equal(arg.cpu().numpy(), d[f"{name}.arg"]), name
+        s = scatter_sum(feat, data).cpu().numpy()
+        assert np.array_equal(s, d[f"{name}.sum"].astype(np.float32)), name      # small integers / infinities: exact
+        mean = scatter_mean(feat, data).cpu().numpy()
+        assert np.array_equal(mean, d[f"{name}.mean"].astype(np.float32)), name

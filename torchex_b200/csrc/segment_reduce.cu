@@ -91,8 +91,12 @@ struct OpSumComp {  // fp32 sum + error-free two-sum: (s, c) with s + c the exac
 #pragma unroll
     for (int k = 0; k < VEC; ++k) { x.s[k] = __uint_as_float(wa[k]); x.c[k] = __uint_as_float(wb[k]); }
   }
+  // An infinite running sum (infinite input or fp32 overflow) makes the error
+  // term NaN; the sum itself is then the answer, as for a plain fp32 sum.
   template <int VEC>
-  static __device__ __forceinline__ float value(const State<VEC>& x, int k) { return x.s[k] + x.c[k]; }
+  static __device__ __forceinline__ float value(const State<VEC>& x, int k) {
+    return (fabsf(x.s[k]) == INFINITY) ? x.s[k] : x.s[k] + x.c[k];
+  }
   template <int VEC>
   static __device__ __forceinline__ int index(const State<VEC>&, int) { return 0; }
 };
