@@ -142,12 +142,26 @@ def run_ours(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     lib = _native.lib()
-    n, c, m = N_POINTS, CHANNELS, N_SEGMENTS
+    n, c, m = args.points, args.channels, args.segments
+    # ---- inputs resident in HBM: this rank's frame
+    if args.workload == "voxel":
+        # dynamic-voxelisation frames (about two points per voxel), concatenated with offset ids
+        from torchex_b200 import frames as F
+        fr = [W.voxel_frame(200_000, SEED + 1000 * rank + f) for f in range(args.frames)]
+        ids = F.concat_local_ids([i for i, _ in fr], [int(cn.numel()) for _, cn in fr])
+        cnt = torch.cat([cn for _, cn in fr])
+        n, m = int(ids.numel()), int(cnt.numel())
+        workload = (f"voxel frames: {args.frames} x 200,000 points, C={c} fp32, M={m:,} voxels from torch.unique "
+                    "(ids unsorted); step = scatter_sum + scatter_mean + scatter_max forward with a prebuilt plan "
+                    "[secondary workload]")
+    else:
+        ids, cnt = W.skewed_ids(n, m, seed=SEED + rank, giant=n // 10)
+        workload = (f"skewed segments: N={n:,} points, C={c} fp32, M={m:,} segments "
+                    f"(Zipf 1.2 sizes + one {n // 10:,}-point segment), ids randomly permuted; "
+                    "step = scatter_sum + scatter_mean + scatter_max forward with a prebuilt plan"
+                    + ("" if (n, c, m) == (N_POINTS, CHANNELS, N_SEGMENTS) else " [reduced size, for profiling only]"))
     bytes_op = algorithmic_bytes(n, c, m)
     bytes_step = sum(bytes_op.values())
-
-    # ---- inputs resident in HBM: this rank's frame
-    ids, cnt = W.skewed_ids(n, m, seed=SEED + rank)
     feat = W.features(n, c, SEED + rank, device=dev)
     data = ScatterData(ids.to(dev), cnt.to(dev))
     outs = {k: torch.empty((m, c), device=dev) for k in ("sum", "mean", "max")}
@@ -283,11 +297,9 @@ def run_ours(args):
             "steps": k, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": "skewed segments: N=1,000,000 points, C=128 fp32, M=50,000 segments "
-                                   "(Zipf 1.2 sizes + one 100,000-point segment), ids randomly permuted; "
-                                   "step = scatter_sum + scatter_mean + scatter_max forward with a prebuilt plan",
+            "config": {"workload": workload,
                        "points_per_gpu": n, "channels": c, "segments": m, "frames": world,
-                       "sharding": "one frame per GPU, no collective", "l2": "inputs_exceed_l2 (512 MB of features per step op)",
+                       "sharding": "one frame per GPU, no collective", "l2": f"inputs_exceed_l2 ({4 * n * c / 1e6:.0f} MB of features read by each of the three reductions of a step)",
                        "seed": SEED},
             "Mpoints_per_s": round(world * 3 * n / (ms_per_step * 1e-3) / 1e6, 1),
             "pct_of_hbm_8000": round(100 * value / world / HBM_NOMINAL_GBS, 2),
@@ -428,6 +440,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--workload", choices=["skewed", "voxel"], default="skewed",
+                    help="skewed = the headline configuration; voxel = concatenated dynamic-voxelisation frames")
+    ap.add_argument("--frames", type=int, default=4, help="frames of the voxel workload")
+    ap.add_argument("--points", type=int, default=N_POINTS, help="reduced sizes are for profiling only")
+    ap.add_argument("--segments", type=int, default=N_SEGMENTS)
+    ap.add_argument("--channels", type=int, default=CHANNELS)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-multi-frame", action="store_true")

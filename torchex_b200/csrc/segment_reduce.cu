@@ -264,6 +264,28 @@ __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __re
   }
 }
 
+// A segment of exactly one row: sum and mean are the row itself; max goes through
+// the operator so that NaN / -inf rows keep the (-FLT_MAX, -1) answer.
+template <class Op, int VEC>
+__device__ __forceinline__ void store_single(float* __restrict__ out, int32_t* __restrict__ arg, int seg,
+                                             int C, int ch, bool lane_on, const float (&v)[VEC], int row) {
+  if constexpr (Op::kIsMax) {
+    typename Op::template State<VEC> x;
+    Op::template init<VEC>(x);
+    Op::template add<VEC>(x, v, row);
+    store_out<Op, VEC>(out, arg, seg, C, ch, lane_on, x, 1, false);
+  } else {
+    if (!lane_on) return;
+    float* po = out + int64_t(seg) * C + ch;
+    if constexpr (VEC == 4) {
+      *reinterpret_cast<float4*>(po) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) po[k] = v[k];
+    }
+  }
+}
+
 // Workspace: for CTA b and channel slab y there are two records,
 // rec = (y * num_ctas + b) * 2 + {0: head, 1: tail}.  A record is CPS words of
 // `a`, CPS words of `b` (CPS = LPR * VEC channels per slab) and an int4 of
@@ -374,6 +396,11 @@ segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict
   __shared__ int s_cnt[SLOTS];
   __shared__ unsigned s_flag[SLOTS];
 
+#if __CUDA_ARCH__ >= 900
+  // Let the dependent fix-up grid be scheduled now (it parks at its own
+  // griddepcontrol.wait until this grid has finished); a no-op for a plain launch.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
   const int lane_g = threadIdx.x & (LPR - 1);
   const int group = threadIdx.x / LPR;
   const unsigned gmask =
@@ -542,13 +569,18 @@ segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __r
   static_assert(LPR == 16 || LPR == 32, "staged kernel handles 16 or 32 lanes per row");
   static_assert((S - 1) * B <= T && T % B == 0 && LPR % B == 0, "the copy front must stay within two tiles");
 
-  extern __shared__ __align__(16) unsigned char s_dyn[];
-  uint32_t* s_vec = reinterpret_cast<uint32_t*>(s_dyn);  // the ring, reused after the walk
+  extern __shared__ __align__(16) unsigned char s_dyn[];  // the ring
+  __shared__ __align__(16) uint32_t s_vec[SLOTS * 2 * CPS];  // edge runs of the groups
   __shared__ int s_sid[SLOTS];
   __shared__ int s_cnt[SLOTS];
   __shared__ unsigned s_flag[SLOTS];
   __shared__ __align__(8) unsigned long long s_bar[BULK ? GPC * S : 1];  // one mbarrier per (group, stage)
 
+#if __CUDA_ARCH__ >= 900
+  // Let the dependent fix-up grid be scheduled now (it parks at its own
+  // griddepcontrol.wait until this grid has finished); a no-op for a plain launch.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
   const int lane_g = threadIdx.x & (LPR - 1);
   const int group = threadIdx.x / LPR;
   const int lane_base = (threadIdx.x & 31) & ~(LPR - 1);  // first lane of the group
@@ -572,13 +604,6 @@ segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __r
     }
     __syncthreads();
   }
-
-  // Edge runs are parked in registers until the ring can be reused.
-  State head_acc, tail_acc;
-  int head_sid = 0, head_cnt = 0, tail_sid = 0, tail_cnt = 0;
-  unsigned head_flag = 0u, tail_flag = 0u;
-  Op::template init<VEC>(head_acc);
-  Op::template init<VEC>(tail_acc);
 
   if (g0 < g1) {
     const int L = g1 - g0;
@@ -683,17 +708,45 @@ segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __r
     State acc;
     Op::template init<VEC>(acc);
 
+    // Ends the current run: a complete segment goes to `out`, a run open at an
+    // edge of this range is parked in the group's shared-memory slot.
     auto close_run = [&](int sid_now, int cnt, bool open_right) {
       const bool open_left = is_first && first_open_left;
       if (!open_left && !open_right) {
         store_out<Op, VEC>(out, arg, sid_now, C, ch, lane_on, acc, cnt, mean);
-      } else if (!open_right) {
-        head_acc = acc; head_sid = sid_now; head_cnt = cnt; head_flag = kValid | kOpenLeft;
       } else {
-        tail_acc = acc; tail_sid = sid_now; tail_cnt = cnt;
-        tail_flag = kValid | kOpenRight | (open_left ? kOpenLeft : 0u);
+        const int slot = 2 * group + (open_right ? 1 : 0);
+        uint32_t* pa = s_vec + slot * 2 * CPS + lane_g * VEC;
+        store_state<Op, VEC>(pa, pa + CPS, acc);
+        if (lane_g == 0) {
+          s_sid[slot] = sid_now;
+          s_cnt[slot] = cnt;
+          s_flag[slot] = kValid | (open_left ? kOpenLeft : 0u) | (open_right ? kOpenRight : 0u);
+        }
       }
     };
+    // One row of a batch that holds run ends.  `single`: the row is a whole segment.
+    auto row_step = [&](int q, const float4& t4, int row, bool end_k, bool single, int sids_reg, int lane_k) {
+      const float v[VEC] = {t4.x, t4.y, t4.z, t4.w};
+      if (single) {
+        const int sid_now = __shfl_sync(gmask, sids_reg, lane_k, LPR);
+        store_single<Op, VEC>(out, arg, sid_now, C, ch, lane_on, v, row);
+        is_first = false;
+        run_start = q + 1;
+      } else {
+        Op::template add<VEC>(acc, v, row);
+        if (end_k) {
+          const int sid_now = __shfl_sync(gmask, sids_reg, lane_k, LPR);
+          close_run(sid_now, q - run_start + 1, false);
+          is_first = false;
+          run_start = q + 1;
+          Op::template init<VEC>(acc);
+        }
+      }
+    };
+    // 1 when the previous row closed a run, i.e. the next row starts a segment
+    // (at the start of the range: unless the first run continues from the left).
+    unsigned carry = first_open_left ? 0u : 1u;
 
 #pragma unroll
     for (int bb = 0; bb < S - 1; ++bb) issue(bb, bb);
@@ -725,39 +778,46 @@ segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __r
       int rows_reg = 0;
       if constexpr (Op::kIsMax && HAS_PERM) rows_reg = tile_reg(cur_row_r, j0);
 
-      if (ends == 0u && q0 + B <= L) {
-        // eight rows of one run: no bookkeeping
+      if (q0 + B <= L) {
+        if (ends == 0u) {
+          // eight rows of one run: no bookkeeping
 #pragma unroll
-        for (int k = 0; k < B; ++k) {
-          const float4 t4 = src[k * kSlotFloat4];
-          const float v[VEC] = {t4.x, t4.y, t4.z, t4.w};
-          int row = g0 + q0 + k;
-          if constexpr (Op::kIsMax && HAS_PERM) row = __shfl_sync(gmask, rows_reg, (j0 & (LPR - 1)) + k, LPR);
-          Op::template add<VEC>(acc, v, row);
-        }
-      } else {
-        // a batch with run ends (or the ragged last batch): same loads, then a
-        // per-row check; the rows are already in registers when a run is closed
-        const int nv = min(B, L - q0);
-        const int sids_reg = tile_reg(cur_sid_r, j0);
-        float4 t4[B];
-#pragma unroll
-        for (int k = 0; k < B; ++k) t4[k] = src[(k < nv ? k : 0) * kSlotFloat4];
-#pragma unroll
-        for (int k = 0; k < B; ++k) {
-          if (k < nv) {
-            const float v[VEC] = {t4[k].x, t4[k].y, t4[k].z, t4[k].w};
+          for (int k = 0; k < B; ++k) {
+            const float4 t4 = src[k * kSlotFloat4];
+            const float v[VEC] = {t4.x, t4.y, t4.z, t4.w};
             int row = g0 + q0 + k;
             if constexpr (Op::kIsMax && HAS_PERM) row = __shfl_sync(gmask, rows_reg, (j0 & (LPR - 1)) + k, LPR);
             Op::template add<VEC>(acc, v, row);
-            if ((ends >> k) & 1u) {  // last row of its segment
-              const int sid_now = __shfl_sync(gmask, sids_reg, (j0 & (LPR - 1)) + k, LPR);
-              close_run(sid_now, q0 + k - run_start + 1, false);
-              is_first = false;
-              run_start = q0 + k + 1;
-              Op::template init<VEC>(acc);
-            }
           }
+          carry = 0u;
+        } else {
+          // a full batch with run ends: the rows are in registers before any run is closed
+          const int sids_reg = tile_reg(cur_sid_r, j0);
+          const unsigned singles = ends & ((ends << 1) | carry);  // rows that start and end a run
+          carry = (ends >> (B - 1)) & 1u;
+          float4 t4[B];
+#pragma unroll
+          for (int k = 0; k < B; ++k) t4[k] = src[k * kSlotFloat4];
+#pragma unroll
+          for (int k = 0; k < B; ++k) {
+            int row = g0 + q0 + k;
+            if constexpr (Op::kIsMax && HAS_PERM) row = __shfl_sync(gmask, rows_reg, (j0 & (LPR - 1)) + k, LPR);
+            row_step(q0 + k, t4[k], row, ((ends >> k) & 1u) != 0u, ((singles >> k) & 1u) != 0u, sids_reg,
+                     (j0 & (LPR - 1)) + k);
+          }
+        }
+      } else {
+        // the ragged last batch of the range
+        const int nv = L - q0;
+        const int sids_reg = tile_reg(cur_sid_r, j0);
+        const unsigned singles = ends & ((ends << 1) | carry);
+#pragma unroll 1
+        for (int k = 0; k < nv; ++k) {
+          const float4 t4 = src[k * kSlotFloat4];
+          int row = g0 + q0 + k;
+          if constexpr (Op::kIsMax && HAS_PERM) row = __shfl_sync(gmask, rows_reg, (j0 & (LPR - 1)) + k, LPR);
+          row_step(q0 + k, t4, row, ((ends >> k) & 1u) != 0u, ((singles >> k) & 1u) != 0u, sids_reg,
+                   (j0 & (LPR - 1)) + k);
         }
       }
     }
@@ -768,18 +828,6 @@ segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __r
     }
   }
   if constexpr (!BULK) cp_async_wait<0>();
-  __syncthreads();  // every copy has been waited for and every lane is done with the ring
-
-  if (head_flag) {
-    uint32_t* pa = s_vec + (2 * group) * 2 * CPS + lane_g * VEC;
-    store_state<Op, VEC>(pa, pa + CPS, head_acc);
-    if (lane_g == 0) { s_sid[2 * group] = head_sid; s_cnt[2 * group] = head_cnt; s_flag[2 * group] = head_flag; }
-  }
-  if (tail_flag) {
-    uint32_t* pa = s_vec + (2 * group + 1) * 2 * CPS + lane_g * VEC;
-    store_state<Op, VEC>(pa, pa + CPS, tail_acc);
-    if (lane_g == 0) { s_sid[2 * group + 1] = tail_sid; s_cnt[2 * group + 1] = tail_cnt; s_flag[2 * group + 1] = tail_flag; }
-  }
   __syncthreads();
   stitch_cta<Op, VEC, LPR>(s_vec, s_sid, s_cnt, s_flag, out, arg, ws, C, ch, lane_on, lane_g,
                            group, mean);
@@ -844,13 +892,24 @@ segment_fixup_kernel(Workspace ws, float* __restrict__ out, int32_t* __restrict_
   State acc;
   Op::template init<VEC>(acc);
   int cnt = 0;
-  for (int i = i0; i < i1; ++i) {
-    const int64_t rec = (rec_base + b + i) * 2 + ((i == K - 1) ? 0 : 1);
-    State x;
-    const uint32_t* ga = ws.vec + rec * 2 * CPS + lane_g * VEC;
-    load_state<Op, VEC>(ga, ga + CPS, x);
-    if (i == i0) acc = x; else Op::template merge<VEC>(acc, x);
-    cnt += ws.meta[rec].y;
+  for (int i = i0; i < i1; i += 4) {  // four independent record loads in flight
+    State x[4];
+    int c4[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int ii = min(i + u, i1 - 1);
+      const int64_t rec = (rec_base + b + ii) * 2 + ((ii == K - 1) ? 0 : 1);
+      const uint32_t* ga = ws.vec + rec * 2 * CPS + lane_g * VEC;
+      load_state<Op, VEC>(ga, ga + CPS, x[u]);
+      c4[u] = ws.meta[rec].y;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (i + u < i1) {
+        if (i + u == i0) acc = x[u]; else Op::template merge<VEC>(acc, x[u]);
+        cnt += c4[u];
+      }
+    }
   }
   uint32_t* pa = s_vec + group * 2 * CPS + lane_g * VEC;
   store_state<Op, VEC>(pa, pa + CPS, acc);

@@ -135,7 +135,8 @@ class FrameShard:
         res = self._reduce(op, feats, self.data)
         if op == "max":
             out, arg = res
-            arg = torch.where(arg >= 0, arg + self.layout.row_base, arg)
+            if self.layout.row_base:  # local rows -> global rows; -1 (no row) stays -1
+                arg.add_(arg.ge(0).to(arg.dtype).mul_(self.layout.row_base))
             if replicated:
                 return gather_shards(out, self.layout, group), gather_shards(arg, self.layout, group)
             return out, arg
