@@ -44,7 +44,7 @@ HBM_FALLBACK_GBS = 6650.0         # earlier copy measurement on this pool, used 
 # DRAM bytes of one reduce launch on this workload (dram__bytes_read.sum +
 # dram__bytes_write.sum of one ncu capture of this script; summary in
 # profiles/reduce_kernel_skewed_1m_c128.txt).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 543_200_000
 
 
 def algorithmic_bytes(n, c, m):
@@ -238,7 +238,8 @@ def run_ours(args):
                 "achieved": round(achieved, 1), "peak": peak, "peak_source": f"hbm_gbs of {peak_kind} copy",
                 "unit": "GB/s", "frac": round(achieved / peak, 4), "frac_of_nominal_8000": round(achieved / HBM_NOMINAL_GBS, 4),
                 "algorithmic_bytes_per_launch": bytes_op["sum"], "us_per_launch": round(sum_ms * 1e3, 2),
-                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH}
+                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (n, c, m) == (N_POINTS, CHANNELS, N_SEGMENTS)
+                and args.workload == "skewed" else None}
 
     # ---- end to end through the public operators, host buffers in pinned memory
     e2e = None
@@ -307,7 +308,7 @@ def run_ours(args):
             "roofline": roofline,
             "cpu_baseline": cpu,
             "e2e": e2e,
-            "gpu_launches": 6 * k,
+            "gpu_launches": 6 * k * world,
             "clocks": clocks,
             "multi_frame": multi,
             "device_wait_timeouts": timeouts,

@@ -508,7 +508,7 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // Bulk (TMA) copy of one row slab, global -> this CTA's shared memory, signalling
-// an mbarrier with the byte count.  Never multicast; the source is always this
+// an mbarrier with the byte count.  One destination CTA only; the source is always this
 // GPU's own memory.  Source, destination and size are multiples of 16 bytes.
 __device__ __forceinline__ void bulk_copy_g2s(unsigned smem_dst, const void* gmem_src, unsigned bytes,
                                               unsigned bar) {
