@@ -287,6 +287,8 @@ def run_ours(args):
     if not args.no_multi_frame:
         multi = multi_frame_bench(args, rank, world, dev, barrier)
 
+    configs = other_configs(dev) if (rank == 0 and world == 1 and not args.no_configs) else None
+
     # ---- host CPU baseline (rank 0, single-GPU run only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -311,11 +313,75 @@ def run_ours(args):
             "gpu_launches": 6 * k * world,
             "clocks": clocks,
             "multi_frame": multi,
+            "other_configs": configs,
             "device_wait_timeouts": timeouts,
         }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def other_configs(dev):
+    """Device-resident timings of the other configurations (forward, and backward
+    for the tie-stress case), through the C ABI with preallocated buffers."""
+    from torchex_b200 import ScatterData, _native, workloads as W
+    lib = _native.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps * 1e3
+
+    def forward(ids, cnt, feat, label, note):
+        n, c = feat.shape
+        m = cnt.numel()
+        data = ScatterData(ids.to(dev), cnt.to(dev))
+        out = torch.empty((m, c), device=dev)
+        arg = torch.empty((m, c), dtype=torch.int32, device=dev)
+        ws = torch.empty(lib.texb_reduce_workspace_bytes(n, c), dtype=torch.uint8, device=dev)
+        perm = None if data.perm is None else data.perm.data_ptr()
+        b = algorithmic_bytes(n, c, m)
+        res = {"points": n, "channels": c, "segments": m, "note": note}
+        for name, op in (("sum", _native.OP_SUM), ("mean", _native.OP_MEAN), ("max", _native.OP_MAX)):
+            us = timed(lambda: lib.texb_segment_reduce(op, feat.data_ptr(), data.sid.data_ptr(), perm,
+                                                       data.preSum.data_ptr(), 0, data.balance.data_ptr(),
+                                                       data.balance.numel(), n, c, m, out.data_ptr(), arg.data_ptr(),
+                                                       ws.data_ptr(), ws.numel(), stream), 50)
+            res[name] = {"us": round(us, 2), "GBps": round(b[name] / us / 1e3, 1), "Mpoints_per_s": round(n / us, 1)}
+        return res, data, arg
+
+    table = {}
+    ids, cnt = W.uniform_ids(20_000, 2_000, SEED)
+    table["uniform_20k_c16"], _, _ = forward(ids, cnt, W.features(20_000, 16, SEED, device=dev), "c1",
+                                             "1.3 MB of features: L2-resident and launch-bound")
+    ids, cnt = W.voxel_frame(200_000, SEED)
+    table["voxel_200k_c64"], _, _ = forward(ids, cnt, W.features(200_000, 64, SEED, device=dev), "c2",
+                                            "51 MB of features: L2-resident across repetitions")
+    ids, cnt, feat, grad = W.small_segments_with_ties(500_000, 128, SEED, device=dev)
+    fw, data, arg = forward(ids, cnt, feat, "c4", "256 MB of features; 10 % duplicated rows (ties)")
+    n, c, m = 500_000, 128, cnt.numel()
+    g_in = torch.empty((n, c), device=dev)
+    b_back = 4 * n * c + 4 * n + 4 * m * c
+    bw = {}
+    sid, perm = data.sid.data_ptr(), (None if data.perm is None else data.perm.data_ptr())
+    for name, fn, nbytes in (
+            ("sum", lambda: lib.texb_scatter_sum_backward(grad.data_ptr(), sid, perm, g_in.data_ptr(), n, c, m, stream), b_back),
+            ("mean", lambda: lib.texb_scatter_mean_backward(grad.data_ptr(), sid, perm, data.preSum.data_ptr(),
+                                                            g_in.data_ptr(), n, c, m, stream), b_back + 4 * m),
+            ("max", lambda: lib.texb_scatter_max_backward(grad.data_ptr(), arg.data_ptr(), sid, perm, g_in.data_ptr(),
+                                                          n, c, m, stream), b_back + 4 * m * c)):
+        us = timed(fn, 50)
+        bw[name] = {"us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1)}
+    fw["backward"] = bw
+    table["ties_500k_c128"] = fw
+    return table
 
 
 def multi_frame_bench(args, rank, world, dev, barrier):
@@ -417,6 +483,7 @@ def run_reference(args):
     value = bytes_step / dt / 1e9
     sample = (f"first {n_s:,} of {n:,} points of the workload ({100 * n_s / n:.1f} %), all {m:,} output rows, "
               f"torch.Tensor.scatter_reduce_ sum + mean + amax per step")
+    ref_cuda = reference_cuda_timing(n, c, m) if torch.cuda.is_available() else None
     line = {
         "impl": "reference", "metric": "scatter_fwd_GBps", "value": round(value, 3), "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": round(dt * 1e3, 3),
@@ -430,8 +497,51 @@ def run_reference(args):
                          "sample": sample},
         "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "Mpoints_per_s": round(3 * n_s / dt / 1e6, 2),
+        "reference_cuda": ref_cuda,
     }
     print(json.dumps(line))
+
+
+def reference_cuda_timing(n, c, m):
+    """TorchEx's own CUDA kernels (compiled unmodified into oracle/_ref) on the SORTED
+    variant of the workload -- the only layout they accept -- timed with CUDA events
+    on cuda:0.  Reported beside the CPU arm; it is not the arm's value."""
+    try:
+        from oracle import scatter_oracle as O
+        from torchex_b200 import workloads as W
+        if not O.reference_available():
+            return {"unavailable": "oracle/_ref/libtorchex_scatter_ref.so was not built"}
+        ref = O.reference_lib()
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        ids, cnt = W.skewed_ids(n, m, seed=SEED, shuffled=False)
+        max_cnt = int(cnt.max())
+        if ref.torchex_ref_limits(c, m, max_cnt, n) != 0:
+            return {"unavailable": "shape outside the reference's launch limits"}
+        feat = W.features(n, c, SEED, device=dev)
+        d_ids = ids.int().to(dev)
+        pre = torch.zeros(m + 1, dtype=torch.int32, device=dev)
+        out = torch.zeros((m, c), device=dev)
+        arg = torch.zeros((m, c), dtype=torch.int32, device=dev)
+        assert ref.torchex_ref_get_pre_sum(d_ids.data_ptr(), pre.data_ptr(), n) == 0
+        b = algorithmic_bytes(n, c, m)
+        res = {"layout": "ids sorted (required by the reference)", "max_cnt": max_cnt}
+        for name, call in (("sum", lambda: ref.torchex_ref_scatter_sum(feat.data_ptr(), pre.data_ptr(), out.data_ptr(), c, m, max_cnt, n)),
+                           ("max", lambda: ref.torchex_ref_scatter_max(feat.data_ptr(), pre.data_ptr(), out.data_ptr(), arg.data_ptr(), c, m, max_cnt, n))):
+            assert call() == 0
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 3
+            e0.record()
+            for _ in range(reps):
+                assert call() == 0
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / reps
+            res[name] = {"ms": round(ms, 3), "GBps": round(b[name] / ms / 1e6, 1)}
+        return res
+    except Exception as exc:  # the CPU arm must still print its line
+        return {"unavailable": f"{type(exc).__name__}: {exc}"}
 
 
 def main():
@@ -450,6 +560,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-multi-frame", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="skip the timings of the other configurations")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

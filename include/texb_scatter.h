@@ -206,26 +206,37 @@ int texb_scatter_max(const float* feats, const int32_t* pre_sum, float* out,
                      size_t workspace_bytes, void* stream);
 
 /* ---- backward -------------------------------------------------------------
- * Replace the ATen expressions of the autograd Functions. */
+ * Replace the ATen expressions of the autograd Functions.  In all three,
+ * entry i of ids[n] names the segment and the row of g_in that is written is
+ * perm[i], or i itself when perm is NULL.  Two ways to call them:
+ *   - ids = unq_inv in the caller's order, perm = NULL: the reference's
+ *     g[unq_inv] gather, one row of g fetched per point;
+ *   - ids = the plan's sid, perm = the plan's perm (NULL if the ids arrived
+ *     sorted): the same result walked in segment order, where neighbouring
+ *     entries share their segment and the rows of g / arg are fetched once.
+ * Every row of g_in is written exactly once (perm is a permutation). */
 
-/* g_in[i, :] = g[unq_inv[i], :]
+/* g_in[row_i, :] = g[ids[i], :]
  * (ScatterSumFunction.backward, torchex/operator_py/scatter_op.py:47-50). */
-int texb_scatter_sum_backward(const float* g, const int32_t* unq_inv,
-                              float* g_in, int64_t n, int channel,
-                              int64_t num_segments, void* stream);
+int texb_scatter_sum_backward(const float* g, const int32_t* ids,
+                              const int32_t* perm, float* g_in, int64_t n,
+                              int channel, int64_t num_segments, void* stream);
 
-/* g_in[i, :] = g[unq_inv[i], :] / count(unq_inv[i]), count taken from offsets
+/* g_in[row_i, :] = g[ids[i], :] / count(ids[i]), count taken from offsets and the
+ * quotient rounded as an IEEE fp32 division
  * (ScatterMeanFunction.backward, torchex/operator_py/scatter_op.py:73-78). */
-int texb_scatter_mean_backward(const float* g, const int32_t* unq_inv,
-                               const int32_t* offsets, float* g_in, int64_t n,
-                               int channel, int64_t num_segments, void* stream);
+int texb_scatter_mean_backward(const float* g, const int32_t* ids,
+                               const int32_t* perm, const int32_t* offsets,
+                               float* g_in, int64_t n, int channel,
+                               int64_t num_segments, void* stream);
 
-/* g_in[i, c] = (arg[unq_inv[i], c] == i) ? g[unq_inv[i], c] : 0, one fused
+/* g_in[row_i, c] = (arg[ids[i], c] == row_i) ? g[ids[i], c] : 0, one fused
  * pass instead of zeros + scatter_ (the intent of ScatterMaxFunction.backward,
  * torchex/operator_py/scatter_op.py:105-111, which raises as shipped). */
 int texb_scatter_max_backward(const float* g, const int32_t* arg,
-                              const int32_t* unq_inv, float* g_in, int64_t n,
-                              int channel, int64_t num_segments, void* stream);
+                              const int32_t* ids, const int32_t* perm,
+                              float* g_in, int64_t n, int channel,
+                              int64_t num_segments, void* stream);
 
 #ifdef __cplusplus
 }

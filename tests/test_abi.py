@@ -54,7 +54,7 @@ def test_bad_arguments_are_rejected_without_a_gpu():
     assert lib.texb_plan_build(None, 3, 0, 0, 1, None, None, None, None, None, 0, None) == 1
     assert "id_bytes" in _native.last_error()
     assert lib.texb_ids_inspect(None, 4, 5, None, None) == 1
-    assert lib.texb_scatter_sum_backward(None, None, None, -1, 4, 1, None) == 1
+    assert lib.texb_scatter_sum_backward(None, None, None, None, -1, 4, 1, None) == 1
     assert lib.texb_scatter_sum(None, None, None, 4, 3, 1, 10, None, 0, None) == 1
     assert lib.texb_tune_set(b"no_such_knob", 1) == 1
     assert lib.texb_tune_set(b"rows_per_cta", 7) == 1

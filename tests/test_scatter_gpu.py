@@ -197,3 +197,58 @@ def test_golden_hand_checkable_cases():
         assert np.array_equal(s, d[f"{name}.sum"].astype(np.float32)), name      # small integers / infinities: exact
         mean = scatter_mean(feat, data).cpu().numpy()
         assert np.array_equal(mean, d[f"{name}.mean"].astype(np.float32)), name
+
+
+def test_mean_is_the_sum_divided_like_torch_divides():
+    """The fused mean uses a shared-reciprocal division; it must round exactly like
+    the reference's `sum / unq_cnts` (scatter_op.py:69), forward and backward."""
+    for ids, cnt in (W.skewed_ids(400_000, 20_000, seed=41, giant=60_000), W.voxel_frame(200_000, seed=42)):
+        m = cnt.numel()
+        data = ScatterData(ids.to(DEV), cnt.to(DEV))
+        x = (W.features(ids.numel(), 32, 43) * 37.0).to(DEV)
+        mean = scatter_mean(x, data)
+        total = scatter_sum(x, data)
+        assert torch.equal(mean, total / cnt.to(DEV)[:, None])
+        g = (W.features(m, 32, 44) * 1e-3).to(DEV)
+        x.requires_grad_(True)
+        scatter_mean(x, data).backward(g)
+        assert torch.equal(x.grad, (g / cnt.to(DEV)[:, None])[ids.to(DEV)])
+    # extreme dividends take the true division
+    ids = torch.tensor([0, 0, 0, 1, 1, 1, 1, 1, 1, 1], device=DEV)
+    cnt = torch.tensor([3, 7], device=DEV)
+    vals = torch.tensor([1e-38, 3e-39, 0.0, 1e38, 3e38, -1e38, float("inf"), 1e-45, 5e-31, -0.0], device=DEV)
+    x = vals[:, None].repeat(1, 4).contiguous()
+    data = ScatterData(ids, cnt)
+    got = scatter_mean(x, data)
+    want = scatter_sum(x, data) / cnt[:, None]
+    assert torch.equal(torch.nan_to_num(got, nan=7.0), torch.nan_to_num(want, nan=7.0))
+
+
+def test_backward_entry_points_in_caller_order():
+    """The C ABI also accepts ids in the caller's order with no permutation (the
+    reference's g[unq_inv] gather); both walks give the same rows."""
+    lib = _native.lib()
+    ids, cnt, feat, grad = W.small_segments_with_ties(30_000, 20, seed=45)
+    n, c, m = 30_000, 20, cnt.numel()
+    data = ScatterData(ids.to(DEV), cnt.to(DEV))
+    g = grad.to(DEV)
+    _, arg = scatter_max(feat.to(DEV), data)
+    stream = torch.cuda.current_stream().cuda_stream
+    un = data.unq_inv
+    for mode in ("sum", "mean", "max"):
+        a = torch.empty((n, c), device=DEV)
+        b = torch.empty((n, c), device=DEV)
+        if mode == "sum":
+            s1 = lib.texb_scatter_sum_backward(g.data_ptr(), un.data_ptr(), None, a.data_ptr(), n, c, m, stream)
+            s2 = lib.texb_scatter_sum_backward(g.data_ptr(), data.sid.data_ptr(), data.perm.data_ptr(), b.data_ptr(), n, c, m, stream)
+            want = O.spec_sum_backward(grad, ids)
+        elif mode == "mean":
+            s1 = lib.texb_scatter_mean_backward(g.data_ptr(), un.data_ptr(), None, data.preSum.data_ptr(), a.data_ptr(), n, c, m, stream)
+            s2 = lib.texb_scatter_mean_backward(g.data_ptr(), data.sid.data_ptr(), data.perm.data_ptr(), data.preSum.data_ptr(), b.data_ptr(), n, c, m, stream)
+            want = O.spec_mean_backward(grad, ids, cnt)
+        else:
+            s1 = lib.texb_scatter_max_backward(g.data_ptr(), arg.data_ptr(), un.data_ptr(), None, a.data_ptr(), n, c, m, stream)
+            s2 = lib.texb_scatter_max_backward(g.data_ptr(), arg.data_ptr(), data.sid.data_ptr(), data.perm.data_ptr(), b.data_ptr(), n, c, m, stream)
+            want = O.spec_max_backward(grad, arg.cpu(), n)
+        assert s1 == 0 and s2 == 0, _native.last_error()
+        assert np.array_equal(a.cpu().numpy(), want) and np.array_equal(b.cpu().numpy(), want), mode

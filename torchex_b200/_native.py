@@ -44,11 +44,11 @@ _SIGNATURES = {
     "texb_scatter_max": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int,
                                     _c.c_int, _c.c_int, _c.c_int64, _c.c_void_p, _c.c_size_t,
                                     _c.c_void_p]),
-    "texb_scatter_sum_backward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64,
+    "texb_scatter_sum_backward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64,
                                              _c.c_int, _c.c_int64, _c.c_void_p]),
-    "texb_scatter_mean_backward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+    "texb_scatter_mean_backward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                               _c.c_int64, _c.c_int, _c.c_int64, _c.c_void_p]),
-    "texb_scatter_max_backward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+    "texb_scatter_max_backward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                              _c.c_int64, _c.c_int, _c.c_int64, _c.c_void_p]),
 }
 

@@ -27,11 +27,12 @@ int segment_reduce_static_impl(int, const float*, const int32_t*, const int32_t*
 size_t static_scratch_bytes_impl();
 int device_status_impl(int*);
 int expand_offsets_impl(const int32_t*, int32_t*, int64_t, int64_t, cudaStream_t);
-int sum_backward_impl(const float*, const int32_t*, float*, int64_t, int, int64_t, cudaStream_t);
-int mean_backward_impl(const float*, const int32_t*, const int32_t*, float*, int64_t, int, int64_t,
-                       cudaStream_t);
-int max_backward_impl(const float*, const int32_t*, const int32_t*, float*, int64_t, int, int64_t,
+int sum_backward_impl(const float*, const int32_t*, const int32_t*, float*, int64_t, int, int64_t,
                       cudaStream_t);
+int mean_backward_impl(const float*, const int32_t*, const int32_t*, const int32_t*, float*, int64_t, int,
+                       int64_t, cudaStream_t);
+int max_backward_impl(const float*, const int32_t*, const int32_t*, const int32_t*, float*, int64_t, int,
+                      int64_t, cudaStream_t);
 
 namespace {
 thread_local char t_error[512] = "";
@@ -241,23 +242,23 @@ int texb_scatter_max(const float* feats, const int32_t* pre_sum, float* out, int
                        workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
-int texb_scatter_sum_backward(const float* g, const int32_t* unq_inv, float* g_in, int64_t n,
-                              int channel, int64_t num_segments, void* stream) {
-  return sum_backward_impl(g, unq_inv, g_in, n, channel, num_segments,
+int texb_scatter_sum_backward(const float* g, const int32_t* ids, const int32_t* perm, float* g_in,
+                              int64_t n, int channel, int64_t num_segments, void* stream) {
+  return sum_backward_impl(g, ids, perm, g_in, n, channel, num_segments,
                            static_cast<cudaStream_t>(stream));
 }
 
-int texb_scatter_mean_backward(const float* g, const int32_t* unq_inv, const int32_t* offsets,
-                               float* g_in, int64_t n, int channel, int64_t num_segments,
-                               void* stream) {
-  return mean_backward_impl(g, unq_inv, offsets, g_in, n, channel, num_segments,
+int texb_scatter_mean_backward(const float* g, const int32_t* ids, const int32_t* perm,
+                               const int32_t* offsets, float* g_in, int64_t n, int channel,
+                               int64_t num_segments, void* stream) {
+  return mean_backward_impl(g, ids, perm, offsets, g_in, n, channel, num_segments,
                             static_cast<cudaStream_t>(stream));
 }
 
-int texb_scatter_max_backward(const float* g, const int32_t* arg, const int32_t* unq_inv,
-                              float* g_in, int64_t n, int channel, int64_t num_segments,
-                              void* stream) {
-  return max_backward_impl(g, arg, unq_inv, g_in, n, channel, num_segments,
+int texb_scatter_max_backward(const float* g, const int32_t* arg, const int32_t* ids,
+                              const int32_t* perm, float* g_in, int64_t n, int channel,
+                              int64_t num_segments, void* stream) {
+  return max_backward_impl(g, arg, ids, perm, g_in, n, channel, num_segments,
                            static_cast<cudaStream_t>(stream));
 }
 

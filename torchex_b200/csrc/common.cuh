@@ -32,4 +32,42 @@ constexpr int kCtaThreads = 256;
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+#ifdef __CUDACC__
+// v[k] / float(count) for VEC values that share the divisor, rounded exactly like
+// an IEEE fp32 division (what `sum / unq_cnts` and `g / unq_cnts` compute in
+// torchex/operator_py/scatter_op.py:69, 76).  One reciprocal refined to nearly
+// full double-word accuracy serves all VEC quotients; each quotient gets two
+// residual corrections, which leaves it correctly rounded whenever the dividend
+// is a normal number far from the overflow and underflow thresholds.  Anything
+// else (zero, subnormal, huge, infinite, NaN dividend) takes the true division.
+template <int VEC>
+__device__ __forceinline__ void divide_by_count(float (&v)[VEC], int count) {
+  if (count == 1) return;
+  const float b = float(count);
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(b));
+  y = fmaf(y, fmaf(-b, y, 1.f), y);
+  y = fmaf(y, fmaf(-b, y, 1.f), y);
+  float lo = fabsf(v[0]), hi = lo;
+#pragma unroll
+  for (int k = 1; k < VEC; ++k) {
+    lo = fminf(lo, fabsf(v[k]));
+    hi = fmaxf(hi, fabsf(v[k]));
+  }
+  if (lo > 1e-30f && hi < 1e30f) {  // false as well when a value is NaN
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      const float a = v[k];
+      float q = a * y;
+      q = fmaf(fmaf(-b, q, a), y, q);
+      q = fmaf(fmaf(-b, q, a), y, q);
+      v[k] = q;
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) v[k] = __fdiv_rn(v[k], b);
+  }
+}
+#endif
+
 }  // namespace texb

@@ -5,9 +5,12 @@
 //   max : g_in[i, c] = (arg[sid_i, c] == i) ? g[sid_i, c] : 0
 //
 // Lanes run along the channel axis (128-bit accesses when the layout allows),
-// a group of lanes handles eight consecutive points per step, and g_in is
-// written with streaming stores so that g / arg (reused by every point of a
-// segment) stay resident in L2.  No memset, no atomics.
+// a group of lanes handles eight consecutive entries of `ids` per step, and g_in
+// is written with streaming stores so that g / arg stay resident in cache.  With
+// a permutation the walk is in segment-sorted order (ids = the plan's sid, row =
+// perm[i]): consecutive entries then belong to the same segment, so the rows of
+// g and arg are fetched once from L2 and afterwards hit in L1, instead of one
+// random 512-byte L2 read per point.  No memset, no atomics.
 //
 // Replaces the ATen expressions in ScatterSumFunction.backward,
 // ScatterMeanFunction.backward and ScatterMaxFunction.backward
@@ -19,7 +22,7 @@ namespace texb {
 namespace {
 
 constexpr int kModeSum = 0, kModeMean = 1, kModeMax = 2;
-constexpr int kRowsPerStep = 8;
+constexpr int kRowsPerStep = 4;
 
 template <int VEC>
 struct Pack { float v[VEC]; };
@@ -60,71 +63,97 @@ __device__ __forceinline__ void store_stream(float* p, const Pack<VEC>& r) {
   }
 }
 
-template <int MODE, int VEC, int LPR>
-__global__ void __launch_bounds__(kCtaThreads)
-broadcast_back_kernel(const float* __restrict__ g, const int32_t* __restrict__ arg,
-                      const int32_t* __restrict__ ids, const int32_t* __restrict__ offsets,
-                      float* __restrict__ g_in, int64_t n, int C, int64_t m) {
-  constexpr int GPC = kCtaThreads / LPR;
-  const int lane_g = threadIdx.x & (LPR - 1);
-  const int group = threadIdx.x / LPR;
-  const int64_t r0 = (int64_t(blockIdx.x) * GPC + group) * kRowsPerStep;
-  if (r0 >= n) return;
+// Entries handled per step and per group of lanes; a group walks
+// kStepsPerGroup consecutive steps and fetches the ids / rows / counts of the
+// next step while it works on the current one.
+constexpr int kStepsPerGroup = 8;
 
-  int s[kRowsPerStep];
-  float den[kRowsPerStep];
+struct StepMeta {
+  int s[kRowsPerStep];    // segment of each entry, -1: write a zero row
+  int row[kRowsPerStep];  // row of g_in each entry writes, -1: nothing
+  int den[kRowsPerStep];  // row count of the segment (mean only)
+};
+
+template <int MODE>
+__device__ __forceinline__ void load_meta(StepMeta& mt, int64_t e0, const int32_t* __restrict__ ids,
+                                          const int32_t* __restrict__ perm,
+                                          const int32_t* __restrict__ offsets, int64_t n, int64_t m) {
 #pragma unroll
   for (int k = 0; k < kRowsPerStep; ++k) {
-    const int64_t i = r0 + k;
-    int v = (i < n) ? __ldg(ids + i) : -1;
-    s[k] = (v >= 0 && v < m) ? v : -1;  // ids outside the range get a zero row
+    const int64_t i = e0 + k;
+    const bool in = i < n;
+    const int v = in ? __ldg(ids + i) : -1;
+    mt.s[k] = (v >= 0 && v < m) ? v : -1;  // ids outside the range get a zero row
+    int r = in ? int(i) : -1;
+    if (perm != nullptr && in) {
+      const int pr = __ldg(perm + i);
+      r = (pr >= 0 && pr < n) ? pr : -1;  // a bad permutation entry writes nothing
+    }
+    mt.row[k] = r;
   }
   if constexpr (MODE == kModeMean) {
 #pragma unroll
     for (int k = 0; k < kRowsPerStep; ++k) {
-      den[k] = 1.f;
-      if (s[k] >= 0) den[k] = float(__ldg(offsets + s[k] + 1) - __ldg(offsets + s[k]));
-    }
-  }
-  for (int ch = lane_g * VEC; ch < C; ch += LPR * VEC) {
-    Pack<VEC> val[kRowsPerStep];
-#pragma unroll
-    for (int k = 0; k < kRowsPerStep; ++k) {
-      if (s[k] >= 0) {
-        val[k] = load_f<VEC>(g + int64_t(s[k]) * C + ch);
-        if constexpr (MODE == kModeMax) {
-          PackI<VEC> a = load_i<VEC>(arg + int64_t(s[k]) * C + ch);
-          const int64_t i = r0 + k;
-#pragma unroll
-          for (int q = 0; q < VEC; ++q)
-            if (int64_t(a.v[q]) != i) val[k].v[q] = 0.f;
-        }
-        if constexpr (MODE == kModeMean) {
-#pragma unroll
-          for (int q = 0; q < VEC; ++q) val[k].v[q] = __fdiv_rn(val[k].v[q], den[k]);
-        }
-      } else {
-#pragma unroll
-        for (int q = 0; q < VEC; ++q) val[k].v[q] = 0.f;
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < kRowsPerStep; ++k) {
-      const int64_t i = r0 + k;
-      if (i < n) store_stream<VEC>(g_in + i * C + ch, val[k]);
+      mt.den[k] = 1;
+      if (mt.s[k] >= 0) mt.den[k] = __ldg(offsets + mt.s[k] + 1) - __ldg(offsets + mt.s[k]);
     }
   }
 }
 
+template <int MODE, int VEC, int LPR>
+__global__ void __launch_bounds__(kCtaThreads, 4)
+broadcast_back_kernel(const float* __restrict__ g, const int32_t* __restrict__ arg,
+                      const int32_t* __restrict__ ids, const int32_t* __restrict__ perm,
+                      const int32_t* __restrict__ offsets, float* __restrict__ g_in, int64_t n, int C,
+                      int64_t m) {
+  constexpr int GPC = kCtaThreads / LPR;
+  const int lane_g = threadIdx.x & (LPR - 1);
+  const int group = threadIdx.x / LPR;
+  const int64_t e_begin = (int64_t(blockIdx.x) * GPC + group) * (kRowsPerStep * kStepsPerGroup);
+  if (e_begin >= n) return;
+  const int64_t e_end = min(e_begin + int64_t(kRowsPerStep * kStepsPerGroup), n);
+
+  StepMeta cur, nxt;
+  load_meta<MODE>(cur, e_begin, ids, perm, offsets, n, m);
+  for (int64_t e0 = e_begin; e0 < e_end; e0 += kRowsPerStep) {
+    const bool more = e0 + kRowsPerStep < e_end;
+    if (more) load_meta<MODE>(nxt, e0 + kRowsPerStep, ids, perm, offsets, n, m);
+    for (int ch = lane_g * VEC; ch < C; ch += LPR * VEC) {
+      Pack<VEC> val[kRowsPerStep];
+#pragma unroll
+      for (int k = 0; k < kRowsPerStep; ++k) {
+        if (cur.s[k] >= 0) {
+          val[k] = load_f<VEC>(g + int64_t(cur.s[k]) * C + ch);
+          if constexpr (MODE == kModeMax) {
+            PackI<VEC> a = load_i<VEC>(arg + int64_t(cur.s[k]) * C + ch);
+#pragma unroll
+            for (int q = 0; q < VEC; ++q)
+              if (a.v[q] != cur.row[k]) val[k].v[q] = 0.f;
+          }
+          if constexpr (MODE == kModeMean) divide_by_count<VEC>(val[k].v, cur.den[k]);
+        } else {
+#pragma unroll
+          for (int q = 0; q < VEC; ++q) val[k].v[q] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < kRowsPerStep; ++k) {
+        if (cur.row[k] >= 0) store_stream<VEC>(g_in + int64_t(cur.row[k]) * C + ch, val[k]);
+      }
+    }
+    if (more) cur = nxt;
+  }
+}
+
 template <int MODE, int VEC>
-int launch_lpr(int lpr, const float* g, const int32_t* arg, const int32_t* ids,
+int launch_lpr(int lpr, const float* g, const int32_t* arg, const int32_t* ids, const int32_t* perm,
                const int32_t* offsets, float* g_in, int64_t n, int C, int64_t m,
                cudaStream_t stream) {
   const int gpc = kCtaThreads / lpr;
-  const unsigned blocks = unsigned(ceil_div(n, int64_t(gpc) * kRowsPerStep));
+  const unsigned blocks = unsigned(ceil_div(n, int64_t(gpc) * kRowsPerStep * kStepsPerGroup));
 #define TEXB_LAUNCH(L)                                                                   \
   broadcast_back_kernel<MODE, VEC, L><<<blocks, kCtaThreads, 0, stream>>>(g, arg, ids,   \
-                                                                         offsets, g_in, n, C, m)
+                                                                         perm, offsets, g_in, n, C, m)
   switch (lpr) {
     case 1: TEXB_LAUNCH(1); break;
     case 2: TEXB_LAUNCH(2); break;
@@ -138,8 +167,8 @@ int launch_lpr(int lpr, const float* g, const int32_t* arg, const int32_t* ids,
 }
 
 template <int MODE>
-int launch_back(const float* g, const int32_t* arg, const int32_t* ids, const int32_t* offsets,
-                float* g_in, int64_t n, int C, int64_t m, cudaStream_t stream) {
+int launch_back(const float* g, const int32_t* arg, const int32_t* ids, const int32_t* perm,
+                const int32_t* offsets, float* g_in, int64_t n, int C, int64_t m, cudaStream_t stream) {
   if (n < 0 || m < 0 || C < 1) return fail(TEXB_ERR_INVALID_ARGUMENT, "backward: bad sizes");
   if (n == 0) return TEXB_OK;
   if (!g_in || !ids || (m > 0 && !g) || (MODE == kModeMax && m > 0 && !arg) ||
@@ -150,23 +179,23 @@ int launch_back(const float* g, const int32_t* arg, const int32_t* ids, const in
   const int vec = vec4 ? 4 : 1;
   int lpr = 1;
   while (lpr < C / vec && lpr < 32) lpr <<= 1;
-  if (vec4) return launch_lpr<MODE, 4>(lpr, g, arg, ids, offsets, g_in, n, C, m, stream);
-  return launch_lpr<MODE, 1>(lpr, g, arg, ids, offsets, g_in, n, C, m, stream);
+  if (vec4) return launch_lpr<MODE, 4>(lpr, g, arg, ids, perm, offsets, g_in, n, C, m, stream);
+  return launch_lpr<MODE, 1>(lpr, g, arg, ids, perm, offsets, g_in, n, C, m, stream);
 }
 
 }  // namespace
 
-int sum_backward_impl(const float* g, const int32_t* ids, float* g_in, int64_t n, int C, int64_t m,
-                      cudaStream_t stream) {
-  return launch_back<kModeSum>(g, nullptr, ids, nullptr, g_in, n, C, m, stream);
+int sum_backward_impl(const float* g, const int32_t* ids, const int32_t* perm, float* g_in, int64_t n,
+                      int C, int64_t m, cudaStream_t stream) {
+  return launch_back<kModeSum>(g, nullptr, ids, perm, nullptr, g_in, n, C, m, stream);
 }
-int mean_backward_impl(const float* g, const int32_t* ids, const int32_t* offsets, float* g_in,
-                       int64_t n, int C, int64_t m, cudaStream_t stream) {
-  return launch_back<kModeMean>(g, nullptr, ids, offsets, g_in, n, C, m, stream);
+int mean_backward_impl(const float* g, const int32_t* ids, const int32_t* perm, const int32_t* offsets,
+                       float* g_in, int64_t n, int C, int64_t m, cudaStream_t stream) {
+  return launch_back<kModeMean>(g, nullptr, ids, perm, offsets, g_in, n, C, m, stream);
 }
-int max_backward_impl(const float* g, const int32_t* arg, const int32_t* ids, float* g_in,
-                      int64_t n, int C, int64_t m, cudaStream_t stream) {
-  return launch_back<kModeMax>(g, arg, ids, nullptr, g_in, n, C, m, stream);
+int max_backward_impl(const float* g, const int32_t* arg, const int32_t* ids, const int32_t* perm,
+                      float* g_in, int64_t n, int C, int64_t m, cudaStream_t stream) {
+  return launch_back<kModeMax>(g, arg, ids, perm, nullptr, g_in, n, C, m, stream);
 }
 
 }  // namespace texb

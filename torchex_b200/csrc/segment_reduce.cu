@@ -240,11 +240,7 @@ __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __re
   float r[VEC];
 #pragma unroll
   for (int k = 0; k < VEC; ++k) r[k] = Op::template value<VEC>(x, k);
-  if (!Op::kIsMax && mean) {
-    const float c = float(cnt);
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) r[k] = __fdiv_rn(r[k], c);
-  }
+  if (!Op::kIsMax && mean) divide_by_count<VEC>(r, cnt);
   float* po = out + int64_t(seg) * C + ch;
   if constexpr (VEC == 4) {
     *reinterpret_cast<float4*>(po) = make_float4(r[0], r[1], r[2], r[3]);

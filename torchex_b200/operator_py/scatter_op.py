@@ -148,6 +148,28 @@ def _grad(g: torch.Tensor) -> torch.Tensor:
     return g.contiguous() if g.dtype == torch.float32 else g.float().contiguous()
 
 
+def _broadcast_back(mode: str, data: "ScatterData", g: torch.Tensor, arg) -> torch.Tensor:
+    """Gradient of the input rows: one fused pass in segment-sorted order (the
+    plan's ``sid`` / ``perm``), so each row of ``g`` is fetched once per segment."""
+    g = _grad(g)
+    n, c, m = data.unq_inv.numel(), g.shape[1], data.num_unq
+    g_input = g.new_empty((n, c))
+    lib = _native.lib()
+    perm = None if data.perm is None else data.perm.data_ptr()
+    with torch.cuda.device(g.device):
+        if mode == "sum":
+            st = lib.texb_scatter_sum_backward(g.data_ptr(), data.sid.data_ptr(), perm, g_input.data_ptr(),
+                                               n, c, m, _stream())
+        elif mode == "mean":
+            st = lib.texb_scatter_mean_backward(g.data_ptr(), data.sid.data_ptr(), perm, data.preSum.data_ptr(),
+                                                g_input.data_ptr(), n, c, m, _stream())
+        else:
+            st = lib.texb_scatter_max_backward(g.data_ptr(), arg.data_ptr(), data.sid.data_ptr(), perm,
+                                               g_input.data_ptr(), n, c, m, _stream())
+        _native.check(st, f"texb_scatter_{mode}_backward")
+    return g_input
+
+
 class ScatterSumFunction(Function):
 
     @staticmethod
@@ -158,21 +180,12 @@ class ScatterSumFunction(Function):
         num_total.  Returns float32 [num_unq, channel].
         """
         out, _ = _reduce(_native.OP_SUM, feats, data, want_arg=False)
-        ctx.save_for_backward(data.unq_inv)
-        ctx.num_unq = data.num_unq
+        ctx.plan = data
         return out
 
     @staticmethod
     def backward(ctx, g):
-        (unq_inv,) = ctx.saved_tensors
-        g = _grad(g)
-        n, c = unq_inv.numel(), g.shape[1]
-        g_input = g.new_empty((n, c))
-        with torch.cuda.device(g.device):
-            _native.check(_native.lib().texb_scatter_sum_backward(
-                g.data_ptr(), unq_inv.data_ptr(), g_input.data_ptr(), n, c, ctx.num_unq, _stream()),
-                "texb_scatter_sum_backward")
-        return g_input, None
+        return _broadcast_back("sum", ctx.plan, g, None), None
 
 
 class ScatterMeanFunction(Function):
@@ -182,21 +195,12 @@ class ScatterMeanFunction(Function):
         """out[s] = mean of the rows of feats whose id is s (one fused kernel;
         the divisor is the number of rows actually reduced)."""
         out, _ = _reduce(_native.OP_MEAN, feats, data, want_arg=False)
-        ctx.save_for_backward(data.unq_inv, data.preSum)
-        ctx.num_unq = data.num_unq
+        ctx.plan = data
         return out
 
     @staticmethod
     def backward(ctx, g):
-        unq_inv, pre_sum = ctx.saved_tensors
-        g = _grad(g)
-        n, c = unq_inv.numel(), g.shape[1]
-        g_input = g.new_empty((n, c))
-        with torch.cuda.device(g.device):
-            _native.check(_native.lib().texb_scatter_mean_backward(
-                g.data_ptr(), unq_inv.data_ptr(), pre_sum.data_ptr(), g_input.data_ptr(), n, c,
-                ctx.num_unq, _stream()), "texb_scatter_mean_backward")
-        return g_input, None
+        return _broadcast_back("mean", ctx.plan, g, None), None
 
 
 class ScatterMaxFunction(Function):
@@ -206,22 +210,15 @@ class ScatterMaxFunction(Function):
         """(out, arg): per-segment maximum and the row of feats that holds it
         (int32, lowest row on ties).  arg is not differentiable."""
         out, arg = _reduce(_native.OP_MAX, feats, data, want_arg=True)
-        ctx.save_for_backward(arg, data.unq_inv)
+        ctx.save_for_backward(arg)
         ctx.mark_non_differentiable(arg)
-        ctx.num_unq = data.num_unq
+        ctx.plan = data
         return out, arg
 
     @staticmethod
     def backward(ctx, g_out, g_arg):
-        arg, unq_inv = ctx.saved_tensors
-        g = _grad(g_out)
-        n, c = unq_inv.numel(), g.shape[1]
-        g_input = g.new_empty((n, c))
-        with torch.cuda.device(g.device):
-            _native.check(_native.lib().texb_scatter_max_backward(
-                g.data_ptr(), arg.data_ptr(), unq_inv.data_ptr(), g_input.data_ptr(), n, c,
-                ctx.num_unq, _stream()), "texb_scatter_max_backward")
-        return g_input, None
+        (arg,) = ctx.saved_tensors
+        return _broadcast_back("max", ctx.plan, g_out, arg), None
 
 
 class GetPreSumFunction(Function):
