@@ -174,7 +174,7 @@ def run_ours(args):
     def reduce(name):
         st = lib.texb_segment_reduce(ops[name], feat.data_ptr(), data.sid.data_ptr(), perm_ptr,
                                      data.preSum.data_ptr(), 0, data.balance.data_ptr(), data.balance.numel(),
-                                     n, c, m, outs[name].data_ptr(), arg.data_ptr(), ws.data_ptr(), ws.numel(),
+                                     n, c, m, outs[name].data_ptr(), arg.data_ptr(), 0, ws.data_ptr(), ws.numel(),
                                      stream)
         if st != 0:
             raise RuntimeError(_native.last_error())
@@ -316,7 +316,7 @@ def run_ours(args):
             "other_configs": configs,
             "device_wait_timeouts": timeouts,
         }
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -352,7 +352,7 @@ def other_configs(dev):
         for name, op in (("sum", _native.OP_SUM), ("mean", _native.OP_MEAN), ("max", _native.OP_MAX)):
             us = timed(lambda: lib.texb_segment_reduce(op, feat.data_ptr(), data.sid.data_ptr(), perm,
                                                        data.preSum.data_ptr(), 0, data.balance.data_ptr(),
-                                                       data.balance.numel(), n, c, m, out.data_ptr(), arg.data_ptr(),
+                                                       data.balance.numel(), n, c, m, out.data_ptr(), arg.data_ptr(), 0,
                                                        ws.data_ptr(), ws.numel(), stream), 50)
             res[name] = {"us": round(us, 2), "GBps": round(b[name] / us / 1e3, 1), "Mpoints_per_s": round(n / us, 1)}
         return res, data, arg
@@ -499,7 +499,7 @@ def run_reference(args):
         "Mpoints_per_s": round(3 * n_s / dt / 1e6, 2),
         "reference_cuda": ref_cuda,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 def reference_cuda_timing(n, c, m):
@@ -544,7 +544,21 @@ def reference_cuda_timing(n, c, m):
         return {"unavailable": f"{type(exc).__name__}: {exc}"}
 
 
+def emit(line: dict) -> None:
+    """The one JSON line, on the real stdout (see `main`)."""
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
+
+
+_REAL_STDOUT = 1
+
+
 def main():
+    # Libraries (NCCL's version banner, for one) print to stdout; keep stdout for the
+    # single JSON line by pointing fd 1 at stderr and writing the line to a saved copy.
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)

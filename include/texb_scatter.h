@@ -138,16 +138,18 @@ size_t texb_reduce_workspace_bytes(int64_t n, int channel);
  *                 long segments stay within 1e-6 + 1e-5*|x| of the exact sum.
  *   TEXB_OP_MEAN: that sum divided (IEEE fp32 division) by the row count.
  *   TEXB_OP_MAX : maximum and, in arg[num_segments, channel] (int32), the
- *                 feats row holding it; ties go to the lowest row; NaN never
- *                 wins (as in the reference, scatter_kernel.cu:146-151).
+ *                 feats row holding it plus arg_base (0 for a stand-alone call;
+ *                 the first global row of a shard when feats is one shard of a
+ *                 larger batch; "no row" stays -1); ties go to the lowest row;
+ *                 NaN never wins (as in the reference, scatter_kernel.cu:146-151).
  * No floating-point atomics: results are bit-reproducible run to run.
  * Limits: n < 2^31, channel >= 1. */
 int texb_segment_reduce(int op, const float* feats, const int32_t* sid,
                         const int32_t* perm, const int32_t* offsets,
                         int has_empty, const int32_t* balance, int balance_len,
                         int64_t n, int channel, int64_t num_segments,
-                        float* out, int32_t* arg, void* workspace,
-                        size_t workspace_bytes, void* stream);
+                        float* out, int32_t* arg, int32_t arg_base,
+                        void* workspace, size_t workspace_bytes, void* stream);
 
 /* texb_segment_reduce for callers that cannot allocate device memory.
  * No counterpart in the reference.
@@ -183,7 +185,7 @@ int texb_segment_reduce_static(int op, const float* feats, const int32_t* sid,
                                int has_empty, const int32_t* balance,
                                int balance_len, int64_t n, int channel,
                                int64_t num_segments, float* out, int32_t* arg,
-                               void* stream);
+                               int32_t arg_base, void* stream);
 
 /* Workspace for the two reference-shaped entry points below: room to expand
  * pre_sum back into per-row segment ids plus texb_reduce_workspace_bytes. */

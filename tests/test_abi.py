@@ -46,11 +46,11 @@ def test_header_cites_the_reference_interfaces():
 def test_bad_arguments_are_rejected_without_a_gpu():
     lib = _native.lib()
     assert lib.texb_version() >= 100
-    assert lib.texb_segment_reduce(9, None, None, None, None, 0, None, 0, 0, 1, 0, None, None, None, 0, None) == 1
+    assert lib.texb_segment_reduce(9, None, None, None, None, 0, None, 0, 0, 1, 0, None, None, 0, None, 0, None) == 1
     assert "unknown reduce op" in _native.last_error()
-    assert lib.texb_segment_reduce(0, None, None, None, None, 0, None, 0, -1, 1, 0, None, None, None, 0, None) == 1
-    assert lib.texb_segment_reduce(0, None, None, None, None, 0, None, 0, 1 << 31, 4, 5, None, None, None, 0, None) == 2
-    assert lib.texb_segment_reduce(0, None, None, None, None, 0, None, 0, 10, 4, 5, None, None, None, 0, None) == 1
+    assert lib.texb_segment_reduce(0, None, None, None, None, 0, None, 0, -1, 1, 0, None, None, 0, None, 0, None) == 1
+    assert lib.texb_segment_reduce(0, None, None, None, None, 0, None, 0, 1 << 31, 4, 5, None, None, 0, None, 0, None) == 2
+    assert lib.texb_segment_reduce(0, None, None, None, None, 0, None, 0, 10, 4, 5, None, None, 0, None, 0, None) == 1
     assert lib.texb_plan_build(None, 3, 0, 0, 1, None, None, None, None, None, 0, None) == 1
     assert "id_bytes" in _native.last_error()
     assert lib.texb_ids_inspect(None, 4, 5, None, None) == 1

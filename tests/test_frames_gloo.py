@@ -34,9 +34,10 @@ class _CpuData:
         self.ids, self.m = ids, cnts.numel()
 
 
-def _cpu_reduce(op, feats, data):
+def _cpu_reduce(op, feats, data, row_base=0):
     if op == "max":
         mx, arg = O.spec_scatter_max(feats, data.ids, data.m)
+        arg = np.where(arg >= 0, arg + row_base, arg).astype(np.int32)
         return torch.from_numpy(mx), torch.from_numpy(arg)
     s64, cnt = O.spec_scatter_sum_f64(feats, data.ids, data.m)
     if op == "mean":

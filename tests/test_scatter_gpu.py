@@ -252,3 +252,21 @@ def test_backward_entry_points_in_caller_order():
             want = O.spec_max_backward(grad, arg.cpu(), n)
         assert s1 == 0 and s2 == 0, _native.last_error()
         assert np.array_equal(a.cpu().numpy(), want) and np.array_equal(b.cpu().numpy(), want), mode
+
+
+def test_arg_base_offsets_reported_rows():
+    lib = _native.lib()
+    ids = torch.tensor([3, 0, 3, 1, 0], device=DEV)
+    cnt = torch.bincount(ids, minlength=5)          # segments 2 and 4 are empty
+    data = ScatterData(ids, cnt)
+    feat = torch.tensor([[1.0], [5.0], [2.0], [7.0], [5.0]], device=DEV).repeat(1, 4).contiguous()
+    out = torch.empty((5, 4), device=DEV)
+    arg = torch.empty((5, 4), dtype=torch.int32, device=DEV)
+    ws = torch.empty(lib.texb_reduce_workspace_bytes(5, 4), dtype=torch.uint8, device=DEV)
+    st = lib.texb_segment_reduce(_native.OP_MAX, feat.data_ptr(), data.sid.data_ptr(), data.perm.data_ptr(),
+                                 data.preSum.data_ptr(), 1, data.balance.data_ptr(), data.balance.numel(), 5, 4, 5,
+                                 out.data_ptr(), arg.data_ptr(), 1000, ws.data_ptr(), ws.numel(),
+                                 torch.cuda.current_stream().cuda_stream)
+    assert st == 0, _native.last_error()
+    assert arg[:, 0].tolist() == [1001, 1003, -1, 1002, -1]     # ties -> lowest row; empty stays -1
+    assert out[:, 0].tolist()[:2] == [5.0, 7.0]

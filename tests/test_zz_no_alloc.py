@@ -30,7 +30,7 @@ def _call(static, op, feat, data, m, out, arg, ws):
     stream = torch.cuda.current_stream().cuda_stream
     perm = None if data.perm is None else data.perm.data_ptr()
     head = (op, feat.data_ptr(), data.sid.data_ptr(), perm, data.preSum.data_ptr(), int(data.has_empty),
-            data.balance.data_ptr(), data.balance.numel(), n, c, m, out.data_ptr(), arg.data_ptr())
+            data.balance.data_ptr(), data.balance.numel(), n, c, m, out.data_ptr(), arg.data_ptr(), 0)
     if static:
         status = lib.texb_segment_reduce_static(*head, stream)
     else:
@@ -76,7 +76,7 @@ def test_static_scratch_entry_rejects_oversized_shapes():
     try:
         _native.tune_set("rows_per_cta", 64)  # 2 records per 64 rows: far beyond 4 MiB at this size
         n, c = 4_000_000, 128
-        status = lib.texb_segment_reduce_static(_native.OP_SUM, 1, 1, None, None, 0, None, 0, n, c, 10, 1, None, None)
+        status = lib.texb_segment_reduce_static(_native.OP_SUM, 1, 1, None, None, 0, None, 0, n, c, 10, 1, None, 0, None)
         assert status == 2  # TEXB_ERR_UNSUPPORTED, reported before any pointer is touched
         assert "scratch" in _native.last_error()
     finally:

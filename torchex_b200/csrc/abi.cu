@@ -19,11 +19,12 @@ int plan_build_impl(const void*, int, int64_t, int64_t, int, int32_t*, int32_t*,
 int get_pre_sum_impl(const int32_t*, int32_t*, int64_t, int64_t, cudaStream_t);
 size_t reduce_workspace_bytes_impl(int64_t, int);
 int segment_reduce_impl(int, const float*, const int32_t*, const int32_t*, const int32_t*, int,
-                        const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, void*, size_t,
-                        cudaStream_t);
+                        const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, int32_t, void*,
+                        size_t, cudaStream_t);
 int plan_balance_impl(const int32_t*, int64_t, int32_t*, int, cudaStream_t);
 int segment_reduce_static_impl(int, const float*, const int32_t*, const int32_t*, const int32_t*, int,
-                               const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, cudaStream_t);
+                               const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, int32_t,
+                               cudaStream_t);
 size_t static_scratch_bytes_impl();
 int device_status_impl(int*);
 int expand_offsets_impl(const int32_t*, int32_t*, int64_t, int64_t, cudaStream_t);
@@ -181,9 +182,10 @@ int texb_plan_balance(const int32_t* sid, int64_t n, int32_t* balance_out, int b
 int texb_segment_reduce(int op, const float* feats, const int32_t* sid, const int32_t* perm,
                         const int32_t* offsets, int has_empty, const int32_t* balance,
                         int balance_len, int64_t n, int channel, int64_t num_segments, float* out,
-                        int32_t* arg, void* workspace, size_t workspace_bytes, void* stream) {
+                        int32_t* arg, int32_t arg_base, void* workspace, size_t workspace_bytes,
+                        void* stream) {
   return segment_reduce_impl(op, feats, sid, perm, offsets, has_empty, balance, balance_len, n,
-                             channel, num_segments, out, arg, workspace, workspace_bytes,
+                             channel, num_segments, out, arg, arg_base, workspace, workspace_bytes,
                              static_cast<cudaStream_t>(stream));
 }
 
@@ -192,9 +194,10 @@ size_t texb_static_scratch_bytes(void) { return static_scratch_bytes_impl(); }
 int texb_segment_reduce_static(int op, const float* feats, const int32_t* sid, const int32_t* perm,
                                const int32_t* offsets, int has_empty, const int32_t* balance,
                                int balance_len, int64_t n, int channel, int64_t num_segments,
-                               float* out, int32_t* arg, void* stream) {
+                               float* out, int32_t* arg, int32_t arg_base, void* stream) {
   return segment_reduce_static_impl(op, feats, sid, perm, offsets, has_empty, balance, balance_len, n,
-                                    channel, num_segments, out, arg, static_cast<cudaStream_t>(stream));
+                                    channel, num_segments, out, arg, arg_base,
+                                    static_cast<cudaStream_t>(stream));
 }
 
 size_t texb_scatter_compat_workspace_bytes(int64_t num_total, int channel) {
@@ -222,7 +225,7 @@ static int compat_reduce(int op, const float* feats, const int32_t* pre_sum, flo
   if (st != TEXB_OK) return st;
   // The reference kernels write every row, including those of empty ranges.
   return segment_reduce_impl(op, feats, sid, nullptr, pre_sum, /*has_empty=*/1, nullptr, 0, num_total, channel,
-                             num_unq, out, arg, reinterpret_cast<void*>(base + sid_bytes),
+                             num_unq, out, arg, /*arg_base=*/0, reinterpret_cast<void*>(base + sid_bytes),
                              workspace_bytes - pad - sid_bytes, stream);
 }
 

@@ -235,7 +235,8 @@ __device__ __forceinline__ void load_state(const uint32_t* pa, const uint32_t* p
 template <class Op, int VEC>
 __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __restrict__ arg,
                                        int seg, int C, int ch, bool lane_on,
-                                       const typename Op::template State<VEC>& x, int cnt, bool mean) {
+                                       const typename Op::template State<VEC>& x, int cnt, bool mean,
+                                       int arg_base) {
   if (!lane_on) return;
   float r[VEC];
 #pragma unroll
@@ -251,11 +252,19 @@ __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __re
   if constexpr (Op::kIsMax) {
     int32_t* pa = arg + int64_t(seg) * C + ch;
     if constexpr (VEC == 4) {
-      *reinterpret_cast<int4*>(pa) = make_int4(Op::template index<VEC>(x, 0), Op::template index<VEC>(x, 1),
-                                               Op::template index<VEC>(x, 2), Op::template index<VEC>(x, 3));
+      int ix[VEC];
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {  // rows are reported relative to arg_base; "no row" stays -1
+        const int i = Op::template index<VEC>(x, k);
+        ix[k] = i < 0 ? i : i + arg_base;
+      }
+      *reinterpret_cast<int4*>(pa) = make_int4(ix[0], ix[1], ix[2], ix[3]);
     } else {
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) pa[k] = Op::template index<VEC>(x, k);
+      for (int k = 0; k < VEC; ++k) {
+        const int i = Op::template index<VEC>(x, k);
+        pa[k] = i < 0 ? i : i + arg_base;
+      }
     }
   }
 }
@@ -264,12 +273,12 @@ __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __re
 // the operator so that NaN / -inf rows keep the (-FLT_MAX, -1) answer.
 template <class Op, int VEC>
 __device__ __forceinline__ void store_single(float* __restrict__ out, int32_t* __restrict__ arg, int seg,
-                                             int C, int ch, bool lane_on, const float (&v)[VEC], int row) {
+                                             int C, int ch, bool lane_on, const float (&v)[VEC], int row, int arg_base) {
   if constexpr (Op::kIsMax) {
     typename Op::template State<VEC> x;
     Op::template init<VEC>(x);
     Op::template add<VEC>(x, v, row);
-    store_out<Op, VEC>(out, arg, seg, C, ch, lane_on, x, 1, false);
+    store_out<Op, VEC>(out, arg, seg, C, ch, lane_on, x, 1, false, arg_base);
   } else {
     if (!lane_on) return;
     float* po = out + int64_t(seg) * C + ch;
@@ -298,7 +307,7 @@ template <class Op, int VEC, int LPR>
 __device__ __forceinline__ void stitch_cta(const uint32_t* s_vec, const int* s_sid, const int* s_cnt,
                                            const unsigned* s_flag, float* __restrict__ out,
                                            int32_t* __restrict__ arg, Workspace ws, int C, int ch,
-                                           bool lane_on, int lane_g, int group, bool mean) {
+                                           bool lane_on, int lane_g, int group, bool mean, int arg_base) {
   using State = typename Op::template State<VEC>;
   constexpr int GPC = kCtaThreads / LPR;
   constexpr int CPS = LPR * VEC;
@@ -328,7 +337,7 @@ __device__ __forceinline__ void stitch_cta(const uint32_t* s_vec, const int* s_s
     }
     if (!(f & kOpenRight)) {
       if (!cur_open_left) {
-        store_out<Op, VEC>(out, arg, cur_sid, C, ch, lane_on, cur, cur_cnt, mean);
+        store_out<Op, VEC>(out, arg, cur_sid, C, ch, lane_on, cur, cur_cnt, mean, arg_base);
       } else {
         uint32_t* ga = ws.vec + rec * 2 * CPS + lane_g * VEC;
         store_state<Op, VEC>(ga, ga + CPS, cur);
@@ -380,7 +389,7 @@ __global__ void __launch_bounds__(kCtaThreads)
 segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict__ sid,
                       const int32_t* __restrict__ perm, float* __restrict__ out,
                       int32_t* __restrict__ arg, Workspace ws, int n, int C,
-                      Split sp, bool mean) {
+                      Split sp, bool mean, int arg_base) {
   using State = typename Op::template State<VEC>;
   constexpr int GPC = kCtaThreads / LPR;           // groups per CTA
   constexpr int CPS = LPR * VEC;                   // channels per slab
@@ -425,7 +434,7 @@ segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict
     auto close_run = [&](bool open_right) {
       const bool open_left = is_first && first_open_left;
       if (!open_left && !open_right) {
-        store_out<Op, VEC>(out, arg, cur_sid, C, ch, lane_on, acc, cnt, mean);
+        store_out<Op, VEC>(out, arg, cur_sid, C, ch, lane_on, acc, cnt, mean, arg_base);
       } else {
         const int slot = 2 * group + (open_right ? 1 : 0);
         uint32_t* pa = s_vec + slot * 2 * CPS + lane_g * VEC;
@@ -482,7 +491,7 @@ segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict
   }
   __syncthreads();
   stitch_cta<Op, VEC, LPR>(s_vec, s_sid, s_cnt, s_flag, out, arg, ws, C, ch, lane_on, lane_g,
-                           group, mean);
+                           group, mean, arg_base);
 }
 
 // ---- staged kernel --------------------------------------------------------------
@@ -554,7 +563,7 @@ __global__ void __launch_bounds__(kCtaThreads, 2)
 segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __restrict__ sid,
                              const int32_t* __restrict__ perm, float* __restrict__ out,
                              int32_t* __restrict__ arg, Workspace ws, int n, int C,
-                             Split sp, bool mean) {
+                             Split sp, bool mean, int arg_base) {
   constexpr int VEC = 4;
   using State = typename Op::template State<VEC>;
   constexpr int GPC = kCtaThreads / LPR;
@@ -709,7 +718,7 @@ segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __r
     auto close_run = [&](int sid_now, int cnt, bool open_right) {
       const bool open_left = is_first && first_open_left;
       if (!open_left && !open_right) {
-        store_out<Op, VEC>(out, arg, sid_now, C, ch, lane_on, acc, cnt, mean);
+        store_out<Op, VEC>(out, arg, sid_now, C, ch, lane_on, acc, cnt, mean, arg_base);
       } else {
         const int slot = 2 * group + (open_right ? 1 : 0);
         uint32_t* pa = s_vec + slot * 2 * CPS + lane_g * VEC;
@@ -726,7 +735,7 @@ segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __r
       const float v[VEC] = {t4.x, t4.y, t4.z, t4.w};
       if (single) {
         const int sid_now = __shfl_sync(gmask, sids_reg, lane_k, LPR);
-        store_single<Op, VEC>(out, arg, sid_now, C, ch, lane_on, v, row);
+        store_single<Op, VEC>(out, arg, sid_now, C, ch, lane_on, v, row, arg_base);
         is_first = false;
         run_start = q + 1;
       } else {
@@ -826,7 +835,7 @@ segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __r
   if constexpr (!BULK) cp_async_wait<0>();
   __syncthreads();
   stitch_cta<Op, VEC, LPR>(s_vec, s_sid, s_cnt, s_flag, out, arg, ws, C, ch, lane_on, lane_g,
-                           group, mean);
+                           group, mean, arg_base);
 }
 
 // ---- fix-up kernel --------------------------------------------------------------
@@ -838,7 +847,7 @@ segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __r
 template <class Op, int VEC, int LPR>
 __global__ void __launch_bounds__(kCtaThreads)
 segment_fixup_kernel(Workspace ws, float* __restrict__ out, int32_t* __restrict__ arg,
-                     int num_ctas, int C, bool mean) {
+                     int num_ctas, int C, bool mean, int arg_base) {
   using State = typename Op::template State<VEC>;
   constexpr int GPC = kCtaThreads / LPR;
   constexpr int CPS = LPR * VEC;
@@ -920,7 +929,7 @@ segment_fixup_kernel(Workspace ws, float* __restrict__ out, int32_t* __restrict_
       Op::template merge<VEC>(acc, x);
       cnt += s_cnt[g];
     }
-    store_out<Op, VEC>(out, arg, m0.x, C, ch, lane_on, acc, cnt, mean);
+    store_out<Op, VEC>(out, arg, m0.x, C, ch, lane_on, acc, cnt, mean, arg_base);
   }
 }
 
@@ -1039,6 +1048,7 @@ struct Call {
   cudaStream_t stream;
   const int32_t* balance;
   int balance_k;
+  int arg_base;
 };
 
 // Resident CTAs per SM of one kernel instantiation (asked once per process).
@@ -1073,7 +1083,7 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
 
   const dim3 grid(s.num_ctas, g.num_slabs);
   kernel<<<grid, kCtaThreads, dyn_smem, c.stream>>>(c.feats, c.sid, c.perm, c.out, c.arg, ws, c.n, c.C,
-                                                    s, c.mean);
+                                                    s, c.mean, c.arg_base);
   int st = check_launch("segment reduce kernel");
   if (st != TEXB_OK || s.num_ctas <= 1) return st;
 
@@ -1089,12 +1099,12 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, segment_fixup_kernel<Op, VEC, LPR>, ws, c.out, c.arg,
-                                       s.num_ctas, c.C, c.mean);
+                                       s.num_ctas, c.C, c.mean, c.arg_base);
     if (e != cudaSuccess)
       return fail(TEXB_ERR_CUDA, "segment_fixup_kernel launch: %s", cudaGetErrorString(e));
   } else {
     segment_fixup_kernel<Op, VEC, LPR><<<grid, kCtaThreads, 0, c.stream>>>(ws, c.out, c.arg, s.num_ctas,
-                                                                           c.C, c.mean);
+                                                                           c.C, c.mean, c.arg_base);
   }
   return check_launch("segment_fixup_kernel");
 }
@@ -1158,7 +1168,7 @@ int dispatch_layout(const Layout& g, const Call& c) {
 int segment_reduce_impl(int op, const float* feats, const int32_t* sid, const int32_t* perm,
                         const int32_t* offsets, int has_empty, const int32_t* balance,
                         int balance_len, int64_t n, int C, int64_t m, float* out, int32_t* arg,
-                        void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                        int32_t arg_base, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
   if (op != TEXB_OP_SUM && op != TEXB_OP_MEAN && op != TEXB_OP_MAX)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "unknown reduce op %d", op);
   if (n < 0 || m < 0 || C < 1)
@@ -1187,7 +1197,7 @@ int segment_reduce_impl(int op, const float* feats, const int32_t* sid, const in
   if (balance && balance_len < 2)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "balance table needs at least 2 entries");
   Call c = {feats, sid, perm, out, arg, workspace, workspace_bytes, int(n), C, op == TEXB_OP_MEAN, stream,
-            balance, balance ? balance_len - 1 : 0};
+            balance, balance ? balance_len - 1 : 0, int(arg_base)};
   if (op == TEXB_OP_MAX) return dispatch_layout<OpMax>(g, c);
   if (tuning().compensated) return dispatch_layout<OpSumComp>(g, c);
   return dispatch_layout<OpSumPlain>(g, c);
@@ -1218,7 +1228,7 @@ size_t static_scratch_bytes_impl() { return kStaticScratchBytes; }
 int segment_reduce_static_impl(int op, const float* feats, const int32_t* sid, const int32_t* perm,
                                const int32_t* offsets, int has_empty, const int32_t* balance,
                                int balance_len, int64_t n, int C, int64_t m, float* out, int32_t* arg,
-                               cudaStream_t stream) {
+                               int32_t arg_base, cudaStream_t stream) {
   constexpr int kMaxDevices = 64;
   static std::mutex mu;
   static void* device_ptr[kMaxDevices] = {};
@@ -1248,7 +1258,7 @@ int segment_reduce_static_impl(int op, const float* feats, const int32_t* sid, c
     scratch = device_ptr[dev];
   }
   return segment_reduce_impl(op, feats, sid, perm, offsets, has_empty, balance, balance_len, n, C, m, out,
-                             arg, scratch, kStaticScratchBytes, stream);
+                             arg, arg_base, scratch, kStaticScratchBytes, stream);
 }
 
 int device_status_impl(int* wait_timeouts) {

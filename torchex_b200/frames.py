@@ -107,7 +107,8 @@ def gather_shards(local: torch.Tensor, layout: ShardLayout, group=None) -> torch
 class FrameShard:
     """One rank's share of a multi-frame batch.
 
-    ``reduce`` is a callable ``(op, feats, data) -> tensor or (tensor, arg)``;
+    ``reduce`` is a callable ``(op, feats, data, row_base) -> tensor or (tensor, arg)``
+    whose ``arg`` already holds global rows (``row_base`` + local row);
     the default runs the CUDA operators of this package.  Tests on CPU ranks
     pass a stand-in so the bookkeeping is exercised without a GPU.
     """
@@ -132,17 +133,21 @@ class FrameShard:
         """Reduces this rank's points.  Returns the shard's ``[seg_count, C]``
         result (for ``max`` also ``arg`` holding GLOBAL row numbers), or with
         ``replicated=True`` the full ``[seg_total, C]`` tensors on every rank."""
-        res = self._reduce(op, feats, self.data)
+        res = self._reduce(op, feats, self.data, self.layout.row_base)
         if op == "max":
             out, arg = res
-            if self.layout.row_base:  # local rows -> global rows; -1 (no row) stays -1
-                arg.add_(arg.ge(0).to(arg.dtype).mul_(self.layout.row_base))
             if replicated:
                 return gather_shards(out, self.layout, group), gather_shards(arg, self.layout, group)
             return out, arg
         return gather_shards(res, self.layout, group) if replicated else res
 
 
-def _cuda_reduce(op: str, feats: torch.Tensor, data):
-    from .operator_py import scatter_max, scatter_mean, scatter_sum
-    return {"sum": scatter_sum, "mean": scatter_mean, "max": scatter_max}[op](feats, data)
+def _cuda_reduce(op: str, feats: torch.Tensor, data, row_base: int = 0):
+    """The CUDA operators; for ``max`` the kernel itself reports rows as
+    ``row_base + local row`` (global rows of the batch)."""
+    from .operator_py import scatter_mean, scatter_sum
+    from .operator_py.scatter_op import _reduce
+    from . import _native
+    if op == "max":
+        return _reduce(_native.OP_MAX, feats, data, want_arg=True, arg_base=row_base)
+    return {"sum": scatter_sum, "mean": scatter_mean}[op](feats, data)

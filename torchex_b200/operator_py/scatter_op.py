@@ -115,31 +115,47 @@ class ScatterData:
         self.max_cnt = max_cnt
         self.has_empty = num_empty > 0
         self.num_unq = m
+        self._perm_ptr = None if self.perm is None else self.perm.data_ptr()
+        self._workspaces = {}
 
 
-def _reduce(op: int, feats: torch.Tensor, data: ScatterData, want_arg: bool):
+def _reduce(op: int, feats: torch.Tensor, data: ScatterData, want_arg: bool, arg_base: int = 0):
     feats = _as_feats(feats)
     n, c = feats.shape
     if n != data.unq_inv.numel():
         raise RuntimeError(f"feats has {n} rows but ScatterData was built for {data.unq_inv.numel()}")
-    if feats.device != data.sid.device:
+    dev = feats.device
+    if dev != data.sid.device:
         raise RuntimeError("feats and ScatterData live on different devices")
     if c < 1:
         raise RuntimeError("feats needs at least one channel")
     lib = _native.lib()
     m = data.num_unq
-    out = feats.new_empty((m, c))
-    arg = torch.empty((m, c), dtype=torch.int32, device=feats.device) if want_arg else None
-    with torch.cuda.device(feats.device):
-        ws = _scratch(lib.texb_reduce_workspace_bytes(n, c), feats.device)
+    out = torch.empty((m, c), dtype=torch.float32, device=dev)
+    arg = torch.empty((m, c), dtype=torch.int32, device=dev) if want_arg else None
+    switch = torch.cuda.current_device() != dev.index
+    if switch:
+        prev = torch.cuda.current_device()
+        torch.cuda.set_device(dev)
+    try:
+        stream = _stream()
+        # The workspace is kept with the plan, one per (channel count, stream): calls on
+        # one stream are ordered, calls on different streams get different scratch.
+        key = (c, stream)
+        ws = data._workspaces.get(key)
+        if ws is None or ws.numel() < lib.texb_reduce_workspace_bytes(n, c):
+            ws = _scratch(lib.texb_reduce_workspace_bytes(n, c), dev)
+            data._workspaces[key] = ws
         _native.check(
-            lib.texb_segment_reduce(op, feats.data_ptr(), data.sid.data_ptr(),
-                                    None if data.perm is None else data.perm.data_ptr(),
+            lib.texb_segment_reduce(op, feats.data_ptr(), data.sid.data_ptr(), data._perm_ptr,
                                     data.preSum.data_ptr(), int(data.has_empty or n == 0),
                                     data.balance.data_ptr(), data.balance.numel(), n, c, m,
-                                    out.data_ptr(), None if arg is None else arg.data_ptr(),
-                                    ws.data_ptr(), ws.numel(), _stream()),
+                                    out.data_ptr(), None if arg is None else arg.data_ptr(), int(arg_base),
+                                    ws.data_ptr(), ws.numel(), stream),
             "texb_segment_reduce")
+    finally:
+        if switch:
+            torch.cuda.set_device(prev)
     return out, arg
 
 
@@ -245,7 +261,30 @@ class GetPreSumFunction(Function):
         return None
 
 
-scatter_sum = ScatterSumFunction.apply
-scatter_mean = ScatterMeanFunction.apply
-scatter_max = ScatterMaxFunction.apply
+def _wants_grad(feats) -> bool:
+    return torch.is_grad_enabled() and isinstance(feats, torch.Tensor) and feats.requires_grad
+
+
+def scatter_sum(feats: torch.Tensor, data: ScatterData) -> torch.Tensor:
+    """``ScatterSumFunction.apply`` (scatter_op.py:138 of the reference); when no
+    gradient is wanted the autograd node is skipped."""
+    if _wants_grad(feats):
+        return ScatterSumFunction.apply(feats, data)
+    return _reduce(_native.OP_SUM, feats, data, want_arg=False)[0]
+
+
+def scatter_mean(feats: torch.Tensor, data: ScatterData) -> torch.Tensor:
+    """``ScatterMeanFunction.apply`` (scatter_op.py:139 of the reference)."""
+    if _wants_grad(feats):
+        return ScatterMeanFunction.apply(feats, data)
+    return _reduce(_native.OP_MEAN, feats, data, want_arg=False)[0]
+
+
+def scatter_max(feats: torch.Tensor, data: ScatterData):
+    """``ScatterMaxFunction.apply`` (scatter_op.py:140 of the reference): ``(out, arg)``."""
+    if _wants_grad(feats):
+        return ScatterMaxFunction.apply(feats, data)
+    return _reduce(_native.OP_MAX, feats, data, want_arg=True)
+
+
 getPreSum = GetPreSumFunction.apply
