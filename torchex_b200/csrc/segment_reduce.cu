@@ -515,10 +515,18 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // Bulk (TMA) copy of one row slab, global -> this CTA's shared memory, signalling
 // an mbarrier with the byte count.  One destination CTA only; the source is always this
 // GPU's own memory.  Source, destination and size are multiples of 16 bytes.
+// `policy` is an L2 eviction policy: feature rows are read exactly once, so they
+// are marked evict-first and leave the L2 to the outputs, the plan and the records.
 __device__ __forceinline__ void bulk_copy_g2s(unsigned smem_dst, const void* gmem_src, unsigned bytes,
-                                              unsigned bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(smem_dst), "l"(gmem_src), "r"(bytes), "r"(bar) : "memory");
+                                              unsigned bar, unsigned long long policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+      ::"r"(smem_dst), "l"(gmem_src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
+}
+__device__ __forceinline__ unsigned long long l2_evict_first_policy() {
+  unsigned long long p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
 }
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -629,6 +637,7 @@ segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __r
         : reinterpret_cast<const float4*>(s_dyn) + threadIdx.x;
     const unsigned bar0 = unsigned(__cvta_generic_to_shared(&s_bar[BULK ? group * S : 0]));
     const float* slab_src = feats + blockIdx.y * CPS;
+    const unsigned long long stream_policy = BULK ? l2_evict_first_policy() : 0ull;
 
     // Tile metadata: lane_g holds positions t * T + r * LPR + lane_g (r < NREG).
     int cur_sid_r[NREG], cur_row_r[NREG], nxt_sid_r[NREG], nxt_row_r[NREG];
@@ -675,7 +684,7 @@ segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __r
             const unsigned bar = bar0 + stage * 8;
             if (k == 0) mbar_arrive_expect_tx(bar, unsigned(nv * row_bytes));
             bulk_copy_g2s(ring_addr + unsigned(stage * B + k) * kRowBytes, slab_src + int64_t(row) * C,
-                          unsigned(row_bytes), bar);
+                          unsigned(row_bytes), bar, stream_policy);
           }
         }
       } else {
