@@ -109,6 +109,15 @@ int texb_plan_build(const void* ids, int id_bytes, int64_t n,
 int texb_plan_balance(const int32_t* sid, int64_t n, int32_t* balance_out,
                       int balance_len, void* stream);
 
+/* rank_out[row] = index of the point inside its segment, counted in increasing
+ * row order, from a plan (sid, perm or NULL, offsets).  The deterministic form of
+ * TorchEx's ingroup_inds, whose kernel hands out the indices with an atomic
+ * counter in arrival order (torchex/src/ingroup_inds/ingroup_inds_kernel.cu:17-30):
+ * both give each segment the set {0 .. count-1}. */
+int texb_segment_rank(const int32_t* sid, const int32_t* perm,
+                      const int32_t* offsets, int64_t n, int64_t* rank_out,
+                      void* stream);
+
 /* Drop-in for getPreSum_launcher(unq_inv, preSum, num_total)
  * (torchex/src/scatter/scatter.cpp:18, scatter_kernel.cu:173-175): sorted
  * int32 ids -> pre_sum[num_unq + 1].  Unlike the reference every entry is

@@ -270,3 +270,25 @@ def test_arg_base_offsets_reported_rows():
     assert st == 0, _native.last_error()
     assert arg[:, 0].tolist() == [1001, 1003, -1, 1002, -1]     # ties -> lowest row; empty stays -1
     assert out[:, 0].tolist()[:2] == [5.0, 7.0]
+
+
+def test_ingroup_inds_and_gather_back():
+    from torchex_b200 import gather_back, ingroup_inds, ingroup_rank
+    ids, cnt = W.voxel_frame(60_000, seed=51)
+    d_ids = ids.to(DEV)
+    rank = ingroup_inds(d_ids)
+    assert rank.dtype == torch.int64 and rank.shape == ids.shape
+    # stable rank in row order: number of earlier rows with the same id
+    order = torch.argsort(ids, stable=True)
+    start = torch.cumsum(cnt, 0) - cnt
+    want = torch.empty_like(ids)
+    want[order] = torch.arange(ids.numel()) - start[ids[order]]
+    assert torch.equal(rank.cpu(), want)
+    # every group holds exactly 0 .. count-1 (the property the reference's atomic version has)
+    assert torch.equal(torch.bincount(ids * 0 + rank.cpu(), minlength=1)[:1], torch.tensor([cnt.numel()]))
+    data = ScatterData(d_ids, cnt.to(DEV))
+    assert torch.equal(ingroup_rank(data), rank)
+    vals = W.features(cnt.numel(), 24, 52).to(DEV)
+    assert torch.equal(gather_back(vals, data), vals[d_ids])
+    srt = torch.sort(ids).values.to(DEV)
+    assert torch.equal(gather_back(vals, ScatterData(srt, cnt.to(DEV))), vals[srt])

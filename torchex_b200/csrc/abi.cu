@@ -22,6 +22,7 @@ int segment_reduce_impl(int, const float*, const int32_t*, const int32_t*, const
                         const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, int32_t, void*,
                         size_t, cudaStream_t);
 int plan_balance_impl(const int32_t*, int64_t, int32_t*, int, cudaStream_t);
+int segment_rank_impl(const int32_t*, const int32_t*, const int32_t*, int64_t, int64_t*, cudaStream_t);
 int segment_reduce_static_impl(int, const float*, const int32_t*, const int32_t*, const int32_t*, int,
                                const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, int32_t,
                                cudaStream_t);
@@ -177,6 +178,11 @@ size_t texb_reduce_workspace_bytes(int64_t n, int channel) {
 int texb_plan_balance(const int32_t* sid, int64_t n, int32_t* balance_out, int balance_len,
                       void* stream) {
   return plan_balance_impl(sid, n, balance_out, balance_len, static_cast<cudaStream_t>(stream));
+}
+
+int texb_segment_rank(const int32_t* sid, const int32_t* perm, const int32_t* offsets, int64_t n,
+                      int64_t* rank_out, void* stream) {
+  return segment_rank_impl(sid, perm, offsets, n, rank_out, static_cast<cudaStream_t>(stream));
 }
 
 int texb_segment_reduce(int op, const float* feats, const int32_t* sid, const int32_t* perm,

@@ -119,6 +119,41 @@ class ScatterData:
         self._workspaces = {}
 
 
+def ingroup_rank(data: ScatterData) -> torch.Tensor:
+    """Index of every point inside its segment (int64 [num_total]), in increasing
+    row order, from an existing plan."""
+    n = data.unq_inv.numel()
+    out = torch.empty(n, dtype=torch.int64, device=data.sid.device)
+    with torch.cuda.device(out.device):
+        _native.check(_native.lib().texb_segment_rank(data.sid.data_ptr(), data._perm_ptr, data.preSum.data_ptr(),
+                                                      n, out.data_ptr(), _stream()), "texb_segment_rank")
+    return out
+
+
+def ingroup_inds(group_inds: torch.Tensor) -> torch.Tensor:
+    """Same call as TorchEx's ``ingroup_inds`` (torchex/operator_py/ingroup_inds_op.py:10-29):
+    for ids ``group_inds`` [N] returns each element's index inside its group.  The
+    reference numbers the members in the arrival order of an atomic counter; here
+    they are numbered in increasing position, so the result is reproducible."""
+    if not group_inds.is_cuda:
+        raise RuntimeError("group_inds must be a CUDAtensor")
+    flat = group_inds.reshape(-1)
+    if flat.numel() == 0:
+        return torch.empty_like(group_inds, dtype=torch.int64)
+    num_groups = int(flat.max()) + 1
+    data = ScatterData(flat, torch.empty(num_groups, dtype=torch.int64, device=flat.device))
+    return ingroup_rank(data).reshape(group_inds.shape)
+
+
+def gather_back(values: torch.Tensor, data: ScatterData) -> torch.Tensor:
+    """``values[unq_inv]``: broadcasts one row per segment ([num_unq, C]) back to
+    the points ([num_total, C]) -- the step that follows pooling in FSD / SST --
+    with the segment-order kernel of the sum backward."""
+    if values.ndim != 2 or values.shape[0] != data.num_unq:
+        raise RuntimeError(f"values must be [num_unq={data.num_unq}, C], got {tuple(values.shape)}")
+    return _broadcast_back("sum", data, values, None)
+
+
 def _reduce(op: int, feats: torch.Tensor, data: ScatterData, want_arg: bool, arg_base: int = 0):
     feats = _as_feats(feats)
     n, c = feats.shape
