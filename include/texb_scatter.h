@@ -58,7 +58,9 @@ int texb_device_status(int* wait_timeouts);
 
 /* Tuning knobs for experiments: "rows_per_cta" (0 = one wave of CTAs),
  * "staged" (0 register kernel, 1 cp.async ring, 2 bulk-copy ring),
- * "compensated" (1 = error-free sums), "fixup_pdl".
+ * "compensated" (1 = error-free sums), "fixup_pdl", "balanced", "end_cost_x4"
+ * (cost of closing a segment in quarter rows, used by texb_plan_balance),
+ * "l2_stream_hint" (1 = feature rows are copied with an L2 evict-first policy).
  * Process-wide; returns TEXB_ERR_INVALID_ARGUMENT for unknown keys or values
  * out of range.  texb_tune_get returns the current value or -1. */
 int texb_tune_set(const char* key, int value);

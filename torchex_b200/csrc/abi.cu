@@ -40,7 +40,7 @@ namespace {
 thread_local char t_error[512] = "";
 
 std::mutex g_tuning_mutex;
-Tuning g_tuning = {0, 2, 1, 1, 1, 8};
+Tuning g_tuning = {0, 2, 1, 1, 1, 8, 0};
 bool g_tuning_env_read = false;
 
 int env_int(const char* name, int fallback) {
@@ -75,6 +75,11 @@ bool set_knob(Tuning& t, const char* key, int value) {
     t.balanced = value;
     return true;
   }
+  if (!std::strcmp(key, "l2_stream_hint")) {
+    if (value != 0 && value != 1) return false;
+    t.l2_stream_hint = value;
+    return true;
+  }
   if (!std::strcmp(key, "end_cost_x4")) {
     if (value < 0 || value > 1024) return false;
     t.end_cost_x4 = value;
@@ -92,6 +97,7 @@ void read_env_locked() {
   set_knob(g_tuning, "fixup_pdl", env_int("TEXB_FIXUP_PDL", g_tuning.fixup_pdl));
   set_knob(g_tuning, "balanced", env_int("TEXB_BALANCED", g_tuning.balanced));
   set_knob(g_tuning, "end_cost_x4", env_int("TEXB_END_COST_X4", g_tuning.end_cost_x4));
+  set_knob(g_tuning, "l2_stream_hint", env_int("TEXB_L2_STREAM_HINT", g_tuning.l2_stream_hint));
 }
 }  // namespace
 
@@ -143,6 +149,7 @@ int texb_tune_get(const char* key) {
   if (!std::strcmp(key, "fixup_pdl")) return t.fixup_pdl;
   if (!std::strcmp(key, "balanced")) return t.balanced;
   if (!std::strcmp(key, "end_cost_x4")) return t.end_cost_x4;
+  if (!std::strcmp(key, "l2_stream_hint")) return t.l2_stream_hint;
   return -1;
 }
 

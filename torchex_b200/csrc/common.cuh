@@ -24,6 +24,7 @@ struct Tuning {
   int fixup_pdl;     // 1: launch the fix-up kernel with programmatic dependent launch
   int balanced;      // 1: use the plan's balance table to cut the rows by estimated cost
   int end_cost_x4;   // cost of closing a segment, in quarter rows, for that table
+  int l2_stream_hint;  // 1: bulk copies of feature rows carry an L2 evict-first policy
 };
 Tuning tuning();
 
