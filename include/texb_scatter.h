@@ -111,6 +111,36 @@ int texb_plan_build(const void* ids, int id_bytes, int64_t n,
 int texb_plan_balance(const int32_t* sid, int64_t n, int32_t* balance_out,
                       int balance_len, void* stream);
 
+/* ---- plan straight from keys (the caller's torch.unique step) ----------------
+ * TorchEx's callers obtain unq_inv / unq_cnts with
+ * torch.unique(coors, dim=0, return_inverse=True, return_counts=True) before
+ * they build ScatterData (torchex/operator_py/scatter_op.py:7-21 takes both as
+ * inputs).  These two calls fold that step into the plan builder: keys[n]
+ * (int32 or int64, any order, values in [0, key_bound), key_bound <= 2^31;
+ * typically the linearised voxel coordinate) are sorted once by the same radix
+ * sort, and the dense ids, counts, offsets and permutation all come out of that
+ * one sort.  Dense ids follow increasing key, as torch.unique orders them.
+ *
+ * Call texb_unique_count, read stats_dev[0] (= number of distinct keys M) on
+ * the host to size the outputs, then texb_unique_fill with the SAME workspace
+ * (texb_unique_workspace_bytes(n)), untouched in between.
+ *   texb_unique_count: sorted != 0 means keys are already non-decreasing (no
+ *     sort runs, perm_out is not written and may be NULL).
+ *   texb_unique_fill: perm = perm_out of the first call (NULL if sorted);
+ *     writes sid_out[n] (dense id per sorted position), offsets_out[M + 1],
+ *     unq_inv_out[n] (dense id per row, the "inverse"), unique_keys_out[M], and
+ *     plan_stats_dev[0..3] as texb_plan_build does ([0] largest count). */
+size_t texb_unique_workspace_bytes(int64_t n);
+int texb_unique_count(const void* keys, int key_bytes, int64_t n,
+                      int64_t key_bound, int sorted, int32_t* sorted_keys_out,
+                      int32_t* perm_out, int32_t* stats_dev, void* workspace,
+                      size_t workspace_bytes, void* stream);
+int texb_unique_fill(const int32_t* sorted_keys, const int32_t* perm, int64_t n,
+                     int64_t num_segments, int32_t* sid_out,
+                     int32_t* offsets_out, int32_t* unq_inv_out,
+                     int32_t* unique_keys_out, int32_t* plan_stats_dev,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
 /* rank_out[row] = index of the point inside its segment, counted in increasing
  * row order, from a plan (sid, perm or NULL, offsets).  The deterministic form of
  * TorchEx's ingroup_inds, whose kernel hands out the indices with an atomic

@@ -334,3 +334,32 @@ def test_config5_multi_frame_full_size_properties():
     sums_of_means = shard.scatter("sum", gather_back(mean, data))
     assert torch.allclose(sums_of_means, mean * cnt[:, None], rtol=1e-5, atol=1e-6)
     assert _native.device_wait_timeouts() == 0
+
+
+@pytest.mark.parametrize("pre_sorted", [False, True])
+def test_plan_from_coords_matches_torch_unique(pre_sorted):
+    g = torch.Generator().manual_seed(61)
+    coors = torch.stack([torch.randint(0, 4, (50_000,), generator=g), torch.randint(0, 40, (50_000,), generator=g),
+                         torch.randint(0, 37, (50_000,), generator=g)], 1)
+    if pre_sorted:
+        key = (coors[:, 0] * 40 + coors[:, 1]) * 37 + coors[:, 2]
+        coors = coors[torch.argsort(key)]
+    uniq, inv, cnt = torch.unique(coors, dim=0, return_inverse=True, return_counts=True)
+    for grid in (None, [4, 40, 37], [5, 64, 64]):
+        data = ScatterData.from_coords(coors.to(DEV), grid)
+        assert data.num_unq == uniq.shape[0] and data.is_sorted == pre_sorted
+        assert torch.equal(data.unq_inv.cpu().long(), inv)
+        assert torch.equal(data.unq_cnts.cpu().reshape(-1), cnt)
+        assert torch.equal(data.unq_coors.cpu(), uniq)
+        assert data.max_cnt == int(cnt.max())
+    feat = W.features(50_000, 32, 62)
+    ref = ScatterData(inv.to(DEV), cnt.to(DEV))
+    for fn in (scatter_sum, scatter_mean):
+        assert torch.equal(fn(feat.to(DEV), data), fn(feat.to(DEV), ref))
+    a, b = scatter_max(feat.to(DEV), data), scatter_max(feat.to(DEV), ref)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    keys = torch.tensor([7, 7, 2, 2_000_000_000, 2, 7], device=DEV)
+    d2 = ScatterData.from_keys(keys)
+    assert d2.unq_keys.tolist() == [2, 7, 2_000_000_000] and d2.unq_inv.tolist() == [1, 1, 0, 2, 0, 1]
+    with pytest.raises(ValueError):
+        ScatterData.from_keys(torch.tensor([-1, 3], device=DEV))

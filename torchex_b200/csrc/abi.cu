@@ -22,6 +22,11 @@ int segment_reduce_impl(int, const float*, const int32_t*, const int32_t*, const
                         const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, int32_t, void*,
                         size_t, cudaStream_t);
 int plan_balance_impl(const int32_t*, int64_t, int32_t*, int, cudaStream_t);
+size_t unique_workspace_bytes_impl(int64_t);
+int unique_count_impl(const void*, int, int64_t, int64_t, int, int32_t*, int32_t*, int32_t*, void*, size_t,
+                      cudaStream_t);
+int unique_fill_impl(const int32_t*, const int32_t*, int64_t, int64_t, int32_t*, int32_t*, int32_t*, int32_t*,
+                     int32_t*, void*, size_t, cudaStream_t);
 int segment_rank_impl(const int32_t*, const int32_t*, const int32_t*, int64_t, int64_t*, cudaStream_t);
 int segment_reduce_static_impl(int, const float*, const int32_t*, const int32_t*, const int32_t*, int,
                                const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, int32_t,
@@ -185,6 +190,23 @@ size_t texb_reduce_workspace_bytes(int64_t n, int channel) {
 int texb_plan_balance(const int32_t* sid, int64_t n, int32_t* balance_out, int balance_len,
                       void* stream) {
   return plan_balance_impl(sid, n, balance_out, balance_len, static_cast<cudaStream_t>(stream));
+}
+
+size_t texb_unique_workspace_bytes(int64_t n) { return unique_workspace_bytes_impl(n); }
+
+int texb_unique_count(const void* keys, int key_bytes, int64_t n, int64_t key_bound, int sorted,
+                      int32_t* sorted_keys_out, int32_t* perm_out, int32_t* stats_dev, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+  return unique_count_impl(keys, key_bytes, n, key_bound, sorted, sorted_keys_out, perm_out, stats_dev,
+                           workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int texb_unique_fill(const int32_t* sorted_keys, const int32_t* perm, int64_t n, int64_t num_segments,
+                     int32_t* sid_out, int32_t* offsets_out, int32_t* unq_inv_out, int32_t* unique_keys_out,
+                     int32_t* plan_stats_dev, void* workspace, size_t workspace_bytes, void* stream) {
+  return unique_fill_impl(sorted_keys, perm, n, num_segments, sid_out, offsets_out, unq_inv_out,
+                          unique_keys_out, plan_stats_dev, workspace, workspace_bytes,
+                          static_cast<cudaStream_t>(stream));
 }
 
 int texb_segment_rank(const int32_t* sid, const int32_t* perm, const int32_t* offsets, int64_t n,

@@ -412,6 +412,179 @@ int plan_build_impl(const void* ids, int id_bytes, int64_t n, int64_t m, int sor
   return run_offsets<int32_t>(sid_out, nullptr, offsets_out, n, m, plan_stats_dev, stream);
 }
 
+namespace {
+
+// ---- dense ids from arbitrary keys (the torch.unique step) ----------------------------
+// Sorted keys -> run starts -> dense ids.  Tile = kSortTile consecutive sorted
+// positions; thread t of a tile owns 16 consecutive positions.
+
+__global__ void __launch_bounds__(kSortThreads)
+unique_tile_count_kernel(const int32_t* __restrict__ keys, int n, uint32_t* __restrict__ tile_counts) {
+  __shared__ uint32_t s_warp[kSortWarps];
+  const int64_t p0 = int64_t(blockIdx.x) * kSortTile + int64_t(threadIdx.x) * kSortItems;
+  uint32_t c = 0;
+#pragma unroll 4
+  for (int k = 0; k < kSortItems; ++k) {
+    const int64_t p = p0 + k;
+    if (p < n) c += (p == 0) || (keys[p] != keys[p - 1]);
+  }
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+  if ((threadIdx.x & 31) == 0) s_warp[threadIdx.x >> 5] = c;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t t = 0;
+    for (int w = 0; w < kSortWarps; ++w) t += s_warp[w];
+    tile_counts[blockIdx.x] = t;
+  }
+}
+
+// After the exclusive scan of tile_counts: total number of distinct keys.
+__global__ void unique_total_kernel(const uint32_t* __restrict__ tile_base, const int32_t* __restrict__ keys,
+                                    int n, int num_tiles, int32_t* stats) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  // base of the last tile + its own count (recounted: the scan overwrote it)
+  uint32_t c = 0;
+  for (int64_t p = int64_t(num_tiles - 1) * kSortTile; p < n; ++p) c += (p == 0) || (keys[p] != keys[p - 1]);
+  stats[0] = int32_t(tile_base[num_tiles - 1] + c);
+}
+
+__global__ void __launch_bounds__(kSortThreads)
+unique_fill_kernel(const int32_t* __restrict__ keys, const int32_t* __restrict__ perm, int n, int m,
+                   const uint32_t* __restrict__ tile_base, int32_t* __restrict__ sid,
+                   int32_t* __restrict__ offsets, int32_t* __restrict__ unq_inv,
+                   int32_t* __restrict__ unique_keys) {
+  __shared__ uint32_t s_warp[kSortWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t p0 = int64_t(blockIdx.x) * kSortTile + int64_t(threadIdx.x) * kSortItems;
+  uint32_t flags = 0;
+#pragma unroll 4
+  for (int k = 0; k < kSortItems; ++k) {
+    const int64_t p = p0 + k;
+    if (p < n && ((p == 0) || (keys[p] != keys[p - 1]))) flags |= 1u << k;
+  }
+  const uint32_t mine = __popc(flags);
+  uint32_t incl = mine;
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) s_warp[warp] = incl;
+  __syncthreads();
+  uint32_t before = tile_base[blockIdx.x] + incl - mine;
+  for (int w = 0; w < warp; ++w) before += s_warp[w];
+  // `before` = number of run starts in front of this thread's first position
+  int32_t id = int32_t(before) - 1;
+  for (int k = 0; k < kSortItems; ++k) {
+    const int64_t p = p0 + k;
+    if (p >= n) break;
+    if (flags & (1u << k)) {
+      ++id;
+      if (id < m) {
+        offsets[id] = int32_t(p);
+        unique_keys[id] = keys[p];
+      }
+    }
+    sid[p] = id;
+    const int row = perm ? perm[p] : int(p);
+    if (row >= 0 && row < n) unq_inv[row] = id;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) offsets[m] = n;
+}
+
+__global__ void narrow_keys_kernel(const int64_t* __restrict__ in, int32_t* __restrict__ out, int64_t n) {
+  const int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
+  if (i < n) out[i] = clamp_id<int64_t>(in[i]);
+}
+
+struct UniqueWorkspace {
+  SortWorkspace sort;
+  uint32_t* tile_counts;
+  size_t bytes;
+};
+
+UniqueWorkspace carve_unique_workspace(void* ws, int64_t n) {
+  UniqueWorkspace u;
+  u.sort = carve_sort_workspace(ws, n);
+  const size_t tiles = size_t(ceil_div(n > 0 ? n : 1, kSortTile));
+  uintptr_t base = reinterpret_cast<uintptr_t>(u.sort.tmp_keys) + align_up(u.sort.bytes, 256);
+  u.tile_counts = reinterpret_cast<uint32_t*>(base);
+  u.bytes = align_up(u.sort.bytes, 256) + align_up(tiles * sizeof(uint32_t), 256) + 256;
+  return u;
+}
+
+}  // namespace
+
+size_t unique_workspace_bytes_impl(int64_t n) { return n > 0 ? carve_unique_workspace(nullptr, n).bytes : 512; }
+
+int unique_count_impl(const void* keys, int key_bytes, int64_t n, int64_t key_bound, int sorted,
+                      int32_t* sorted_keys, int32_t* perm, int32_t* stats_dev, void* workspace,
+                      size_t workspace_bytes, cudaStream_t stream) {
+  if (key_bytes != 4 && key_bytes != 8)
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "key_bytes must be 4 or 8, got %d", key_bytes);
+  if (n < 0 || key_bound < 0 || !stats_dev || (n > 0 && (!keys || !sorted_keys)))
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "unique_count: bad pointer or size");
+  if (n > INT_MAX - 65536 || key_bound > INT_MAX)
+    return fail(TEXB_ERR_UNSUPPORTED, "unique_count: n and the keys must be below 2^31");
+  if (!sorted && n > 0 && !perm)
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "unique_count: perm is required for unsorted keys");
+  cudaError_t e = cudaMemsetAsync(stats_dev, 0, 4 * sizeof(int32_t), stream);
+  if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  if (n == 0) return TEXB_OK;
+  UniqueWorkspace uw = carve_unique_workspace(workspace, n);
+  const size_t pad = reinterpret_cast<uintptr_t>(uw.sort.tmp_keys) - reinterpret_cast<uintptr_t>(workspace);
+  if (!workspace || workspace_bytes + 256 < uw.bytes + pad)
+    return fail(TEXB_ERR_WORKSPACE, "unique workspace: need %zu bytes, got %zu", uw.bytes, workspace_bytes);
+  if (sorted) {
+    if (key_bytes == 8) {
+      narrow_keys_kernel<<<unsigned(ceil_div(n, 256)), 256, 0, stream>>>(static_cast<const int64_t*>(keys),
+                                                                        sorted_keys, n);
+    } else if (static_cast<const void*>(sorted_keys) != keys) {
+      e = cudaMemcpyAsync(sorted_keys, keys, size_t(n) * sizeof(int32_t), cudaMemcpyDeviceToDevice, stream);
+      if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "cudaMemcpyAsync: %s", cudaGetErrorString(e));
+    }
+  } else {
+    if (static_cast<const void*>(sorted_keys) == keys)
+      return fail(TEXB_ERR_INVALID_ARGUMENT, "unique_count: sorted_keys may not alias unsorted keys");
+    int st = (key_bytes == 4) ? run_sort<int32_t>(keys, n, key_bound, sorted_keys, perm, uw.sort, stream)
+                              : run_sort<int64_t>(keys, n, key_bound, sorted_keys, perm, uw.sort, stream);
+    if (st != TEXB_OK) return st;
+  }
+  const int tiles = int(ceil_div(n, kSortTile));
+  unique_tile_count_kernel<<<tiles, kSortThreads, 0, stream>>>(sorted_keys, int(n), uw.tile_counts);
+  exclusive_scan_kernel<<<1, 1024, 0, stream>>>(uw.tile_counts, tiles);
+  unique_total_kernel<<<1, 32, 0, stream>>>(uw.tile_counts, sorted_keys, int(n), tiles, stats_dev);
+  return check_launch("unique count kernels");
+}
+
+int unique_fill_impl(const int32_t* sorted_keys, const int32_t* perm, int64_t n, int64_t m, int32_t* sid,
+                     int32_t* offsets, int32_t* unq_inv, int32_t* unique_keys, int32_t* plan_stats_dev,
+                     void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  if (n < 0 || m < 0 || !offsets || !plan_stats_dev ||
+      (n > 0 && (!sorted_keys || !sid || !unq_inv || !unique_keys)))
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "unique_fill: bad pointer or size");
+  if (n > INT_MAX - 65536) return fail(TEXB_ERR_UNSUPPORTED, "unique_fill: n must be below 2^31 - 65536");
+  cudaError_t e = cudaMemsetAsync(plan_stats_dev, 0, 4 * sizeof(int32_t), stream);
+  if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  if (n == 0) {
+    e = cudaMemsetAsync(offsets, 0, size_t(m + 1) * sizeof(int32_t), stream);
+    if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    return TEXB_OK;
+  }
+  UniqueWorkspace uw = carve_unique_workspace(workspace, n);
+  const size_t pad = reinterpret_cast<uintptr_t>(uw.sort.tmp_keys) - reinterpret_cast<uintptr_t>(workspace);
+  if (!workspace || workspace_bytes + 256 < uw.bytes + pad)
+    return fail(TEXB_ERR_WORKSPACE, "unique workspace: need %zu bytes, got %zu", uw.bytes, workspace_bytes);
+  const int tiles = int(ceil_div(n, kSortTile));
+  unique_fill_kernel<<<tiles, kSortThreads, 0, stream>>>(sorted_keys, perm, int(n), int(m), uw.tile_counts, sid,
+                                                         offsets, unq_inv, unique_keys);
+  int st = check_launch("unique_fill_kernel");
+  if (st != TEXB_OK || m == 0) return st;
+  int64_t blocks = ceil_div(m, 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  plan_stats_kernel<<<unsigned(blocks), 256, 0, stream>>>(offsets, int(m), plan_stats_dev);
+  return check_launch("plan_stats_kernel");
+}
+
 int plan_balance_impl(const int32_t* sid, int64_t n, int32_t* table, int table_len, cudaStream_t stream) {
   if (n < 0 || !table || table_len < 2 || (n > 0 && !sid))
     return fail(TEXB_ERR_INVALID_ARGUMENT, "plan_balance: bad pointer or size");

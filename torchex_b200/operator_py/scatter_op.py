@@ -119,6 +119,106 @@ class ScatterData:
         self._workspaces = {}
 
 
+def _plan_from_keys(cls, keys: torch.Tensor):
+    """Shared body of ScatterData.from_keys / from_coords."""
+    if not keys.is_cuda:
+        raise RuntimeError("keys must be a CUDAtensor")
+    keys = keys.reshape(-1)
+    if keys.dtype not in (torch.int32, torch.int64):
+        keys = keys.long()
+    keys = keys.contiguous()
+    n, dev, lib = keys.numel(), keys.device, _native.lib()
+    self = cls.__new__(cls)
+    with torch.cuda.device(dev):
+        stats = torch.empty(4, dtype=torch.int32, device=dev)
+        _native.check(lib.texb_ids_inspect(keys.data_ptr(), keys.element_size(), n, stats.data_ptr(), _stream()),
+                      "texb_ids_inspect")
+        is_sorted, k_min, k_max, _ = (int(v) for v in stats.cpu())
+        if n > 0 and (k_min < 0 or k_max >= 2 ** 31 - 1):
+            raise ValueError(f"keys must lie in [0, 2^31 - 1); got [{k_min}, {k_max}]")
+        bound = k_max + 1 if n > 0 else 1
+        ws = _scratch(lib.texb_unique_workspace_bytes(n), dev)
+        sorted_keys = torch.empty(n, dtype=torch.int32, device=dev)
+        perm = None if is_sorted else torch.empty(n, dtype=torch.int32, device=dev)
+        _native.check(lib.texb_unique_count(keys.data_ptr(), keys.element_size(), n, bound, is_sorted,
+                                            sorted_keys.data_ptr(), None if perm is None else perm.data_ptr(),
+                                            stats.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
+                      "texb_unique_count")
+        m = int(stats.cpu()[0])
+        self.sid = torch.empty(n, dtype=torch.int32, device=dev)
+        self.preSum = torch.empty(m + 1, dtype=torch.int32, device=dev)
+        self.unq_inv = torch.empty(n, dtype=torch.int32, device=dev)
+        self.unq_keys = torch.empty(m, dtype=torch.int32, device=dev)
+        plan_stats = torch.empty(4, dtype=torch.int32, device=dev)
+        _native.check(lib.texb_unique_fill(sorted_keys.data_ptr(), None if perm is None else perm.data_ptr(), n, m,
+                                           self.sid.data_ptr(), self.preSum.data_ptr(), self.unq_inv.data_ptr(),
+                                           self.unq_keys.data_ptr(), plan_stats.data_ptr(), ws.data_ptr(),
+                                           ws.numel(), _stream()), "texb_unique_fill")
+        self.perm = perm
+        self.is_sorted = bool(is_sorted)
+        self.balance = torch.empty(_native.BALANCE_PIECES + 1, dtype=torch.int32, device=dev)
+        _native.check(lib.texb_plan_balance(self.sid.data_ptr(), n, self.balance.data_ptr(),
+                                            self.balance.numel(), _stream()), "texb_plan_balance")
+        self.unq_cnts = (self.preSum[1:] - self.preSum[:-1]).long().unsqueeze(-1)
+        self.max_cnt = int(plan_stats.cpu()[0])
+    self.has_empty = False
+    self.num_unq = m
+    self._perm_ptr = None if self.perm is None else self.perm.data_ptr()
+    self._workspaces = {}
+    return self
+
+
+def _from_keys(cls, keys: torch.Tensor):
+    """Plan from arbitrary integer keys in [0, 2^31 - 1) (for instance linearised
+    voxel coordinates): replaces ``torch.unique(keys, return_inverse=True,
+    return_counts=True)`` followed by ``ScatterData(inverse, counts)`` with one
+    device sort.  ``unq_inv`` (dense id per point, ordered by key like
+    ``torch.unique``), ``unq_cnts`` and ``unq_keys`` are attributes of the result."""
+    return _plan_from_keys(cls, keys)
+
+
+def _from_coords(cls, coors: torch.Tensor, grid_size=None):
+    """Plan from integer voxel coordinates ``coors`` [N, D]: replaces
+    ``torch.unique(coors, dim=0, return_inverse=True, return_counts=True)``.
+    ``grid_size`` (D extents) avoids a device-to-host copy of the coordinate
+    maxima; the product of the extents must stay below 2^31.  Dense ids follow the
+    lexicographic order of the coordinate rows, as ``torch.unique(dim=0)`` does;
+    ``unq_coors`` [num_unq, D] holds the distinct rows."""
+    if coors.ndim != 2:
+        raise RuntimeError(f"coors must be [N, D], got {tuple(coors.shape)}")
+    d = coors.shape[1]
+    c64 = coors.long()
+    if grid_size is None:
+        if coors.shape[0] == 0:
+            grid_size = [1] * d
+        else:
+            if int(c64.min()) < 0:
+                raise ValueError("coors must be non-negative")
+            grid_size = [int(v) + 1 for v in c64.max(0).values.cpu()]
+    if len(grid_size) != d:
+        raise ValueError("grid_size needs one extent per coordinate column")
+    total = 1
+    for g in grid_size:
+        total *= int(g)
+    if total >= 2 ** 31 - 1:
+        raise ValueError(f"grid of {total} cells does not fit the 31-bit key space")
+    key = torch.zeros(coors.shape[0], dtype=torch.int64, device=coors.device)
+    for j in range(d):
+        key = key * int(grid_size[j]) + c64[:, j]
+    self = _plan_from_keys(cls, key)
+    rest = self.unq_keys.long()
+    cols = []
+    for j in reversed(range(d)):
+        cols.append(rest % int(grid_size[j]))
+        rest = rest // int(grid_size[j])
+    self.unq_coors = torch.stack(list(reversed(cols)), 1).to(coors.dtype)
+    return self
+
+
+ScatterData.from_keys = classmethod(_from_keys)
+ScatterData.from_coords = classmethod(_from_coords)
+
+
 def ingroup_rank(data: ScatterData) -> torch.Tensor:
     """Index of every point inside its segment (int64 [num_total]), in increasing
     row order, from an existing plan."""
