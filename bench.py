@@ -394,6 +394,25 @@ def other_configs(dev):
         return res, data, arg
 
     table = {}
+    # the headline workload with bf16 features (fp32 accumulation and output)
+    n, c, m = N_POINTS, CHANNELS, N_SEGMENTS
+    ids, cnt = W.skewed_ids(n, m, seed=SEED)
+    data = ScatterData(ids.to(dev), cnt.to(dev))
+    feat16 = W.features(n, c, SEED, device=dev).to(torch.bfloat16)
+    out = torch.empty((m, c), device=dev)
+    arg = torch.empty((m, c), dtype=torch.int32, device=dev)
+    ws = torch.empty(lib.texb_reduce_workspace_bytes(n, c), dtype=torch.uint8, device=dev)
+    res = {"points": n, "channels": c, "segments": m, "note": "bf16 features, fp32 accumulation and output; "
+           "bytes counted with 2-byte features"}
+    for name, op in (("sum", _native.OP_SUM), ("mean", _native.OP_MEAN), ("max", _native.OP_MAX)):
+        us = timed(lambda: lib.texb_segment_reduce_bf16(op, feat16.data_ptr(), data.sid.data_ptr(), data.perm.data_ptr(),
+                                                        data.preSum.data_ptr(), 0, data.balance.data_ptr(),
+                                                        data.balance.numel(), n, c, m, out.data_ptr(), arg.data_ptr(), 0,
+                                                        ws.data_ptr(), ws.numel(), stream), 50)
+        nbytes = algorithmic_bytes(n, c, m)[name] - 2 * n * c
+        res[name] = {"us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1), "Mpoints_per_s": round(n / us, 1)}
+    table["skewed_1m_c128_bf16"] = res
+    del feat16, data, out, arg
     ids, cnt = W.uniform_ids(20_000, 2_000, SEED)
     table["uniform_20k_c16"], _, _ = forward(ids, cnt, W.features(20_000, 16, SEED, device=dev), "c1",
                                              "1.3 MB of features: L2-resident and launch-bound")

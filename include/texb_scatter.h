@@ -192,6 +192,22 @@ int texb_segment_reduce(int op, const float* feats, const int32_t* sid,
                         float* out, int32_t* arg, int32_t arg_base,
                         void* workspace, size_t workspace_bytes, void* stream);
 
+/* texb_segment_reduce for bf16 features (feats_bf16[N, channel], row-major):
+ * every value is widened exactly to fp32, accumulated as in the fp32 entry
+ * point (error-free sums, exact maxima) and written as fp32, so the result
+ * equals texb_segment_reduce on the widened features while reading half the
+ * bytes.  The reference is fp32-only (torchex/src/scatter/scatter.cpp:30, 48).
+ * Limits: channel a multiple of 8 and at least 128, pointers 16-byte aligned;
+ * other shapes return TEXB_ERR_UNSUPPORTED (widen them to fp32 instead).
+ * Workspace: texb_reduce_workspace_bytes, as for fp32. */
+int texb_segment_reduce_bf16(int op, const void* feats_bf16, const int32_t* sid,
+                             const int32_t* perm, const int32_t* offsets,
+                             int has_empty, const int32_t* balance,
+                             int balance_len, int64_t n, int channel,
+                             int64_t num_segments, float* out, int32_t* arg,
+                             int32_t arg_base, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
 /* texb_segment_reduce for callers that cannot allocate device memory.
  * No counterpart in the reference.
  *

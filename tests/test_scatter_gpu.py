@@ -363,3 +363,26 @@ def test_plan_from_coords_matches_torch_unique(pre_sorted):
     assert d2.unq_keys.tolist() == [2, 7, 2_000_000_000] and d2.unq_inv.tolist() == [1, 1, 0, 2, 0, 1]
     with pytest.raises(ValueError):
         ScatterData.from_keys(torch.tensor([-1, 3], device=DEV))
+
+
+@pytest.mark.parametrize("channel", [128, 136, 256, 64])
+@pytest.mark.parametrize("shuffled", [True, False])
+def test_bf16_features_equal_the_fp32_path_on_widened_values(channel, shuffled):
+    """bf16 rows are widened exactly, so the result must be bit-identical to the
+    fp32 kernels run on feats.float() (channel 64 exercises the widening fallback)."""
+    ids, cnt = W.skewed_ids(90_000, 4_000, seed=71, giant=15_000, shuffled=shuffled)
+    feat16 = W.features(90_000, channel, 72).to(torch.bfloat16).to(DEV)
+    data = ScatterData(ids.to(DEV), cnt.to(DEV))
+    wide = feat16.float()
+    for fn in (scatter_sum, scatter_mean):
+        got, want = fn(feat16, data), fn(wide, data)
+        assert got.dtype == torch.float32 and torch.equal(got, want), fn.__name__
+    (g_mx, g_arg), (w_mx, w_arg) = scatter_max(feat16, data), scatter_max(wide, data)
+    assert torch.equal(g_mx, w_mx) and torch.equal(g_arg, w_arg)
+    # and against the oracle directly
+    s64, _ = O.spec_scatter_sum_f64(wide.cpu(), ids, cnt.numel())
+    assert O.within_tolerance(scatter_sum(feat16, data).cpu().numpy(), s64, REL, ABS).all()
+    x = feat16.clone().requires_grad_(True)
+    scatter_mean(x, data).sum().backward()
+    assert x.grad.dtype == torch.bfloat16
+    assert _native.device_wait_timeouts() == 0

@@ -41,6 +41,10 @@ _SIGNATURES = {
                                        _c.c_int, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int, _c.c_int64,
                                        _c.c_void_p, _c.c_void_p, _c.c_int32, _c.c_void_p, _c.c_size_t,
                                        _c.c_void_p]),
+    "texb_segment_reduce_bf16": (_c.c_int, [_c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                            _c.c_int, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int, _c.c_int64,
+                                            _c.c_void_p, _c.c_void_p, _c.c_int32, _c.c_void_p, _c.c_size_t,
+                                            _c.c_void_p]),
     "texb_static_scratch_bytes": (_c.c_size_t, []),
     "texb_segment_reduce_static": (_c.c_int, [_c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                               _c.c_int, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int, _c.c_int64,

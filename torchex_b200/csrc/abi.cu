@@ -18,7 +18,7 @@ int plan_build_impl(const void*, int, int64_t, int64_t, int, int32_t*, int32_t*,
                     void*, size_t, cudaStream_t);
 int get_pre_sum_impl(const int32_t*, int32_t*, int64_t, int64_t, cudaStream_t);
 size_t reduce_workspace_bytes_impl(int64_t, int);
-int segment_reduce_impl(int, const float*, const int32_t*, const int32_t*, const int32_t*, int,
+int segment_reduce_impl(int, const void*, int, const int32_t*, const int32_t*, const int32_t*, int,
                         const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, int32_t, void*,
                         size_t, cudaStream_t);
 int plan_balance_impl(const int32_t*, int64_t, int32_t*, int, cudaStream_t);
@@ -219,7 +219,17 @@ int texb_segment_reduce(int op, const float* feats, const int32_t* sid, const in
                         int balance_len, int64_t n, int channel, int64_t num_segments, float* out,
                         int32_t* arg, int32_t arg_base, void* workspace, size_t workspace_bytes,
                         void* stream) {
-  return segment_reduce_impl(op, feats, sid, perm, offsets, has_empty, balance, balance_len, n,
+  return segment_reduce_impl(op, feats, 4, sid, perm, offsets, has_empty, balance, balance_len, n,
+                             channel, num_segments, out, arg, arg_base, workspace, workspace_bytes,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int texb_segment_reduce_bf16(int op, const void* feats_bf16, const int32_t* sid, const int32_t* perm,
+                             const int32_t* offsets, int has_empty, const int32_t* balance,
+                             int balance_len, int64_t n, int channel, int64_t num_segments, float* out,
+                             int32_t* arg, int32_t arg_base, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+  return segment_reduce_impl(op, feats_bf16, 2, sid, perm, offsets, has_empty, balance, balance_len, n,
                              channel, num_segments, out, arg, arg_base, workspace, workspace_bytes,
                              static_cast<cudaStream_t>(stream));
 }
@@ -259,7 +269,7 @@ static int compat_reduce(int op, const float* feats, const int32_t* pre_sum, flo
   int st = expand_offsets_impl(pre_sum, sid, num_total, num_unq, stream);
   if (st != TEXB_OK) return st;
   // The reference kernels write every row, including those of empty ranges.
-  return segment_reduce_impl(op, feats, sid, nullptr, pre_sum, /*has_empty=*/1, nullptr, 0, num_total, channel,
+  return segment_reduce_impl(op, feats, 4, sid, nullptr, pre_sum, /*has_empty=*/1, nullptr, 0, num_total, channel,
                              num_unq, out, arg, /*arg_base=*/0, reinterpret_cast<void*>(base + sid_bytes),
                              workspace_bytes - pad - sid_bytes, stream);
 }

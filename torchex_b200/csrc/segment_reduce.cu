@@ -30,6 +30,8 @@
 // from the largest segment and whose lanes run along rows (4-byte loads at a
 // stride of C * 4 bytes).
 
+#include <cuda_bf16.h>
+
 #include <cfloat>
 #include <cstdio>
 #include <mutex>
@@ -196,6 +198,9 @@ template <int VEC>
 __device__ __forceinline__ void store_words(uint32_t* p, const uint32_t (&v)[VEC]) {
   if constexpr (VEC == 4) {
     *reinterpret_cast<uint4*>(p) = make_uint4(v[0], v[1], v[2], v[3]);
+  } else if constexpr (VEC == 8) {
+    reinterpret_cast<uint4*>(p)[0] = make_uint4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<uint4*>(p)[1] = make_uint4(v[4], v[5], v[6], v[7]);
   } else {
 #pragma unroll
     for (int k = 0; k < VEC; ++k) p[k] = v[k];
@@ -207,6 +212,10 @@ __device__ __forceinline__ void load_words(const uint32_t* p, uint32_t (&v)[VEC]
   if constexpr (VEC == 4) {
     uint4 t = *reinterpret_cast<const uint4*>(p);
     v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else if constexpr (VEC == 8) {
+    const uint4 t = reinterpret_cast<const uint4*>(p)[0], u = reinterpret_cast<const uint4*>(p)[1];
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    v[4] = u.x; v[5] = u.y; v[6] = u.z; v[7] = u.w;
   } else {
 #pragma unroll
     for (int k = 0; k < VEC; ++k) v[k] = p[k];
@@ -245,6 +254,9 @@ __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __re
   float* po = out + int64_t(seg) * C + ch;
   if constexpr (VEC == 4) {
     *reinterpret_cast<float4*>(po) = make_float4(r[0], r[1], r[2], r[3]);
+  } else if constexpr (VEC == 8) {
+    reinterpret_cast<float4*>(po)[0] = make_float4(r[0], r[1], r[2], r[3]);
+    reinterpret_cast<float4*>(po)[1] = make_float4(r[4], r[5], r[6], r[7]);
   } else {
 #pragma unroll
     for (int k = 0; k < VEC; ++k) po[k] = r[k];
@@ -259,6 +271,15 @@ __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __re
         ix[k] = i < 0 ? i : i + arg_base;
       }
       *reinterpret_cast<int4*>(pa) = make_int4(ix[0], ix[1], ix[2], ix[3]);
+    } else if constexpr (VEC == 8) {
+      int ix[VEC];
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        const int i = Op::template index<VEC>(x, k);
+        ix[k] = i < 0 ? i : i + arg_base;
+      }
+      reinterpret_cast<int4*>(pa)[0] = make_int4(ix[0], ix[1], ix[2], ix[3]);
+      reinterpret_cast<int4*>(pa)[1] = make_int4(ix[4], ix[5], ix[6], ix[7]);
     } else {
 #pragma unroll
       for (int k = 0; k < VEC; ++k) {
@@ -284,6 +305,9 @@ __device__ __forceinline__ void store_single(float* __restrict__ out, int32_t* _
     float* po = out + int64_t(seg) * C + ch;
     if constexpr (VEC == 4) {
       *reinterpret_cast<float4*>(po) = make_float4(v[0], v[1], v[2], v[3]);
+    } else if constexpr (VEC == 8) {
+      reinterpret_cast<float4*>(po)[0] = make_float4(v[0], v[1], v[2], v[3]);
+      reinterpret_cast<float4*>(po)[1] = make_float4(v[4], v[5], v[6], v[7]);
     } else {
 #pragma unroll
       for (int k = 0; k < VEC; ++k) po[k] = v[k];
@@ -568,26 +592,44 @@ __device__ __forceinline__ void mbar_wait_bounded(unsigned bar, unsigned parity)
 }
 
 constexpr int kStageBatch = 8;    // rows per copy batch
-constexpr int kStageDepth = 3;    // groups in the ring: two in flight, one being reduced
+// Batches in the ring.  fp32 rows: three (two in flight, one being reduced).  bf16
+// rows carry eight channels per lane, which doubles the shared memory of the
+// edge-run slots, so their ring has two batches to keep two CTAs per SM.
+template <class In> constexpr int kStageDepthFor = (sizeof(In) == 4) ? 3 : 2;
 constexpr int kStageTile = 32;    // positions per metadata tile
 constexpr int kStageSlotBytes = kCtaThreads * 16;  // one row slot for the whole CTA
-constexpr int kStageRingBytes = kStageBatch * kStageDepth * kStageSlotBytes;
+template <class In> constexpr int kStageRingBytesFor = kStageBatch * kStageDepthFor<In> * kStageSlotBytes;
 
-template <class Op, int LPR, bool HAS_PERM, bool BULK>
+// The 16 bytes a lane owns of a row, as fp32 channels.
+template <class In, int VEC>
+__device__ __forceinline__ void unpack_lane(const float4& t4, float (&v)[VEC]) {
+  if constexpr (sizeof(In) == 4) {
+    v[0] = t4.x; v[1] = t4.y; v[2] = t4.z; v[3] = t4.w;
+  } else {
+    const unsigned w[4] = {__float_as_uint(t4.x), __float_as_uint(t4.y), __float_as_uint(t4.z), __float_as_uint(t4.w)};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {  // a bf16 is the upper half of the fp32 with the same value
+      v[2 * k] = __uint_as_float(w[k] << 16);
+      v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+    }
+  }
+}
+
+template <class Op, class In, int LPR, bool HAS_PERM, bool BULK>
 __global__ void __launch_bounds__(kCtaThreads, 2)
-segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __restrict__ sid,
+segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __restrict__ sid,
                              const int32_t* __restrict__ perm, float* __restrict__ out,
                              int32_t* __restrict__ arg, Workspace ws, int n, int C,
                              Split sp, bool mean, int arg_base) {
-  constexpr int VEC = 4;
+  constexpr int VEC = 16 / sizeof(In);  // channels in the 16 bytes a lane owns: 4 fp32 or 8 bf16
   using State = typename Op::template State<VEC>;
   constexpr int GPC = kCtaThreads / LPR;
   constexpr int CPS = LPR * VEC;
   constexpr int SLOTS = 2 * GPC;
-  constexpr int B = kStageBatch, S = kStageDepth, T = kStageTile;
+  constexpr int B = kStageBatch, S = kStageDepthFor<In>, T = kStageTile;
   constexpr int NREG = T / LPR;  // tile positions held per lane
   static_assert(LPR == 16 || LPR == 32, "staged kernel handles 16 or 32 lanes per row");
-  static_assert((S - 1) * B <= T && T % B == 0 && LPR % B == 0, "the copy front must stay within two tiles");
+  static_assert(S >= 2 && (S - 1) * B <= T && T % B == 0 && LPR % B == 0, "the copy front must stay within two tiles");
 
   extern __shared__ __align__(16) unsigned char s_dyn[];  // the ring
   __shared__ __align__(16) uint32_t s_vec[SLOTS * 2 * CPS];  // edge runs of the groups
@@ -630,12 +672,12 @@ segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __r
     const int nb = (L + B - 1) / B;
     // Inactive lanes (channel tail of the last slab) copy channel 0 instead of
     // branching around every access; their results are never stored.
-    const float* lane_src = feats + (lane_on ? ch : 0);
+    const In* lane_src = feats + (lane_on ? ch : 0);
     // cp.async layout: slot s of the CTA at s * kStageSlotBytes, lane t at + 16 t.
     // Bulk layout: each group owns S * B consecutive row slabs of kRowBytes.
-    constexpr int kRowBytes = CPS * 4;
+    constexpr int kRowBytes = LPR * 16;
     constexpr int kSlotFloat4 = BULK ? LPR : kCtaThreads;  // float4 stride between slots
-    const int row_bytes = min(CPS, C - blockIdx.y * CPS) * 4;  // the last slab may be narrower
+    const int row_bytes = min(CPS, C - blockIdx.y * CPS) * int(sizeof(In));  // the last slab may be narrower
     const unsigned ring_addr = BULK
         ? unsigned(__cvta_generic_to_shared(s_dyn)) + unsigned(group * S * B) * kRowBytes
         : unsigned(__cvta_generic_to_shared(s_dyn)) + threadIdx.x * 16;
@@ -643,7 +685,7 @@ segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __r
         ? reinterpret_cast<const float4*>(s_dyn) + group * S * B * LPR + lane_g
         : reinterpret_cast<const float4*>(s_dyn) + threadIdx.x;
     const unsigned bar0 = unsigned(__cvta_generic_to_shared(&s_bar[BULK ? group * S : 0]));
-    const float* slab_src = feats + blockIdx.y * CPS;
+    const In* slab_src = feats + blockIdx.y * CPS;
     const unsigned long long stream_policy = BULK ? l2_policy(sp.stream_hint != 0) : 0ull;
 
     // Tile metadata: lane_g holds positions t * T + r * LPR + lane_g (r < NREG).
@@ -748,7 +790,8 @@ segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __r
     };
     // One row of a batch that holds run ends.  `single`: the row is a whole segment.
     auto row_step = [&](int q, const float4& t4, int row, bool end_k, bool single, int sids_reg, int lane_k) {
-      const float v[VEC] = {t4.x, t4.y, t4.z, t4.w};
+      float v[VEC];
+      unpack_lane<In, VEC>(t4, v);
       if (single) {
         const int sid_now = __shfl_sync(gmask, sids_reg, lane_k, LPR);
         store_single<Op, VEC>(out, arg, sid_now, C, ch, lane_on, v, row, arg_base);
@@ -805,7 +848,8 @@ segment_reduce_staged_kernel(const float* __restrict__ feats, const int32_t* __r
 #pragma unroll
           for (int k = 0; k < B; ++k) {
             const float4 t4 = src[k * kSlotFloat4];
-            const float v[VEC] = {t4.x, t4.y, t4.z, t4.w};
+            float v[VEC];
+            unpack_lane<In, VEC>(t4, v);
             int row = g0 + q0 + k;
             if constexpr (Op::kIsMax && HAS_PERM) row = __shfl_sync(gmask, rows_reg, (j0 & (LPR - 1)) + k, LPR);
             Op::template add<VEC>(acc, v, row);
@@ -981,6 +1025,7 @@ __global__ void expand_offsets_kernel(const int32_t* __restrict__ offsets, int32
 // ---- host side ----------------------------------------------------------------
 
 struct Layout {
+  int in_bytes;  // 4: fp32 features, 2: bf16 features (staged kernel only)
   int vec, lpr, cps, num_slabs, gpc;
   int staged;  // 0: register kernel, 1: cp.async ring, 2: bulk-copy (TMA) ring; 128-bit lanes, 16 or 32 lanes per row
 };
@@ -994,9 +1039,11 @@ int sm_count() {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-Layout make_layout(int C, bool allow_vec4) {
+Layout make_layout(int C, bool allow_vec4, int in_bytes = 4) {
   Layout g;
+  g.in_bytes = in_bytes;
   g.vec = (allow_vec4 && C % 4 == 0) ? 4 : 1;
+  if (in_bytes == 2) g.vec = 8;  // the caller has checked C % 8 == 0 and the alignment
   const int lanes = C / g.vec;
   int lpr = 1;
   while (lpr < lanes && lpr < 32) lpr <<= 1;
@@ -1005,7 +1052,8 @@ Layout make_layout(int C, bool allow_vec4) {
   g.cps = g.lpr * g.vec;
   g.num_slabs = (C + g.cps - 1) / g.cps;
   g.gpc = kCtaThreads / g.lpr;
-  g.staged = (g.vec == 4 && g.lpr >= 16) ? tuning().staged : 0;
+  g.staged = (g.vec >= 4 && g.lpr >= 16) ? tuning().staged : 0;
+  if (in_bytes == 2 && g.staged == 0) g.staged = 2;  // bf16 rows exist only in the staged kernel
   return g;
 }
 
@@ -1043,8 +1091,9 @@ size_t records_meta_bytes(const Layout& g, int num_ctas) {
 // over every occupancy the launch may find.
 size_t reduce_workspace_bytes(int64_t n, int C) {
   size_t best = 0;
-  for (int v = 0; v < 2; ++v) {
-    const Layout g = make_layout(C, v == 1);
+  for (int v = 0; v < 3; ++v) {
+    if (v == 2 && C % 8 != 0) continue;
+    const Layout g = (v == 2) ? make_layout(C, true, 2) : make_layout(C, v == 1);
     const Split s = make_split(n, g, kMaxCtasPerSm);
     const size_t bytes = records_vec_bytes(g, s.num_ctas) + records_meta_bytes(g, s.num_ctas);
     if (bytes > best) best = bytes;
@@ -1053,7 +1102,7 @@ size_t reduce_workspace_bytes(int64_t n, int C) {
 }
 
 struct Call {
-  const float* feats;
+  const void* feats;
   const int32_t* sid;
   const int32_t* perm;
   float* out;
@@ -1080,7 +1129,7 @@ int resident_ctas(Kernel kernel, size_t dyn_smem) {
   return blocks < kMaxCtasPerSm ? blocks : kMaxCtasPerSm;
 }
 
-template <class Op, int VEC, int LPR, class Kernel>
+template <class Op, class In, int VEC, int LPR, class Kernel>
 int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g, const Call& c) {
   Split s = make_split(c.n, g, ctas_per_sm);
   if (c.balance && c.balance_k > 0 && tuning().balanced) {
@@ -1099,8 +1148,8 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
   ws.meta = reinterpret_cast<int4*>(base + vec_bytes);
 
   const dim3 grid(s.num_ctas, g.num_slabs);
-  kernel<<<grid, kCtaThreads, dyn_smem, c.stream>>>(c.feats, c.sid, c.perm, c.out, c.arg, ws, c.n, c.C,
-                                                    s, c.mean, c.arg_base);
+  kernel<<<grid, kCtaThreads, dyn_smem, c.stream>>>(static_cast<const In*>(c.feats), c.sid, c.perm, c.out,
+                                                    c.arg, ws, c.n, c.C, s, c.mean, c.arg_base);
   int st = check_launch("segment reduce kernel");
   if (st != TEXB_OK || s.num_ctas <= 1) return st;
 
@@ -1126,29 +1175,34 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
   return check_launch("segment_fixup_kernel");
 }
 
+// Staged walkers (cp.async or bulk-copy ring) for one input type.
+template <class Op, class In, int LPR, bool HAS_PERM>
+int launch_staged(const Layout& g, const Call& c) {
+  constexpr int VEC = 16 / sizeof(In);
+  constexpr int kRing = kStageRingBytesFor<In>;
+  // The shared-memory attribute is per device: set it on every call (a host-side table write).
+  auto staged_launch = [&](auto kernel, int* resident) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);
+    if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    if (*resident == 0) *resident = resident_ctas(kernel, kRing);
+    return launch_pair<Op, In, VEC, LPR>(kernel, kRing, *resident, g, c);
+  };
+  if (g.staged == 2) {
+    static int resident = 0;
+    return staged_launch(segment_reduce_staged_kernel<Op, In, LPR, HAS_PERM, true>, &resident);
+  }
+  static int resident = 0;
+  return staged_launch(segment_reduce_staged_kernel<Op, In, LPR, HAS_PERM, false>, &resident);
+}
+
 template <class Op, int VEC, int LPR, bool HAS_PERM>
 int launch_reduce(const Layout& g, const Call& c) {
   if constexpr (VEC == 4 && (LPR == 16 || LPR == 32)) {
-    if (g.staged) {
-      // The shared-memory attribute is per device: set it on every call (a host-side table write).
-      auto staged_launch = [&](auto kernel, int* resident) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kStageRingBytes);
-        if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        if (*resident == 0) *resident = resident_ctas(kernel, kStageRingBytes);
-        return launch_pair<Op, VEC, LPR>(kernel, kStageRingBytes, *resident, g, c);
-      };
-      if (g.staged == 2) {
-        static int resident = 0;
-        return staged_launch(segment_reduce_staged_kernel<Op, LPR, HAS_PERM, true>, &resident);
-      }
-      static int resident = 0;
-      return staged_launch(segment_reduce_staged_kernel<Op, LPR, HAS_PERM, false>, &resident);
-    }
+    if (g.staged) return launch_staged<Op, float, LPR, HAS_PERM>(g, c);
   }
   auto kernel = segment_reduce_kernel<Op, VEC, LPR, HAS_PERM>;
   static const int resident = resident_ctas(kernel, 0);
-  return launch_pair<Op, VEC, LPR>(kernel, 0, resident, g, c);
+  return launch_pair<Op, float, VEC, LPR>(kernel, 0, resident, g, c);
 }
 
 template <class Op, int VEC, int LPR>
@@ -1159,6 +1213,13 @@ int dispatch_perm(const Layout& g, const Call& c) {
 
 template <class Op>
 int dispatch_layout(const Layout& g, const Call& c) {
+  if (g.in_bytes == 2) {
+    if (g.lpr == 16)
+      return c.perm ? launch_staged<Op, __nv_bfloat16, 16, true>(g, c) : launch_staged<Op, __nv_bfloat16, 16, false>(g, c);
+    if (g.lpr == 32)
+      return c.perm ? launch_staged<Op, __nv_bfloat16, 32, true>(g, c) : launch_staged<Op, __nv_bfloat16, 32, false>(g, c);
+    return fail(TEXB_ERR_UNSUPPORTED, "bf16 features need at least 128 channels (got %d lanes per row)", g.lpr);
+  }
   if (g.vec == 4) {
     switch (g.lpr) {
       case 1: return dispatch_perm<Op, 4, 1>(g, c);
@@ -1182,10 +1243,12 @@ int dispatch_layout(const Layout& g, const Call& c) {
 
 }  // namespace
 
-int segment_reduce_impl(int op, const float* feats, const int32_t* sid, const int32_t* perm,
+int segment_reduce_impl(int op, const void* feats, int in_bytes, const int32_t* sid, const int32_t* perm,
                         const int32_t* offsets, int has_empty, const int32_t* balance,
                         int balance_len, int64_t n, int C, int64_t m, float* out, int32_t* arg,
                         int32_t arg_base, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  if (in_bytes != 4 && in_bytes != 2)
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "features must be fp32 (4 bytes) or bf16 (2 bytes)");
   if (op != TEXB_OP_SUM && op != TEXB_OP_MEAN && op != TEXB_OP_MAX)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "unknown reduce op %d", op);
   if (n < 0 || m < 0 || C < 1)
@@ -1210,7 +1273,11 @@ int segment_reduce_impl(int op, const float* feats, const int32_t* sid, const in
   }
 
   const bool vec_ok = aligned16(feats) && aligned16(out) && (op != TEXB_OP_MAX || aligned16(arg));
-  const Layout g = make_layout(C, vec_ok);
+  if (in_bytes == 2 && (!vec_ok || C % 8 != 0 || C < 128))
+    return fail(TEXB_ERR_UNSUPPORTED,
+                "bf16 features need 16-byte aligned pointers and a channel count that is a multiple of 8 "
+                "and at least 128 (got %d); convert to fp32 for other shapes", C);
+  const Layout g = make_layout(C, vec_ok, in_bytes);
   if (balance && balance_len < 2)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "balance table needs at least 2 entries");
   Call c = {feats, sid, perm, out, arg, workspace, workspace_bytes, int(n), C, op == TEXB_OP_MEAN, stream,
@@ -1274,7 +1341,7 @@ int segment_reduce_static_impl(int op, const float* feats, const int32_t* sid, c
     }
     scratch = device_ptr[dev];
   }
-  return segment_reduce_impl(op, feats, sid, perm, offsets, has_empty, balance, balance_len, n, C, m, out,
+  return segment_reduce_impl(op, feats, 4, sid, perm, offsets, has_empty, balance, balance_len, n, C, m, out,
                              arg, arg_base, scratch, kStaticScratchBytes, stream);
 }
 

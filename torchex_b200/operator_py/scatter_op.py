@@ -14,6 +14,8 @@ Differences a caller can observe:
   * ``arg`` holds the row of ``feats`` as passed by the caller.
   * ids outside ``[0, num_unq)`` raise ``ValueError`` instead of corrupting
     memory.
+  * ``feats`` may also be bfloat16: values are widened exactly, accumulated in
+    fp32 and returned as float32 (the reference is fp32-only).
 """
 from __future__ import annotations
 
@@ -34,8 +36,8 @@ def _scratch(nbytes: int, device) -> torch.Tensor:
 def _as_feats(feats: torch.Tensor) -> torch.Tensor:
     if not feats.is_cuda:
         raise RuntimeError("feats must be a CUDAtensor")
-    if feats.dtype != torch.float32:
-        raise RuntimeError(f"feats must be float32, got {feats.dtype}")
+    if feats.dtype not in (torch.float32, torch.bfloat16):
+        raise RuntimeError(f"feats must be float32 (or bfloat16), got {feats.dtype}")
     if feats.ndim != 2:
         raise RuntimeError(f"feats must be [num_total, channel], got {tuple(feats.shape)}")
     return feats.contiguous()
@@ -257,6 +259,8 @@ def gather_back(values: torch.Tensor, data: ScatterData) -> torch.Tensor:
 def _reduce(op: int, feats: torch.Tensor, data: ScatterData, want_arg: bool, arg_base: int = 0):
     feats = _as_feats(feats)
     n, c = feats.shape
+    if feats.dtype == torch.bfloat16 and (c % 8 != 0 or c < 128 or feats.data_ptr() % 16 != 0):
+        feats = feats.float()  # the bf16 kernel covers wide, aligned rows; others are widened first
     if n != data.unq_inv.numel():
         raise RuntimeError(f"feats has {n} rows but ScatterData was built for {data.unq_inv.numel()}")
     dev = feats.device
@@ -281,12 +285,13 @@ def _reduce(op: int, feats: torch.Tensor, data: ScatterData, want_arg: bool, arg
         if ws is None or ws.numel() < lib.texb_reduce_workspace_bytes(n, c):
             ws = _scratch(lib.texb_reduce_workspace_bytes(n, c), dev)
             data._workspaces[key] = ws
+        entry = lib.texb_segment_reduce_bf16 if feats.dtype == torch.bfloat16 else lib.texb_segment_reduce
         _native.check(
-            lib.texb_segment_reduce(op, feats.data_ptr(), data.sid.data_ptr(), data._perm_ptr,
-                                    data.preSum.data_ptr(), int(data.has_empty or n == 0),
-                                    data.balance.data_ptr(), data.balance.numel(), n, c, m,
-                                    out.data_ptr(), None if arg is None else arg.data_ptr(), int(arg_base),
-                                    ws.data_ptr(), ws.numel(), stream),
+            entry(op, feats.data_ptr(), data.sid.data_ptr(), data._perm_ptr,
+                  data.preSum.data_ptr(), int(data.has_empty or n == 0),
+                  data.balance.data_ptr(), data.balance.numel(), n, c, m,
+                  out.data_ptr(), None if arg is None else arg.data_ptr(), int(arg_base),
+                  ws.data_ptr(), ws.numel(), stream),
             "texb_segment_reduce")
     finally:
         if switch:
@@ -331,12 +336,12 @@ class ScatterSumFunction(Function):
         num_total.  Returns float32 [num_unq, channel].
         """
         out, _ = _reduce(_native.OP_SUM, feats, data, want_arg=False)
-        ctx.plan = data
+        ctx.plan, ctx.in_dtype = data, feats.dtype
         return out
 
     @staticmethod
     def backward(ctx, g):
-        return _broadcast_back("sum", ctx.plan, g, None), None
+        return _broadcast_back("sum", ctx.plan, g, None).to(ctx.in_dtype), None
 
 
 class ScatterMeanFunction(Function):
@@ -346,12 +351,12 @@ class ScatterMeanFunction(Function):
         """out[s] = mean of the rows of feats whose id is s (one fused kernel;
         the divisor is the number of rows actually reduced)."""
         out, _ = _reduce(_native.OP_MEAN, feats, data, want_arg=False)
-        ctx.plan = data
+        ctx.plan, ctx.in_dtype = data, feats.dtype
         return out
 
     @staticmethod
     def backward(ctx, g):
-        return _broadcast_back("mean", ctx.plan, g, None), None
+        return _broadcast_back("mean", ctx.plan, g, None).to(ctx.in_dtype), None
 
 
 class ScatterMaxFunction(Function):
@@ -363,13 +368,13 @@ class ScatterMaxFunction(Function):
         out, arg = _reduce(_native.OP_MAX, feats, data, want_arg=True)
         ctx.save_for_backward(arg)
         ctx.mark_non_differentiable(arg)
-        ctx.plan = data
+        ctx.plan, ctx.in_dtype = data, feats.dtype
         return out, arg
 
     @staticmethod
     def backward(ctx, g_out, g_arg):
         (arg,) = ctx.saved_tensors
-        return _broadcast_back("max", ctx.plan, g_out, arg), None
+        return _broadcast_back("max", ctx.plan, g_out, arg).to(ctx.in_dtype), None
 
 
 class GetPreSumFunction(Function):
