@@ -386,3 +386,40 @@ def test_bf16_features_equal_the_fp32_path_on_widened_values(channel, shuffled):
     scatter_mean(x, data).sum().backward()
     assert x.grad.dtype == torch.bfloat16
     assert _native.device_wait_timeouts() == 0
+
+
+@pytest.mark.parametrize("n,c,m", [(1, 4, 1), (777, 20, 13), (5_000, 128, 300), (40_000, 136, 2_500), (3_000, 3, 3_000)])
+def test_outputs_are_written_exactly_and_nothing_else(n, c, m):
+    """Canaries around out / arg / g_in: every row is written, no byte outside is."""
+    lib = _native.lib()
+    g = torch.Generator().manual_seed(n + c)
+    ids = torch.randint(0, m, (n,), generator=g)
+    ids[: min(n, m)] = torch.arange(min(n, m))
+    cnt = torch.bincount(ids, minlength=m)
+    data = ScatterData(ids.to(DEV), cnt.to(DEV))
+    feat = W.features(n, c, n).to(DEV)
+    pad = 64
+    stream = torch.cuda.current_stream().cuda_stream
+    ws = torch.empty(lib.texb_reduce_workspace_bytes(n, c), dtype=torch.uint8, device=DEV)
+    for op in (_native.OP_SUM, _native.OP_MEAN, _native.OP_MAX):
+        out_buf = torch.full((pad + m * c + pad,), 12345.0, device=DEV)
+        arg_buf = torch.full((pad + m * c + pad,), -777, dtype=torch.int32, device=DEV)
+        out, arg = out_buf[pad: pad + m * c], arg_buf[pad: pad + m * c]
+        st = lib.texb_segment_reduce(op, feat.data_ptr(), data.sid.data_ptr(), data._perm_ptr, data.preSum.data_ptr(),
+                                     int(data.has_empty), data.balance.data_ptr(), data.balance.numel(), n, c, m,
+                                     out.data_ptr(), arg.data_ptr(), 0, ws.data_ptr(), ws.numel(), stream)
+        assert st == 0, _native.last_error()
+        assert bool((out_buf[:pad] == 12345.0).all()) and bool((out_buf[pad + m * c:] == 12345.0).all())
+        assert bool((arg_buf[:pad] == -777).all()) and bool((arg_buf[pad + m * c:] == -777).all())
+        assert not bool((out == 12345.0).any())
+        if op == _native.OP_MAX:
+            assert not bool((arg == -777).any())
+        else:
+            assert bool((arg == -777).all())          # sum / mean never touch arg
+    gin_buf = torch.full((pad + n * c + pad,), 12345.0, device=DEV)
+    gv = W.features(m, c, 9).to(DEV)
+    st = lib.texb_scatter_sum_backward(gv.data_ptr(), data.sid.data_ptr(), data._perm_ptr, gin_buf[pad:].data_ptr(),
+                                       n, c, m, stream)
+    assert st == 0
+    assert bool((gin_buf[:pad] == 12345.0).all()) and bool((gin_buf[pad + n * c:] == 12345.0).all())
+    assert torch.equal(gin_buf[pad: pad + n * c].view(n, c), gv[ids.to(DEV)])
