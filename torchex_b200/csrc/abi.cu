@@ -45,7 +45,7 @@ namespace {
 thread_local char t_error[512] = "";
 
 std::mutex g_tuning_mutex;
-Tuning g_tuning = {0, 2, 1, 1, 1, 8, 0};
+Tuning g_tuning = {0, 2, 1, 1, 1, 5, 0};
 bool g_tuning_env_read = false;
 
 int env_int(const char* name, int fallback) {

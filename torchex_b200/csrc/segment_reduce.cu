@@ -324,6 +324,14 @@ struct Workspace {
   int4* meta;     // [num_slabs * num_ctas * 2]
 };
 
+// Low word of the nanosecond timer.  The last field of a CTA's tail meta records
+// when the CTA finished: a diagnostic for the spread of finishing times.
+__device__ __forceinline__ unsigned global_timer_lo() {
+  unsigned t;
+  asm volatile("mov.u32 %0, %%globaltimer_lo;" : "=r"(t));
+  return t;
+}
+
 // Stitches the edge runs a CTA left in shared memory, in position order (group
 // 0 only).  Segments that live inside the CTA are written to `out`; a run open
 // at the CTA's left or right edge becomes the CTA's head or tail record.
@@ -331,7 +339,8 @@ template <class Op, int VEC, int LPR>
 __device__ __forceinline__ void stitch_cta(const uint32_t* s_vec, const int* s_sid, const int* s_cnt,
                                            const unsigned* s_flag, float* __restrict__ out,
                                            int32_t* __restrict__ arg, Workspace ws, int C, int ch,
-                                           bool lane_on, int lane_g, int group, bool mean, int arg_base) {
+                                           bool lane_on, int lane_g, int group, bool mean, int arg_base,
+                                           unsigned t_start = 0u) {
   using State = typename Op::template State<VEC>;
   constexpr int GPC = kCtaThreads / LPR;
   constexpr int CPS = LPR * VEC;
@@ -366,19 +375,19 @@ __device__ __forceinline__ void stitch_cta(const uint32_t* s_vec, const int* s_s
         uint32_t* ga = ws.vec + rec * 2 * CPS + lane_g * VEC;
         store_state<Op, VEC>(ga, ga + CPS, cur);
         head_flag = kValid | kOpenLeft;
-        if (lane_g == 0) ws.meta[rec] = make_int4(cur_sid, cur_cnt, int(head_flag), 0);
+        if (lane_g == 0) ws.meta[rec] = make_int4(cur_sid, cur_cnt, int(head_flag), int(t_start));
       }
       have = false;
     }
   }
-  if (head_flag == 0u && lane_g == 0) ws.meta[rec] = make_int4(0, 0, 0, 0);
+  if (head_flag == 0u && lane_g == 0) ws.meta[rec] = make_int4(0, 0, 0, int(t_start));
   if (have) {
     uint32_t* ga = ws.vec + (rec + 1) * 2 * CPS + lane_g * VEC;
     store_state<Op, VEC>(ga, ga + CPS, cur);
     const unsigned f = kValid | kOpenRight | (cur_open_left ? kOpenLeft : 0u);
-    if (lane_g == 0) ws.meta[rec + 1] = make_int4(cur_sid, cur_cnt, int(f), 0);
+    if (lane_g == 0) ws.meta[rec + 1] = make_int4(cur_sid, cur_cnt, int(f), int(global_timer_lo()));
   } else if (lane_g == 0) {
-    ws.meta[rec + 1] = make_int4(0, 0, 0, 0);
+    ws.meta[rec + 1] = make_int4(0, 0, 0, int(global_timer_lo()));
   }
 }
 
@@ -429,6 +438,11 @@ segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict
 #if __CUDA_ARCH__ >= 900
   // Let the dependent fix-up grid be scheduled now (it parks at its own
   // griddepcontrol.wait until this grid has finished); a no-op for a plain launch.
+  // This grid may itself be a dependent launch of whatever kernel precedes it in
+  // the stream (typically the fix-up of the previous reduction): its CTAs are then
+  // placed while that kernel drains, and the wait below holds them until all of
+  // its memory operations are visible, before anything is read.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #endif
   const int lane_g = threadIdx.x & (LPR - 1);
@@ -641,8 +655,14 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
 #if __CUDA_ARCH__ >= 900
   // Let the dependent fix-up grid be scheduled now (it parks at its own
   // griddepcontrol.wait until this grid has finished); a no-op for a plain launch.
+  // This grid may itself be a dependent launch of whatever kernel precedes it in
+  // the stream (typically the fix-up of the previous reduction): its CTAs are then
+  // placed while that kernel drains, and the wait below holds them until all of
+  // its memory operations are visible, before anything is read.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #endif
+  const unsigned t_start = global_timer_lo();
   const int lane_g = threadIdx.x & (LPR - 1);
   const int group = threadIdx.x / LPR;
   const int lane_base = (threadIdx.x & 31) & ~(LPR - 1);  // first lane of the group
@@ -895,7 +915,7 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
   if constexpr (!BULK) cp_async_wait<0>();
   __syncthreads();
   stitch_cta<Op, VEC, LPR>(s_vec, s_sid, s_cnt, s_flag, out, arg, ws, C, ch, lane_on, lane_g,
-                           group, mean, arg_base);
+                           group, mean, arg_base, t_start);
 }
 
 // ---- fix-up kernel --------------------------------------------------------------
@@ -920,6 +940,7 @@ segment_fixup_kernel(Workspace ws, float* __restrict__ out, int32_t* __restrict_
   // With programmatic dependent launch this grid may start before the reduce
   // grid has finished; wait for its memory to be visible.  No-op otherwise.
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #endif
 
   const int b = blockIdx.x;
@@ -1148,8 +1169,24 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
   ws.meta = reinterpret_cast<int4*>(base + vec_bytes);
 
   const dim3 grid(s.num_ctas, g.num_slabs);
-  kernel<<<grid, kCtaThreads, dyn_smem, c.stream>>>(static_cast<const In*>(c.feats), c.sid, c.perm, c.out,
-                                                    c.arg, ws, c.n, c.C, s, c.mean, c.arg_base);
+  if (tuning().fixup_pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kCtaThreads);
+    cfg.dynamicSmemBytes = dyn_smem;
+    cfg.stream = c.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<const In*>(c.feats), c.sid, c.perm, c.out,
+                                       c.arg, ws, c.n, c.C, s, c.mean, c.arg_base);
+    if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "segment reduce launch: %s", cudaGetErrorString(e));
+  } else {
+    kernel<<<grid, kCtaThreads, dyn_smem, c.stream>>>(static_cast<const In*>(c.feats), c.sid, c.perm, c.out,
+                                                      c.arg, ws, c.n, c.C, s, c.mean, c.arg_base);
+  }
   int st = check_launch("segment reduce kernel");
   if (st != TEXB_OK || s.num_ctas <= 1) return st;
 
