@@ -173,37 +173,45 @@ radix_histogram_kernel(const void* __restrict__ keys, int n, int shift, uint32_t
 }
 
 // In-place exclusive scan over `count` words by a single CTA of 1024 threads.
+// The array is walked in slabs of 4096 words with coalesced accesses (thread t
+// owns words 4t .. 4t+3 of the slab); the running total carries between slabs.
 __global__ void __launch_bounds__(1024) exclusive_scan_kernel(uint32_t* data, int64_t count) {
   __shared__ uint32_t s_warp[32];
-  const int64_t per = (count + 1023) / 1024;
-  const int64_t i0 = min(int64_t(threadIdx.x) * per, count);
-  const int64_t i1 = min(i0 + per, count);
-  uint32_t sum = 0u;
-  for (int64_t i = i0; i < i1; ++i) sum += data[i];
-  // exclusive scan of the 1024 per-thread sums
+  __shared__ uint32_t s_total;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint32_t incl = sum;
-  for (int o = 1; o < 32; o <<= 1) {
-    uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += t;
-  }
-  if (lane == 31) s_warp[warp] = incl;
-  __syncthreads();
-  if (warp == 0) {
-    uint32_t w = s_warp[lane];
-    uint32_t wi = w;
+  uint32_t carry = 0u;
+  for (int64_t base = 0; base < count; base += 4096) {
+    const int64_t i0 = base + int64_t(threadIdx.x) * 4;
+    uint32_t v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = (i0 + k < count) ? data[i0 + k] : 0u;
+    const uint32_t sum = v[0] + v[1] + v[2] + v[3];
+    uint32_t incl = sum;
     for (int o = 1; o < 32; o <<= 1) {
-      uint32_t t = __shfl_up_sync(0xffffffffu, wi, o);
-      if (lane >= o) wi += t;
+      const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
     }
-    s_warp[lane] = wi - w;  // exclusive base of each warp
-  }
-  __syncthreads();
-  uint32_t run = s_warp[warp] + (incl - sum);
-  for (int64_t i = i0; i < i1; ++i) {
-    const uint32_t v = data[i];
-    data[i] = run;
-    run += v;
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      const uint32_t w = s_warp[lane];
+      uint32_t wi = w;
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xffffffffu, wi, o);
+        if (lane >= o) wi += t;
+      }
+      s_warp[lane] = wi - w;  // exclusive base of each warp
+      if (lane == 31) s_total = wi;
+    }
+    __syncthreads();
+    uint32_t run = carry + s_warp[warp] + (incl - sum);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (i0 + k < count) data[i0 + k] = run;
+      run += v[k];
+    }
+    carry += s_total;
+    __syncthreads();  // s_warp / s_total are rewritten by the next slab
   }
 }
 
