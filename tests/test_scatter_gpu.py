@@ -423,3 +423,25 @@ def test_outputs_are_written_exactly_and_nothing_else(n, c, m):
     assert st == 0
     assert bool((gin_buf[:pad] == 12345.0).all()) and bool((gin_buf[pad + n * c:] == 12345.0).all())
     assert torch.equal(gin_buf[pad: pad + n * c].view(n, c), gv[ids.to(DEV)])
+
+
+def test_same_plan_on_two_streams():
+    """A plan keeps one workspace per stream, so reductions issued concurrently on
+    two streams with the same ScatterData do not share scratch."""
+    ids, cnt = W.skewed_ids(300_000, 9_000, seed=81, giant=50_000)
+    data = ScatterData(ids.to(DEV), cnt.to(DEV))
+    a = W.features(300_000, 128, 82).to(DEV)
+    b = W.features(300_000, 128, 83).to(DEV)
+    want_a, want_b = scatter_sum(a, data), scatter_max(b, data)[0]
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(DEV), torch.cuda.Stream(DEV)
+    got_a, got_b = [], []
+    for _ in range(10):
+        with torch.cuda.stream(s1):
+            got_a.append(scatter_sum(a, data))
+        with torch.cuda.stream(s2):
+            got_b.append(scatter_max(b, data)[0])
+    torch.cuda.synchronize()
+    assert all(torch.equal(g, want_a) for g in got_a)
+    assert all(torch.equal(g, want_b) for g in got_b)
+    assert len(data._workspaces) >= 3
