@@ -49,12 +49,17 @@ int texb_version(void);
  * (torchex/src/scatter/scatter_kernel.cu:173-192). */
 const char* texb_last_error(void);
 
-/* Number of bounded device-side waits that expired since the library was
- * loaded on the current device (0 in a healthy process).  The reduce kernels
- * wait for their bulk copies with an iteration limit; when it runs out they
- * count the event here and return instead of hanging.  Synchronises with the
- * device.  No counterpart in the reference. */
-int texb_device_status(int* wait_timeouts);
+/* Health counters of the current device since the library was loaded (both 0
+ * in a healthy process; either pointer may be NULL).  Synchronises with the
+ * device.  No counterpart in the reference.
+ *   wait_timeouts: bounded device-side waits that expired.  The reduce kernels
+ *     wait for their bulk copies with an iteration limit; when it runs out they
+ *     count the event and return instead of hanging.
+ *   bad_indices: indices found outside their range in a plan handed to the
+ *     reduce kernels (a perm entry outside [0, n), a segment id outside
+ *     [0, num_segments), a balance cut outside [0, n]).  The access is skipped or
+ *     redirected and counted instead of faulting; the output is then wrong. */
+int texb_device_status(int* wait_timeouts, int* bad_indices);
 
 /* Tuning knobs for experiments: "rows_per_cta" (0 = one wave of CTAs),
  * "staged" (0 register kernel, 1 cp.async ring, 2 bulk-copy ring),

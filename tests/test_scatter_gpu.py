@@ -445,3 +445,35 @@ def test_same_plan_on_two_streams():
     assert all(torch.equal(g, want_a) for g in got_a)
     assert all(torch.equal(g, want_b) for g in got_b)
     assert len(data._workspaces) >= 3
+
+
+def test_corrupt_plan_indices_are_skipped_and_counted():
+    """A plan with an out-of-range row, segment id or balance cut must not touch
+    memory outside the buffers: the kernels redirect or skip the access and count
+    it (texb_device_status), so the call returns and the context stays usable."""
+    lib = _native.lib()
+    n, c, m = 50_000, 128, 2_000
+    ids, cnt = W.skewed_ids(n, m, seed=91, giant=8_000)
+    data = ScatterData(ids.to(DEV), cnt.to(DEV))
+    feat = W.features(n, c, 92).to(DEV)
+    before = _native.device_bad_indices()
+    sid, perm, bal = data.sid.clone(), data.perm.clone(), data.balance.clone()
+    perm[1234] = n + 7
+    perm[40_000] = -3
+    sid[777] = m + 3
+    bal[5] = n + 100
+    out = torch.zeros((m, c), device=DEV)
+    arg = torch.zeros((m, c), dtype=torch.int32, device=DEV)
+    ws = torch.empty(lib.texb_reduce_workspace_bytes(n, c), dtype=torch.uint8, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    for op in (_native.OP_SUM, _native.OP_MAX):
+        st = lib.texb_segment_reduce(op, feat.data_ptr(), sid.data_ptr(), perm.data_ptr(), data.preSum.data_ptr(), 0,
+                                     bal.data_ptr(), bal.numel(), n, c, m, out.data_ptr(), arg.data_ptr(), 0,
+                                     ws.data_ptr(), ws.numel(), stream)
+        assert st == 0, _native.last_error()
+    torch.cuda.synchronize()
+    assert _native.device_bad_indices() > before
+    # the library still works afterwards
+    good = scatter_sum(feat, data)
+    s64, _ = O.spec_scatter_sum_f64(feat.cpu(), ids, m)
+    assert O.within_tolerance(good.cpu().numpy(), s64, REL, ABS).all()

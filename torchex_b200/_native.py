@@ -20,7 +20,7 @@ _SIGNATURES = {
     # name: (restype, argtypes)
     "texb_version": (_c.c_int, []),
     "texb_last_error": (_c.c_char_p, []),
-    "texb_device_status": (_c.c_int, [_c.POINTER(_c.c_int)]),
+    "texb_device_status": (_c.c_int, [_c.POINTER(_c.c_int), _c.POINTER(_c.c_int)]),
     "texb_tune_set": (_c.c_int, [_c.c_char_p, _c.c_int]),
     "texb_tune_get": (_c.c_int, [_c.c_char_p]),
     "texb_ids_inspect": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_int64, _c.c_void_p, _c.c_void_p]),
@@ -103,7 +103,14 @@ def check(status: int, what: str) -> None:
 def device_wait_timeouts() -> int:
     """Bounded device-side waits that expired on the current device (0 when healthy)."""
     v = _c.c_int(0)
-    check(lib().texb_device_status(_c.byref(v)), "texb_device_status")
+    check(lib().texb_device_status(_c.byref(v), None), "texb_device_status")
+    return v.value
+
+
+def device_bad_indices() -> int:
+    """Out-of-range plan indices the reduce kernels skipped on the current device (0 when healthy)."""
+    v = _c.c_int(0)
+    check(lib().texb_device_status(None, _c.byref(v)), "texb_device_status")
     return v.value
 
 

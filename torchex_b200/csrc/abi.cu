@@ -32,7 +32,7 @@ int segment_reduce_static_impl(int, const float*, const int32_t*, const int32_t*
                                const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, int32_t,
                                cudaStream_t);
 size_t static_scratch_bytes_impl();
-int device_status_impl(int*);
+int device_status_impl(int*, int*);
 int expand_offsets_impl(const int32_t*, int32_t*, int64_t, int64_t, cudaStream_t);
 int sum_backward_impl(const float*, const int32_t*, const int32_t*, float*, int64_t, int, int64_t,
                       cudaStream_t);
@@ -158,7 +158,9 @@ int texb_tune_get(const char* key) {
   return -1;
 }
 
-int texb_device_status(int* wait_timeouts) { return device_status_impl(wait_timeouts); }
+int texb_device_status(int* wait_timeouts, int* bad_indices) {
+  return device_status_impl(wait_timeouts, bad_indices);
+}
 
 int texb_ids_inspect(const void* ids, int id_bytes, int64_t n, int32_t* stats_dev, void* stream) {
   return ids_inspect_impl(ids, id_bytes, n, stats_dev, static_cast<cudaStream_t>(stream));

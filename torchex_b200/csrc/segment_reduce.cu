@@ -240,12 +240,29 @@ __device__ __forceinline__ void load_state(const uint32_t* pa, const uint32_t* p
   Op::template unpack<VEC>(x, wa, wb);
 }
 
+// Where results go besides the pointers: the offset added to reported rows and the
+// number of output rows, against which every segment id is checked before a store.
+struct OutSpec {
+  int arg_base;
+  int num_segments;
+};
+
+// Number of indices found outside their range (a row of `perm` outside [0, n), a
+// segment id outside [0, num_segments), a cut of the balance table outside [0, n]).
+// Such an index comes from a corrupt plan; the access is skipped and counted here
+// (sticky; read with texb_device_status) instead of faulting the GPU.
+__device__ int g_bad_indices = 0;
+
 // Writes one finished segment row.  `ch` is this lane's first channel.
 template <class Op, int VEC>
 __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __restrict__ arg,
                                        int seg, int C, int ch, bool lane_on,
                                        const typename Op::template State<VEC>& x, int cnt, bool mean,
-                                       int arg_base) {
+                                       OutSpec ospec) {
+  if (unsigned(seg) >= unsigned(ospec.num_segments)) {
+    if (ch == 0) atomicAdd(&g_bad_indices, 1);
+    return;
+  }
   if (!lane_on) return;
   float r[VEC];
 #pragma unroll
@@ -266,9 +283,9 @@ __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __re
     if constexpr (VEC == 4) {
       int ix[VEC];
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) {  // rows are reported relative to arg_base; "no row" stays -1
+      for (int k = 0; k < VEC; ++k) {  // rows are reported relative to ospec; "no row" stays -1
         const int i = Op::template index<VEC>(x, k);
-        ix[k] = i < 0 ? i : i + arg_base;
+        ix[k] = i < 0 ? i : i + ospec.arg_base;
       }
       *reinterpret_cast<int4*>(pa) = make_int4(ix[0], ix[1], ix[2], ix[3]);
     } else if constexpr (VEC == 8) {
@@ -276,7 +293,7 @@ __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __re
 #pragma unroll
       for (int k = 0; k < VEC; ++k) {
         const int i = Op::template index<VEC>(x, k);
-        ix[k] = i < 0 ? i : i + arg_base;
+        ix[k] = i < 0 ? i : i + ospec.arg_base;
       }
       reinterpret_cast<int4*>(pa)[0] = make_int4(ix[0], ix[1], ix[2], ix[3]);
       reinterpret_cast<int4*>(pa)[1] = make_int4(ix[4], ix[5], ix[6], ix[7]);
@@ -284,7 +301,7 @@ __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __re
 #pragma unroll
       for (int k = 0; k < VEC; ++k) {
         const int i = Op::template index<VEC>(x, k);
-        pa[k] = i < 0 ? i : i + arg_base;
+        pa[k] = i < 0 ? i : i + ospec.arg_base;
       }
     }
   }
@@ -294,13 +311,17 @@ __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __re
 // the operator so that NaN / -inf rows keep the (-FLT_MAX, -1) answer.
 template <class Op, int VEC>
 __device__ __forceinline__ void store_single(float* __restrict__ out, int32_t* __restrict__ arg, int seg,
-                                             int C, int ch, bool lane_on, const float (&v)[VEC], int row, int arg_base) {
+                                             int C, int ch, bool lane_on, const float (&v)[VEC], int row, OutSpec ospec) {
   if constexpr (Op::kIsMax) {
     typename Op::template State<VEC> x;
     Op::template init<VEC>(x);
     Op::template add<VEC>(x, v, row);
-    store_out<Op, VEC>(out, arg, seg, C, ch, lane_on, x, 1, false, arg_base);
+    store_out<Op, VEC>(out, arg, seg, C, ch, lane_on, x, 1, false, ospec);
   } else {
+    if (unsigned(seg) >= unsigned(ospec.num_segments)) {
+      if (ch == 0) atomicAdd(&g_bad_indices, 1);
+      return;
+    }
     if (!lane_on) return;
     float* po = out + int64_t(seg) * C + ch;
     if constexpr (VEC == 4) {
@@ -339,7 +360,7 @@ template <class Op, int VEC, int LPR>
 __device__ __forceinline__ void stitch_cta(const uint32_t* s_vec, const int* s_sid, const int* s_cnt,
                                            const unsigned* s_flag, float* __restrict__ out,
                                            int32_t* __restrict__ arg, Workspace ws, int C, int ch,
-                                           bool lane_on, int lane_g, int group, bool mean, int arg_base,
+                                           bool lane_on, int lane_g, int group, bool mean, OutSpec ospec,
                                            unsigned t_start = 0u) {
   using State = typename Op::template State<VEC>;
   constexpr int GPC = kCtaThreads / LPR;
@@ -370,7 +391,7 @@ __device__ __forceinline__ void stitch_cta(const uint32_t* s_vec, const int* s_s
     }
     if (!(f & kOpenRight)) {
       if (!cur_open_left) {
-        store_out<Op, VEC>(out, arg, cur_sid, C, ch, lane_on, cur, cur_cnt, mean, arg_base);
+        store_out<Op, VEC>(out, arg, cur_sid, C, ch, lane_on, cur, cur_cnt, mean, ospec);
       } else {
         uint32_t* ga = ws.vec + rec * 2 * CPS + lane_g * VEC;
         store_state<Op, VEC>(ga, ga + CPS, cur);
@@ -414,6 +435,11 @@ __device__ __forceinline__ void group_range(const Split& sp, int n, int group, i
     g0 = min(c0 + group * sp.rows_per_group, c1);
     g1 = min(g0 + sp.rows_per_group, c1);
   }
+  // cuts of a corrupt balance table are pulled back into [0, n], in order
+  const int lo = min(max(g0, 0), n), hi = min(max(g1, lo), n);
+  if ((lo != g0 || hi != g1) && (threadIdx.x & 31) == 0) atomicAdd(&g_bad_indices, 1);
+  g0 = lo;
+  g1 = hi;
 }
 
 // ---- register kernel ------------------------------------------------------------
@@ -423,7 +449,7 @@ __global__ void __launch_bounds__(kCtaThreads)
 segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict__ sid,
                       const int32_t* __restrict__ perm, float* __restrict__ out,
                       int32_t* __restrict__ arg, Workspace ws, int n, int C,
-                      Split sp, bool mean, int arg_base) {
+                      Split sp, bool mean, OutSpec ospec) {
   using State = typename Op::template State<VEC>;
   constexpr int GPC = kCtaThreads / LPR;           // groups per CTA
   constexpr int CPS = LPR * VEC;                   // channels per slab
@@ -473,7 +499,7 @@ segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict
     auto close_run = [&](bool open_right) {
       const bool open_left = is_first && first_open_left;
       if (!open_left && !open_right) {
-        store_out<Op, VEC>(out, arg, cur_sid, C, ch, lane_on, acc, cnt, mean, arg_base);
+        store_out<Op, VEC>(out, arg, cur_sid, C, ch, lane_on, acc, cnt, mean, ospec);
       } else {
         const int slot = 2 * group + (open_right ? 1 : 0);
         uint32_t* pa = s_vec + slot * 2 * CPS + lane_g * VEC;
@@ -492,6 +518,10 @@ segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict
       if (p < g1) {
         my_sid = __ldg(sid + p);
         my_row = HAS_PERM ? __ldg(perm + p) : p;
+        if (HAS_PERM && unsigned(my_row) >= unsigned(n)) {  // corrupt plan: read row 0 instead, and say so
+          my_row = 0;
+          atomicAdd(&g_bad_indices, 1);
+        }
       }
 #pragma unroll 1
       for (int j = 0; j < LPR; j += U) {
@@ -530,7 +560,7 @@ segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict
   }
   __syncthreads();
   stitch_cta<Op, VEC, LPR>(s_vec, s_sid, s_cnt, s_flag, out, arg, ws, C, ch, lane_on, lane_g,
-                           group, mean, arg_base);
+                           group, mean, ospec);
 }
 
 // ---- staged kernel --------------------------------------------------------------
@@ -634,7 +664,7 @@ __global__ void __launch_bounds__(kCtaThreads, 2)
 segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __restrict__ sid,
                              const int32_t* __restrict__ perm, float* __restrict__ out,
                              int32_t* __restrict__ arg, Workspace ws, int n, int C,
-                             Split sp, bool mean, int arg_base) {
+                             Split sp, bool mean, OutSpec ospec) {
   constexpr int VEC = 16 / sizeof(In);  // channels in the 16 bytes a lane owns: 4 fp32 or 8 bf16
   using State = typename Op::template State<VEC>;
   constexpr int GPC = kCtaThreads / LPR;
@@ -720,6 +750,10 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
         m_sid[r] = in ? __ldg(sid + p) : -1;
         const int nxt = (in && p + 1 < n) ? __ldg(sid + p + 1) : -2;
         m_row[r] = HAS_PERM ? (in ? __ldg(perm + p) : 0) : p;
+        if (HAS_PERM && unsigned(m_row[r]) >= unsigned(n)) {  // corrupt plan: read row 0 instead, and say so
+          m_row[r] = 0;
+          atomicAdd(&g_bad_indices, 1);
+        }
         const unsigned bal = __ballot_sync(gmask, in && (m_sid[r] != nxt));
         m_mask |= ((bal >> lane_base) & ((LPR == 32) ? 0xffffffffu : ((1u << LPR) - 1u))) << (r * LPR);
       }
@@ -796,7 +830,7 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
     auto close_run = [&](int sid_now, int cnt, bool open_right) {
       const bool open_left = is_first && first_open_left;
       if (!open_left && !open_right) {
-        store_out<Op, VEC>(out, arg, sid_now, C, ch, lane_on, acc, cnt, mean, arg_base);
+        store_out<Op, VEC>(out, arg, sid_now, C, ch, lane_on, acc, cnt, mean, ospec);
       } else {
         const int slot = 2 * group + (open_right ? 1 : 0);
         uint32_t* pa = s_vec + slot * 2 * CPS + lane_g * VEC;
@@ -814,7 +848,7 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
       unpack_lane<In, VEC>(t4, v);
       if (single) {
         const int sid_now = __shfl_sync(gmask, sids_reg, lane_k, LPR);
-        store_single<Op, VEC>(out, arg, sid_now, C, ch, lane_on, v, row, arg_base);
+        store_single<Op, VEC>(out, arg, sid_now, C, ch, lane_on, v, row, ospec);
         is_first = false;
         run_start = q + 1;
       } else {
@@ -915,7 +949,7 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
   if constexpr (!BULK) cp_async_wait<0>();
   __syncthreads();
   stitch_cta<Op, VEC, LPR>(s_vec, s_sid, s_cnt, s_flag, out, arg, ws, C, ch, lane_on, lane_g,
-                           group, mean, arg_base, t_start);
+                           group, mean, ospec, t_start);
 }
 
 // ---- fix-up kernel --------------------------------------------------------------
@@ -927,7 +961,7 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
 template <class Op, int VEC, int LPR>
 __global__ void __launch_bounds__(kCtaThreads)
 segment_fixup_kernel(Workspace ws, float* __restrict__ out, int32_t* __restrict__ arg,
-                     int num_ctas, int C, bool mean, int arg_base) {
+                     int num_ctas, int C, bool mean, OutSpec ospec) {
   using State = typename Op::template State<VEC>;
   constexpr int GPC = kCtaThreads / LPR;
   constexpr int CPS = LPR * VEC;
@@ -1010,7 +1044,7 @@ segment_fixup_kernel(Workspace ws, float* __restrict__ out, int32_t* __restrict_
       Op::template merge<VEC>(acc, x);
       cnt += s_cnt[g];
     }
-    store_out<Op, VEC>(out, arg, m0.x, C, ch, lane_on, acc, cnt, mean, arg_base);
+    store_out<Op, VEC>(out, arg, m0.x, C, ch, lane_on, acc, cnt, mean, ospec);
   }
 }
 
@@ -1136,6 +1170,7 @@ struct Call {
   const int32_t* balance;
   int balance_k;
   int arg_base;
+  int m;
 };
 
 // Resident CTAs per SM of one kernel instantiation (asked once per process).
@@ -1181,11 +1216,11 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<const In*>(c.feats), c.sid, c.perm, c.out,
-                                       c.arg, ws, c.n, c.C, s, c.mean, c.arg_base);
+                                       c.arg, ws, c.n, c.C, s, c.mean, OutSpec{c.arg_base, c.m});
     if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "segment reduce launch: %s", cudaGetErrorString(e));
   } else {
     kernel<<<grid, kCtaThreads, dyn_smem, c.stream>>>(static_cast<const In*>(c.feats), c.sid, c.perm, c.out,
-                                                      c.arg, ws, c.n, c.C, s, c.mean, c.arg_base);
+                                                      c.arg, ws, c.n, c.C, s, c.mean, OutSpec{c.arg_base, c.m});
   }
   int st = check_launch("segment reduce kernel");
   if (st != TEXB_OK || s.num_ctas <= 1) return st;
@@ -1202,12 +1237,12 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, segment_fixup_kernel<Op, VEC, LPR>, ws, c.out, c.arg,
-                                       s.num_ctas, c.C, c.mean, c.arg_base);
+                                       s.num_ctas, c.C, c.mean, OutSpec{c.arg_base, c.m});
     if (e != cudaSuccess)
       return fail(TEXB_ERR_CUDA, "segment_fixup_kernel launch: %s", cudaGetErrorString(e));
   } else {
     segment_fixup_kernel<Op, VEC, LPR><<<grid, kCtaThreads, 0, c.stream>>>(ws, c.out, c.arg, s.num_ctas,
-                                                                           c.C, c.mean, c.arg_base);
+                                                                           c.C, c.mean, OutSpec{c.arg_base, c.m});
   }
   return check_launch("segment_fixup_kernel");
 }
@@ -1318,7 +1353,7 @@ int segment_reduce_impl(int op, const void* feats, int in_bytes, const int32_t* 
   if (balance && balance_len < 2)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "balance table needs at least 2 entries");
   Call c = {feats, sid, perm, out, arg, workspace, workspace_bytes, int(n), C, op == TEXB_OP_MEAN, stream,
-            balance, balance ? balance_len - 1 : 0, int(arg_base)};
+            balance, balance ? balance_len - 1 : 0, int(arg_base), int(m)};
   if (op == TEXB_OP_MAX) return dispatch_layout<OpMax>(g, c);
   if (tuning().compensated) return dispatch_layout<OpSumComp>(g, c);
   return dispatch_layout<OpSumPlain>(g, c);
@@ -1382,11 +1417,13 @@ int segment_reduce_static_impl(int op, const float* feats, const int32_t* sid, c
                              arg, arg_base, scratch, kStaticScratchBytes, stream);
 }
 
-int device_status_impl(int* wait_timeouts) {
-  int v = 0;
+int device_status_impl(int* wait_timeouts, int* bad_indices) {
+  int v = 0, w = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, g_wait_timeouts, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(&w, g_bad_indices, sizeof(int));
   if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "cudaMemcpyFromSymbol: %s", cudaGetErrorString(e));
   if (wait_timeouts) *wait_timeouts = v;
+  if (bad_indices) *bad_indices = w;
   return TEXB_OK;
 }
 
