@@ -537,8 +537,8 @@ def run_reference(args):
     O.cpu_forward_step(feat, index_full, m)
     t_full = time.perf_counter() - t
     total_steps = args.steps + max(args.warmup, 1)
-    budget = 120.0 / total_steps
-    frac = min(1.0, budget / t_full)
+    per_step_s = 120.0 / total_steps
+    frac = min(1.0, per_step_s / t_full)
     n_s = max(1000, int(n * frac))
     f_s, i_s = feat[:n_s].contiguous(), ids[:n_s, None].expand(-1, c)
     m_s = m

@@ -3,8 +3,9 @@
 // Work is split by ROWS of the segment-sorted order, never by segments, so a
 // 100 000-row segment and 100 000 one-row segments cost the same:
 //
-//   * a CTA owns `rows_per_cta` consecutive sorted positions (by default the
-//     rows are divided evenly over exactly one resident wave of CTAs); inside it
+//   * a CTA owns a range of consecutive sorted positions (by default the rows are
+//     divided over exactly one resident wave of CTAs, cut by the plan's balance
+//     table so that every group gets the same estimated cost); inside it
 //     every "group" of LPR lanes (LPR * VEC channels wide, one 128-bit access per
 //     lane when VEC == 4) owns a consecutive sub-range and walks it row by row,
 //     keeping one running accumulator per channel;
@@ -15,10 +16,12 @@
 //   * runs that cross a CTA edge go to a small workspace (two records per CTA)
 //     and the fix-up kernel stitches those chains, again in position order.
 //
-// Two walkers share that skeleton.  The staged kernel (rows of 64..128 channels
-// per slab) streams rows with cp.async into a per-lane ring in shared memory,
-// two batches ahead of the batch being reduced; the register kernel (every other
-// layout) keeps eight row loads in flight in registers.
+// Two walkers share that skeleton.  The staged kernel (fp32 or bf16 rows of 16 or
+// 32 sixteen-byte lanes) streams rows into a ring in shared memory with bulk
+// copies (or cp.async), batches ahead of the batch being reduced; the register
+// kernel (every other layout) keeps eight row loads in flight in registers.
+// Both are programmatic dependent launches, as is the fix-up kernel, so in a
+// sequence of reductions each grid is placed while the previous one drains.
 //
 // Sums carry an error-free compensation term (TwoSum) through every add and
 // every merge, so a 175 000-row segment stays within a few ulp of the exact sum.
