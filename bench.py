@@ -47,10 +47,10 @@ HBM_FALLBACK_GBS = 6650.0         # earlier copy measurement on this pool, used 
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 543_200_000
 
 
-def algorithmic_bytes(n, c, m):
+def algorithmic_bytes(n, c, m, feature_bytes=4):
     """Bytes one launch must move: features, one int32 per point, one offset per
-    segment, the output rows (max also writes the int32 argmax rows)."""
-    b_sum = 4 * n * c + 4 * n + 4 * (m + 1) + 4 * m * c
+    segment, the fp32 output rows (max also writes the int32 argmax rows)."""
+    b_sum = feature_bytes * n * c + 4 * n + 4 * (m + 1) + 4 * m * c
     return {"sum": b_sum, "mean": b_sum, "max": b_sum + 4 * m * c}
 
 
@@ -160,9 +160,14 @@ def run_ours(args):
                     f"(Zipf 1.2 sizes + one {n // 10:,}-point segment), ids randomly permuted; "
                     "step = scatter_sum + scatter_mean + scatter_max forward with a prebuilt plan"
                     + ("" if (n, c, m) == (N_POINTS, CHANNELS, N_SEGMENTS) else " [reduced size, for profiling only]"))
-    bytes_op = algorithmic_bytes(n, c, m)
+    bf16 = args.features == "bf16"
+    if bf16:
+        workload = workload.replace("fp32", "bf16 features, fp32 accumulation and output", 1) + " [secondary workload]"
+    bytes_op = algorithmic_bytes(n, c, m, 2 if bf16 else 4)
     bytes_step = sum(bytes_op.values())
     feat = W.features(n, c, SEED + rank, device=dev)
+    if bf16:
+        feat = feat.to(torch.bfloat16)
     data = ScatterData(ids.to(dev), cnt.to(dev))
     outs = {k: torch.empty((m, c), device=dev) for k in ("sum", "mean", "max")}
     arg = torch.empty((m, c), dtype=torch.int32, device=dev)
@@ -171,11 +176,12 @@ def run_ours(args):
     perm_ptr = None if data.perm is None else data.perm.data_ptr()
     ops = {"sum": _native.OP_SUM, "mean": _native.OP_MEAN, "max": _native.OP_MAX}
 
+    entry = lib.texb_segment_reduce_bf16 if bf16 else lib.texb_segment_reduce
+
     def reduce(name):
-        st = lib.texb_segment_reduce(ops[name], feat.data_ptr(), data.sid.data_ptr(), perm_ptr,
-                                     data.preSum.data_ptr(), 0, data.balance.data_ptr(), data.balance.numel(),
-                                     n, c, m, outs[name].data_ptr(), arg.data_ptr(), 0, ws.data_ptr(), ws.numel(),
-                                     stream)
+        st = entry(ops[name], feat.data_ptr(), data.sid.data_ptr(), perm_ptr,
+                   data.preSum.data_ptr(), 0, data.balance.data_ptr(), data.balance.numel(),
+                   n, c, m, outs[name].data_ptr(), arg.data_ptr(), 0, ws.data_ptr(), ws.numel(), stream)
         if st != 0:
             raise RuntimeError(_native.last_error())
 
@@ -247,18 +253,18 @@ def run_ours(args):
     in_stream_us = per_op["sum"]["us"]
     achieved = bytes_op["sum"] / in_stream_us / 1e3
     bracketed = bytes_op["sum"] / (sum_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "segment_reduce_staged_kernel<sum> + segment_fixup_kernel (one launch pair)",
+    roofline = {"bound": "hbm", "kernel": f"segment_reduce_staged_kernel<sum, {args.features}> + segment_fixup_kernel (one launch pair)",
                 "achieved": round(achieved, 1), "peak": peak, "peak_source": f"hbm_gbs of {peak_kind} copy",
                 "unit": "GB/s", "frac": round(achieved / peak, 4), "frac_of_nominal_8000": round(achieved / HBM_NOMINAL_GBS, 4),
                 "algorithmic_bytes_per_launch": bytes_op["sum"], "us_per_launch": in_stream_us,
                 "bracketed_in_timed_region": {"us_per_launch": round(sum_ms * 1e3, 2), "launches": len(ev_sum),
                                               "achieved": round(bracketed, 1), "frac": round(bracketed / peak, 4)},
                 "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (n, c, m) == (N_POINTS, CHANNELS, N_SEGMENTS)
-                and args.workload == "skewed" else None}
+                and args.workload == "skewed" and not bf16 else None}
 
     # ---- end to end through the public operators, host buffers in pinned memory
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and not bf16:  # the end-to-end leg is the fp32 headline's
         h_feat = feat.cpu().pin_memory()
         h_ids = ids.pin_memory()
         h_cnt = cnt.pin_memory()
@@ -342,7 +348,7 @@ def run_ours(args):
 
     # ---- host CPU baseline (rank 0, single-GPU run only)
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not bf16:
         cpu = cpu_baseline(feat.cpu(), ids, m, bytes_step, reps=3)
 
     if rank == 0:
@@ -637,6 +643,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--workload", choices=["skewed", "voxel"], default="skewed",
                     help="skewed = the headline configuration; voxel = concatenated dynamic-voxelisation frames")
+    ap.add_argument("--features", choices=["fp32", "bf16"], default="fp32",
+                    help="bf16: the same reductions on bf16 feature rows (secondary; the headline is fp32)")
     ap.add_argument("--frames", type=int, default=4, help="frames of the voxel workload")
     ap.add_argument("--points", type=int, default=N_POINTS, help="reduced sizes are for profiling only")
     ap.add_argument("--segments", type=int, default=N_SEGMENTS)

@@ -41,6 +41,29 @@
 
 #include "common.cuh"
 
+// Build-time shape of the staged walker's inner loops (override with -D to experiment).
+//
+// TEXB_SLOW_UNROLL: rows of a batch WITH run ends that are expanded inline per trip.
+//   Every expanded row carries its own copy of the code that closes a run (the
+//   division for the mean, the stores, the parking of an edge run).  Expanded
+//   eight times that code no longer fits the instruction cache: the bf16 kernel
+//   ran at an 80-86 % instruction-cache hit rate and 134 / 182 us (sum / mean)
+//   on 1 M skewed rows; expanded twice the same kernel takes 105 / 113 us and
+//   the fp32 kernels are unchanged to within noise.
+// TEXB_FAST_UNROLL: rows of a batch WITHOUT run ends expanded inline (no such code).
+// TEXB_PACKED_F32X2: TwoSum on channel pairs with the packed fp32x2 instructions
+//   (bit-identical to the scalar form; 1 M skewed rows: bf16 sum 81.5 -> 75.1 us,
+//   fp32 sum 97.7 -> 96.0 us, 500 k rows of short segments 59.1 -> 55.7 us).
+#ifndef TEXB_SLOW_UNROLL
+#define TEXB_SLOW_UNROLL 2
+#endif
+#ifndef TEXB_FAST_UNROLL
+#define TEXB_FAST_UNROLL 8
+#endif
+#ifndef TEXB_PACKED_F32X2
+#define TEXB_PACKED_F32X2 1
+#endif
+
 namespace texb {
 namespace {
 
@@ -66,8 +89,31 @@ struct OpSumComp {  // fp32 sum + error-free two-sum: (s, c) with s + c the exac
     const float bp = t - s;
     e = (s - (t - bp)) + (v - bp);
   }
+  // The same TwoSum on two channels at once with the packed fp32x2 instructions of
+  // sm_100 (each half rounds exactly like the scalar instruction, so the result is
+  // bit-identical); a - b is written fma(b, -1, a), which rounds a - b once.
+  static __device__ __forceinline__ void two_sum2(float2 s, float2 v, float2& t, float2& e) {
+    const float2 m1 = make_float2(-1.f, -1.f);
+    t = __fadd2_rn(s, v);
+    const float2 bp = __ffma2_rn(s, m1, t);                 // t - s
+    const float2 a = __ffma2_rn(__ffma2_rn(bp, m1, t), m1, s);  // s - (t - bp)
+    e = __fadd2_rn(a, __ffma2_rn(bp, m1, v));               // + (v - bp)
+  }
   template <int VEC>
   static __device__ __forceinline__ void add(State<VEC>& x, const float (&v)[VEC], int) {
+#if TEXB_PACKED_F32X2
+    if constexpr (VEC % 2 == 0) {
+#pragma unroll
+      for (int k = 0; k < VEC; k += 2) {
+        float2 t, e;
+        two_sum2(make_float2(x.s[k], x.s[k + 1]), make_float2(v[k], v[k + 1]), t, e);
+        const float2 c = __fadd2_rn(make_float2(x.c[k], x.c[k + 1]), e);
+        x.s[k] = t.x; x.s[k + 1] = t.y;
+        x.c[k] = c.x; x.c[k + 1] = c.y;
+      }
+      return;
+    }
+#endif
 #pragma unroll
     for (int k = 0; k < VEC; ++k) {
       float t, e;
@@ -639,15 +685,24 @@ __device__ __forceinline__ void mbar_wait_bounded(unsigned bar, unsigned parity)
 }
 
 constexpr int kStageBatch = 8;    // rows per copy batch
-// Batches in the ring.  fp32 rows: three (two in flight, one being reduced).  bf16
-// rows carry eight channels per lane, which doubles the shared memory of the
-// edge-run slots, so their ring has two batches to keep two CTAs per SM.
-template <class In> constexpr int kStageDepthFor = (sizeof(In) == 4) ? 3 : 2;
 constexpr int kStageTile = 32;    // positions per metadata tile
-constexpr int kStageSlotBytes = kCtaThreads * 16;  // one row slot for the whole CTA
-template <class In> constexpr int kStageRingBytesFor = kStageBatch * kStageDepthFor<In> * kStageSlotBytes;
+// A lane owns LB bytes of every row: 16 (4 fp32 or 8 bf16 channels) or 8 (4 bf16
+// channels, so that a 128-channel bf16 row spans a whole warp like its fp32 twin).
+// Batches in the ring: fp32 rows three (two in flight, one being reduced); bf16
+// rows with 16-byte lanes carry eight channels per lane, which doubles the shared
+// memory of the edge-run slots, so their ring has two batches to keep two CTAs per
+// SM; bf16 rows with 8-byte lanes are half as wide, and three batches (48 KB) let
+// three CTAs share an SM (measured: 82 us against 92 us with four batches and two CTAs).
+template <class In, int LB> constexpr int kStageDepthFor = (sizeof(In) == 4) ? 3 : (LB == 16 ? 2 : 3);
+template <int LB> constexpr int kStageSlotBytesFor = kCtaThreads * LB;  // one row slot for the whole CTA
+template <class In, int LB>
+constexpr int kStageRingBytesFor = kStageBatch * kStageDepthFor<In, LB> * kStageSlotBytesFor<LB>;
 
-// The 16 bytes a lane owns of a row, as fp32 channels.
+template <int LB> struct LaneWord;
+template <> struct LaneWord<16> { using type = float4; };
+template <> struct LaneWord<8> { using type = float2; };
+
+// The bytes a lane owns of a row, as fp32 channels.
 template <class In, int VEC>
 __device__ __forceinline__ void unpack_lane(const float4& t4, float (&v)[VEC]) {
   if constexpr (sizeof(In) == 4) {
@@ -661,19 +716,32 @@ __device__ __forceinline__ void unpack_lane(const float4& t4, float (&v)[VEC]) {
     }
   }
 }
+template <class In, int VEC>
+__device__ __forceinline__ void unpack_lane(const float2& t2, float (&v)[VEC]) {
+  static_assert(sizeof(In) == 2 && VEC == 4, "8-byte lanes hold four bf16 channels");
+  const unsigned w[2] = {__float_as_uint(t2.x), __float_as_uint(t2.y)};
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    v[2 * k] = __uint_as_float(w[k] << 16);
+    v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+  }
+}
 
-template <class Op, class In, int LPR, bool HAS_PERM, bool BULK>
+template <class Op, class In, int LB, int LPR, bool HAS_PERM, bool BULK>
 __global__ void __launch_bounds__(kCtaThreads, 2)
 segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __restrict__ sid,
                              const int32_t* __restrict__ perm, float* __restrict__ out,
                              int32_t* __restrict__ arg, Workspace ws, int n, int C,
                              Split sp, bool mean, OutSpec ospec) {
-  constexpr int VEC = 16 / sizeof(In);  // channels in the 16 bytes a lane owns: 4 fp32 or 8 bf16
+  constexpr int VEC = LB / sizeof(In);  // channels in the bytes a lane owns: 4 fp32, 8 or 4 bf16
   using State = typename Op::template State<VEC>;
+  using Word = typename LaneWord<LB>::type;
   constexpr int GPC = kCtaThreads / LPR;
   constexpr int CPS = LPR * VEC;
   constexpr int SLOTS = 2 * GPC;
-  constexpr int B = kStageBatch, S = kStageDepthFor<In>, T = kStageTile;
+  constexpr int B = kStageBatch, S = kStageDepthFor<In, LB>, T = kStageTile;
+  constexpr int kStageSlotBytes = kStageSlotBytesFor<LB>;
+  static_assert(BULK || LB == 16, "the cp.async ring copies 16 bytes per lane");
   constexpr int NREG = T / LPR;  // tile positions held per lane
   static_assert(LPR == 16 || LPR == 32, "staged kernel handles 16 or 32 lanes per row");
   static_assert(S >= 2 && (S - 1) * B <= T && T % B == 0 && LPR % B == 0, "the copy front must stay within two tiles");
@@ -728,15 +796,15 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
     const In* lane_src = feats + (lane_on ? ch : 0);
     // cp.async layout: slot s of the CTA at s * kStageSlotBytes, lane t at + 16 t.
     // Bulk layout: each group owns S * B consecutive row slabs of kRowBytes.
-    constexpr int kRowBytes = LPR * 16;
-    constexpr int kSlotFloat4 = BULK ? LPR : kCtaThreads;  // float4 stride between slots
+    constexpr int kRowBytes = LPR * LB;
+    constexpr int kSlotFloat4 = BULK ? LPR : kCtaThreads;  // stride between slots, in lane words
     const int row_bytes = min(CPS, C - blockIdx.y * CPS) * int(sizeof(In));  // the last slab may be narrower
     const unsigned ring_addr = BULK
         ? unsigned(__cvta_generic_to_shared(s_dyn)) + unsigned(group * S * B) * kRowBytes
         : unsigned(__cvta_generic_to_shared(s_dyn)) + threadIdx.x * 16;
-    const float4* ring = BULK
-        ? reinterpret_cast<const float4*>(s_dyn) + group * S * B * LPR + lane_g
-        : reinterpret_cast<const float4*>(s_dyn) + threadIdx.x;
+    const Word* ring = BULK
+        ? reinterpret_cast<const Word*>(s_dyn) + group * S * B * LPR + lane_g
+        : reinterpret_cast<const Word*>(s_dyn) + threadIdx.x;
     const unsigned bar0 = unsigned(__cvta_generic_to_shared(&s_bar[BULK ? group * S : 0]));
     const In* slab_src = feats + blockIdx.y * CPS;
     const unsigned long long stream_policy = BULK ? l2_policy(sp.stream_hint != 0) : 0ull;
@@ -846,7 +914,7 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
       }
     };
     // One row of a batch that holds run ends.  `single`: the row is a whole segment.
-    auto row_step = [&](int q, const float4& t4, int row, bool end_k, bool single, int sids_reg, int lane_k) {
+    auto row_step = [&](int q, const Word& t4, int row, bool end_k, bool single, int sids_reg, int lane_k) {
       float v[VEC];
       unpack_lane<In, VEC>(t4, v);
       if (single) {
@@ -893,7 +961,7 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
         cp_async_wait<S - 1>();  // batch b has landed (groups complete in order)
       }
 
-      const float4* src = ring + stage_c * B * kSlotFloat4;
+      const Word* src = ring + stage_c * B * kSlotFloat4;
       stage_c = (stage_c + 1 == S) ? 0 : stage_c + 1;
       const unsigned ends = (cur_mask >> j0) & ((1u << B) - 1u);
       int rows_reg = 0;
@@ -902,9 +970,10 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
       if (q0 + B <= L) {
         if (ends == 0u) {
           // eight rows of one run: no bookkeeping
-#pragma unroll
+          constexpr int FU = TEXB_FAST_UNROLL;
+#pragma unroll FU
           for (int k = 0; k < B; ++k) {
-            const float4 t4 = src[k * kSlotFloat4];
+            const Word t4 = src[k * kSlotFloat4];
             float v[VEC];
             unpack_lane<In, VEC>(t4, v);
             int row = g0 + q0 + k;
@@ -917,15 +986,20 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
           const int sids_reg = tile_reg(cur_sid_r, j0);
           const unsigned singles = ends & ((ends << 1) | carry);  // rows that start and end a run
           carry = (ends >> (B - 1)) & 1u;
-          float4 t4[B];
+          constexpr int U = TEXB_SLOW_UNROLL;
+#pragma unroll 1
+          for (int k0 = 0; k0 < B; k0 += U) {
+            Word t4[U];
 #pragma unroll
-          for (int k = 0; k < B; ++k) t4[k] = src[k * kSlotFloat4];
+            for (int u = 0; u < U; ++u) t4[u] = src[(k0 + u) * kSlotFloat4];
 #pragma unroll
-          for (int k = 0; k < B; ++k) {
-            int row = g0 + q0 + k;
-            if constexpr (Op::kIsMax && HAS_PERM) row = __shfl_sync(gmask, rows_reg, (j0 & (LPR - 1)) + k, LPR);
-            row_step(q0 + k, t4[k], row, ((ends >> k) & 1u) != 0u, ((singles >> k) & 1u) != 0u, sids_reg,
-                     (j0 & (LPR - 1)) + k);
+            for (int u = 0; u < U; ++u) {
+              const int k = k0 + u;
+              int row = g0 + q0 + k;
+              if constexpr (Op::kIsMax && HAS_PERM) row = __shfl_sync(gmask, rows_reg, (j0 & (LPR - 1)) + k, LPR);
+              row_step(q0 + k, t4[u], row, ((ends >> k) & 1u) != 0u, ((singles >> k) & 1u) != 0u, sids_reg,
+                       (j0 & (LPR - 1)) + k);
+            }
           }
         }
       } else {
@@ -935,7 +1009,7 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
         const unsigned singles = ends & ((ends << 1) | carry);
 #pragma unroll 1
         for (int k = 0; k < nv; ++k) {
-          const float4 t4 = src[k * kSlotFloat4];
+          const Word t4 = src[k * kSlotFloat4];
           int row = g0 + q0 + k;
           if constexpr (Op::kIsMax && HAS_PERM) row = __shfl_sync(gmask, rows_reg, (j0 & (LPR - 1)) + k, LPR);
           row_step(q0 + k, t4, row, ((ends >> k) & 1u) != 0u, ((singles >> k) & 1u) != 0u, sids_reg,
@@ -982,7 +1056,12 @@ segment_fixup_kernel(Workspace ws, float* __restrict__ out, int32_t* __restrict_
 
   const int b = blockIdx.x;
   const int64_t rec_base = int64_t(blockIdx.y) * num_ctas;
+  // The first window of head records is fetched together with this CTA's own tail
+  // record, so a chain start pays one trip to L2 before it knows where it ends.
   const int4 m0 = ws.meta[(rec_base + b) * 2 + 1];
+  const int first = b + 1 + threadIdx.x;
+  int4 mh = make_int4(0, 0, 0, 0);
+  if (first < num_ctas) mh = ws.meta[(rec_base + first) * 2];
   const unsigned f0 = unsigned(m0.z);
   if (!(f0 & kValid) || !(f0 & kOpenRight) || (f0 & kOpenLeft)) return;  // block-uniform
 
@@ -991,10 +1070,8 @@ segment_fixup_kernel(Workspace ws, float* __restrict__ out, int32_t* __restrict_
   __syncthreads();
   for (int base = b + 1; base < num_ctas; base += kCtaThreads) {
     const int idx = base + threadIdx.x;
-    if (idx < num_ctas) {
-      const int4 mh = ws.meta[(rec_base + idx) * 2];
-      if (unsigned(mh.z) & kValid) atomicMin(&s_last, idx);
-    }
+    if (base != b + 1 && idx < num_ctas) mh = ws.meta[(rec_base + idx) * 2];
+    if (idx < num_ctas && (unsigned(mh.z) & kValid)) atomicMin(&s_last, idx);
     __syncthreads();
     if (s_last < num_ctas) break;  // uniform: s_last was read after the barrier
     __syncthreads();
@@ -1084,6 +1161,7 @@ __global__ void expand_offsets_kernel(const int32_t* __restrict__ offsets, int32
 
 struct Layout {
   int in_bytes;  // 4: fp32 features, 2: bf16 features (staged kernel only)
+  int lane_bytes;  // bytes of a row one lane owns: vec * in_bytes
   int vec, lpr, cps, num_slabs, gpc;
   int staged;  // 0: register kernel, 1: cp.async ring, 2: bulk-copy (TMA) ring; 128-bit lanes, 16 or 32 lanes per row
 };
@@ -1101,7 +1179,10 @@ Layout make_layout(int C, bool allow_vec4, int in_bytes = 4) {
   Layout g;
   g.in_bytes = in_bytes;
   g.vec = (allow_vec4 && C % 4 == 0) ? 4 : 1;
-  if (in_bytes == 2) g.vec = 8;  // the caller has checked C % 8 == 0 and the alignment
+  // bf16 (the caller has checked C % 8 == 0 and the alignment): rows of up to 128
+  // channels take 8-byte lanes so that one row spans a warp; wider rows 16-byte lanes.
+  if (in_bytes == 2) g.vec = (C <= 128) ? 4 : 8;
+  g.lane_bytes = g.vec * in_bytes;
   const int lanes = C / g.vec;
   int lpr = 1;
   while (lpr < lanes && lpr < 32) lpr <<= 1;
@@ -1251,10 +1332,10 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
 }
 
 // Staged walkers (cp.async or bulk-copy ring) for one input type.
-template <class Op, class In, int LPR, bool HAS_PERM>
+template <class Op, class In, int LB, int LPR, bool HAS_PERM>
 int launch_staged(const Layout& g, const Call& c) {
-  constexpr int VEC = 16 / sizeof(In);
-  constexpr int kRing = kStageRingBytesFor<In>;
+  constexpr int VEC = LB / sizeof(In);
+  constexpr int kRing = kStageRingBytesFor<In, LB>;
   // The shared-memory attribute is per device: set it on every call (a host-side table write).
   auto staged_launch = [&](auto kernel, int* resident) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);
@@ -1262,18 +1343,20 @@ int launch_staged(const Layout& g, const Call& c) {
     if (*resident == 0) *resident = resident_ctas(kernel, kRing);
     return launch_pair<Op, In, VEC, LPR>(kernel, kRing, *resident, g, c);
   };
-  if (g.staged == 2) {
-    static int resident = 0;
-    return staged_launch(segment_reduce_staged_kernel<Op, In, LPR, HAS_PERM, true>, &resident);
+  if constexpr (LB == 16) {
+    if (g.staged != 2) {
+      static int resident = 0;
+      return staged_launch(segment_reduce_staged_kernel<Op, In, LB, LPR, HAS_PERM, false>, &resident);
+    }
   }
   static int resident = 0;
-  return staged_launch(segment_reduce_staged_kernel<Op, In, LPR, HAS_PERM, false>, &resident);
+  return staged_launch(segment_reduce_staged_kernel<Op, In, LB, LPR, HAS_PERM, true>, &resident);
 }
 
 template <class Op, int VEC, int LPR, bool HAS_PERM>
 int launch_reduce(const Layout& g, const Call& c) {
   if constexpr (VEC == 4 && (LPR == 16 || LPR == 32)) {
-    if (g.staged) return launch_staged<Op, float, LPR, HAS_PERM>(g, c);
+    if (g.staged) return launch_staged<Op, float, 16, LPR, HAS_PERM>(g, c);
   }
   auto kernel = segment_reduce_kernel<Op, VEC, LPR, HAS_PERM>;
   static const int resident = resident_ctas(kernel, 0);
@@ -1289,10 +1372,11 @@ int dispatch_perm(const Layout& g, const Call& c) {
 template <class Op>
 int dispatch_layout(const Layout& g, const Call& c) {
   if (g.in_bytes == 2) {
-    if (g.lpr == 16)
-      return c.perm ? launch_staged<Op, __nv_bfloat16, 16, true>(g, c) : launch_staged<Op, __nv_bfloat16, 16, false>(g, c);
-    if (g.lpr == 32)
-      return c.perm ? launch_staged<Op, __nv_bfloat16, 32, true>(g, c) : launch_staged<Op, __nv_bfloat16, 32, false>(g, c);
+    using H = __nv_bfloat16;
+    if (g.lane_bytes == 8 && g.lpr == 32)
+      return c.perm ? launch_staged<Op, H, 8, 32, true>(g, c) : launch_staged<Op, H, 8, 32, false>(g, c);
+    if (g.lane_bytes == 16 && g.lpr == 32)
+      return c.perm ? launch_staged<Op, H, 16, 32, true>(g, c) : launch_staged<Op, H, 16, 32, false>(g, c);
     return fail(TEXB_ERR_UNSUPPORTED, "bf16 features need at least 128 channels (got %d lanes per row)", g.lpr);
   }
   if (g.vec == 4) {
