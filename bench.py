@@ -433,7 +433,23 @@ def other_configs(dev):
         nbytes = algorithmic_bytes(n, c, m)[name] - 2 * n * c
         res[name] = {"us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1), "Mpoints_per_s": round(n / us, 1)}
     table["skewed_1m_c128_bf16"] = res
-    del feat16, data, out, arg
+    # mean and max + argmax of the headline workload from ONE pass over the features
+    # (texb_segment_reduce_pair), fp32 and bf16 rows; bytes: features, ids, offsets, three outputs
+    out2 = torch.empty((m, c), device=dev)
+    ws2 = torch.empty(lib.texb_reduce_pair_workspace_bytes(n, c), dtype=torch.uint8, device=dev)
+    feat32 = feat16.float()
+    pair = {"points": n, "channels": c, "segments": m,
+            "note": "scatter_mean + scatter_max (+ argmax) of the same rows in one pass"}
+    for label, f in (("fp32", feat32), ("bf16", feat16)):
+        us = timed(lambda: lib.texb_segment_reduce_pair(_native.OP_MEAN, f.data_ptr(), f.element_size(),
+                                                        data.sid.data_ptr(), data.perm.data_ptr(),
+                                                        data.preSum.data_ptr(), 0, data.balance.data_ptr(),
+                                                        data.balance.numel(), n, c, m, out2.data_ptr(), out.data_ptr(),
+                                                        arg.data_ptr(), 0, ws2.data_ptr(), ws2.numel(), stream), 50)
+        nbytes = algorithmic_bytes(n, c, m, f.element_size())["max"] + 4 * m * c
+        pair[label] = {"us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1), "Mpoints_per_s": round(n / us, 1)}
+    table["skewed_1m_c128_mean_max_pair"] = pair
+    del feat16, feat32, data, out, out2, arg
     ids, cnt = W.uniform_ids(20_000, 2_000, SEED)
     table["uniform_20k_c16"], _, _ = forward(ids, cnt, W.features(20_000, 16, SEED, device=dev), "c1",
                                              "1.3 MB of features: L2-resident and launch-bound")

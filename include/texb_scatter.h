@@ -213,6 +213,28 @@ int texb_segment_reduce_bf16(int op, const void* feats_bf16, const int32_t* sid,
                              int32_t arg_base, void* workspace,
                              size_t workspace_bytes, void* stream);
 
+/* Sum (or mean) AND maximum of the same rows in one pass over feats: dynamic
+ * voxel encoders pool the same point features both ways, and two calls of
+ * texb_segment_reduce would read feats twice.  No counterpart in the
+ * reference, which runs ScatterMeanFunction and ScatterMaxFunction one after
+ * the other (torchex/operator_py/scatter_op.py:56-103).
+ *   op           : TEXB_OP_SUM or TEXB_OP_MEAN, written to out_sum[num_segments, channel];
+ *   out_max, arg : as out / arg of TEXB_OP_MAX;
+ *   feature_bytes: 4 (feats is fp32) or 2 (bf16; channel a multiple of 8, from
+ *                  128 channels, and at most 128 -- wider bf16 rows: convert);
+ *   workspace    : texb_reduce_pair_workspace_bytes(n, channel) bytes.
+ * Each output is bit-identical to what the single-output call writes when both
+ * use the same split of the rows (they do by default for fp32 rows). */
+size_t texb_reduce_pair_workspace_bytes(int64_t n, int channel);
+int texb_segment_reduce_pair(int op, const void* feats, int feature_bytes,
+                             const int32_t* sid, const int32_t* perm,
+                             const int32_t* offsets, int has_empty,
+                             const int32_t* balance, int balance_len, int64_t n,
+                             int channel, int64_t num_segments, float* out_sum,
+                             float* out_max, int32_t* arg, int32_t arg_base,
+                             void* workspace, size_t workspace_bytes,
+                             void* stream);
+
 /* texb_segment_reduce for callers that cannot allocate device memory.
  * No counterpart in the reference.
  *
@@ -301,6 +323,16 @@ int texb_scatter_max_backward(const float* g, const int32_t* arg,
                               const int32_t* ids, const int32_t* perm,
                               float* g_in, int64_t n, int channel,
                               int64_t num_segments, void* stream);
+
+/* Backward of texb_segment_reduce_pair with TEXB_OP_MEAN: the sum of the two
+ * expressions above, g_in[row_i, c] = g_mean[ids[i], c] / count(ids[i]) +
+ * ((arg[ids[i], c] == row_i) ? g_max[ids[i], c] : 0), in one pass that writes
+ * g_in once. */
+int texb_scatter_mean_max_backward(const float* g_mean, const float* g_max,
+                                   const int32_t* arg, const int32_t* ids,
+                                   const int32_t* perm, const int32_t* offsets,
+                                   float* g_in, int64_t n, int channel,
+                                   int64_t num_segments, void* stream);
 
 #ifdef __cplusplus
 }

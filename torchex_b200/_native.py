@@ -45,6 +45,11 @@ _SIGNATURES = {
                                             _c.c_int, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int, _c.c_int64,
                                             _c.c_void_p, _c.c_void_p, _c.c_int32, _c.c_void_p, _c.c_size_t,
                                             _c.c_void_p]),
+    "texb_reduce_pair_workspace_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int]),
+    "texb_segment_reduce_pair": (_c.c_int, [_c.c_int, _c.c_void_p, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                            _c.c_int, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int, _c.c_int64,
+                                            _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int32, _c.c_void_p,
+                                            _c.c_size_t, _c.c_void_p]),
     "texb_static_scratch_bytes": (_c.c_size_t, []),
     "texb_segment_reduce_static": (_c.c_int, [_c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                               _c.c_int, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int, _c.c_int64,
@@ -61,6 +66,9 @@ _SIGNATURES = {
                                               _c.c_int64, _c.c_int, _c.c_int64, _c.c_void_p]),
     "texb_scatter_max_backward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                              _c.c_int64, _c.c_int, _c.c_int64, _c.c_void_p]),
+    "texb_scatter_mean_max_backward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                                  _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int, _c.c_int64,
+                                                  _c.c_void_p]),
 }
 
 OP_SUM, OP_MEAN, OP_MAX = 0, 1, 2

@@ -18,9 +18,10 @@ int plan_build_impl(const void*, int, int64_t, int64_t, int, int32_t*, int32_t*,
                     void*, size_t, cudaStream_t);
 int get_pre_sum_impl(const int32_t*, int32_t*, int64_t, int64_t, cudaStream_t);
 size_t reduce_workspace_bytes_impl(int64_t, int);
+size_t reduce_pair_workspace_bytes_impl(int64_t, int);
 int segment_reduce_impl(int, const void*, int, const int32_t*, const int32_t*, const int32_t*, int,
                         const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, int32_t, void*,
-                        size_t, cudaStream_t);
+                        size_t, cudaStream_t, float* out_sum = nullptr);
 int plan_balance_impl(const int32_t*, int64_t, int32_t*, int, cudaStream_t);
 size_t unique_workspace_bytes_impl(int64_t);
 int unique_count_impl(const void*, int, int64_t, int64_t, int, int32_t*, int32_t*, int32_t*, void*, size_t,
@@ -40,6 +41,8 @@ int mean_backward_impl(const float*, const int32_t*, const int32_t*, const int32
                        int64_t, cudaStream_t);
 int max_backward_impl(const float*, const int32_t*, const int32_t*, const int32_t*, float*, int64_t, int,
                       int64_t, cudaStream_t);
+int mean_max_backward_impl(const float*, const float*, const int32_t*, const int32_t*, const int32_t*,
+                           const int32_t*, float*, int64_t, int, int64_t, cudaStream_t);
 
 namespace {
 thread_local char t_error[512] = "";
@@ -236,6 +239,23 @@ int texb_segment_reduce_bf16(int op, const void* feats_bf16, const int32_t* sid,
                              static_cast<cudaStream_t>(stream));
 }
 
+size_t texb_reduce_pair_workspace_bytes(int64_t n, int channel) {
+  if (n < 0 || channel < 1) return 0;
+  return reduce_pair_workspace_bytes_impl(n, channel);
+}
+
+int texb_segment_reduce_pair(int op, const void* feats, int feature_bytes, const int32_t* sid,
+                             const int32_t* perm, const int32_t* offsets, int has_empty,
+                             const int32_t* balance, int balance_len, int64_t n, int channel,
+                             int64_t num_segments, float* out_sum, float* out_max, int32_t* arg,
+                             int32_t arg_base, void* workspace, size_t workspace_bytes, void* stream) {
+  if (num_segments > 0 && !out_sum) return fail(TEXB_ERR_INVALID_ARGUMENT, "out_sum is NULL");
+  if (num_segments == 0) return TEXB_OK;
+  return segment_reduce_impl(op, feats, feature_bytes, sid, perm, offsets, has_empty, balance, balance_len, n,
+                             channel, num_segments, out_max, arg, arg_base, workspace, workspace_bytes,
+                             static_cast<cudaStream_t>(stream), out_sum);
+}
+
 size_t texb_static_scratch_bytes(void) { return static_scratch_bytes_impl(); }
 
 int texb_segment_reduce_static(int op, const float* feats, const int32_t* sid, const int32_t* perm,
@@ -310,6 +330,14 @@ int texb_scatter_max_backward(const float* g, const int32_t* arg, const int32_t*
                               int64_t num_segments, void* stream) {
   return max_backward_impl(g, arg, ids, perm, g_in, n, channel, num_segments,
                            static_cast<cudaStream_t>(stream));
+}
+
+int texb_scatter_mean_max_backward(const float* g_mean, const float* g_max, const int32_t* arg,
+                                   const int32_t* ids, const int32_t* perm, const int32_t* offsets,
+                                   float* g_in, int64_t n, int channel, int64_t num_segments,
+                                   void* stream) {
+  return mean_max_backward_impl(g_mean, g_max, arg, ids, perm, offsets, g_in, n, channel, num_segments,
+                                static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

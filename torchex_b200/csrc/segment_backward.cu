@@ -3,6 +3,8 @@
 //   sum : g_in[i, :] = g[sid_i, :]
 //   mean: g_in[i, :] = g[sid_i, :] / count(sid_i)
 //   max : g_in[i, c] = (arg[sid_i, c] == i) ? g[sid_i, c] : 0
+//   mean + max (the two-output forward): the sum of the mean and max expressions,
+//         from g (gradient of the means) and g2 (gradient of the maxima)
 //
 // Lanes run along the channel axis (128-bit accesses when the layout allows),
 // a group of lanes handles eight consecutive entries of `ids` per step, and g_in
@@ -21,7 +23,7 @@
 namespace texb {
 namespace {
 
-constexpr int kModeSum = 0, kModeMean = 1, kModeMax = 2;
+constexpr int kModeSum = 0, kModeMean = 1, kModeMax = 2, kModeMeanMax = 3;
 constexpr int kRowsPerStep = 4;
 
 template <int VEC>
@@ -91,7 +93,7 @@ __device__ __forceinline__ void load_meta(StepMeta& mt, int64_t e0, const int32_
     }
     mt.row[k] = r;
   }
-  if constexpr (MODE == kModeMean) {
+  if constexpr (MODE == kModeMean || MODE == kModeMeanMax) {
 #pragma unroll
     for (int k = 0; k < kRowsPerStep; ++k) {
       mt.den[k] = 1;
@@ -102,7 +104,7 @@ __device__ __forceinline__ void load_meta(StepMeta& mt, int64_t e0, const int32_
 
 template <int MODE, int VEC, int LPR>
 __global__ void __launch_bounds__(kCtaThreads, 4)
-broadcast_back_kernel(const float* __restrict__ g, const int32_t* __restrict__ arg,
+broadcast_back_kernel(const float* __restrict__ g, const float* __restrict__ g2, const int32_t* __restrict__ arg,
                       const int32_t* __restrict__ ids, const int32_t* __restrict__ perm,
                       const int32_t* __restrict__ offsets, float* __restrict__ g_in, int64_t n, int C,
                       int64_t m) {
@@ -130,7 +132,14 @@ broadcast_back_kernel(const float* __restrict__ g, const int32_t* __restrict__ a
             for (int q = 0; q < VEC; ++q)
               if (a.v[q] != cur.row[k]) val[k].v[q] = 0.f;
           }
-          if constexpr (MODE == kModeMean) divide_by_count<VEC>(val[k].v, cur.den[k]);
+          if constexpr (MODE == kModeMean || MODE == kModeMeanMax) divide_by_count<VEC>(val[k].v, cur.den[k]);
+          if constexpr (MODE == kModeMeanMax) {
+            const Pack<VEC> gm = load_f<VEC>(g2 + int64_t(cur.s[k]) * C + ch);
+            const PackI<VEC> a = load_i<VEC>(arg + int64_t(cur.s[k]) * C + ch);
+#pragma unroll
+            for (int q = 0; q < VEC; ++q)
+              if (a.v[q] == cur.row[k]) val[k].v[q] += gm.v[q];
+          }
         } else {
 #pragma unroll
           for (int q = 0; q < VEC; ++q) val[k].v[q] = 0.f;
@@ -146,13 +155,13 @@ broadcast_back_kernel(const float* __restrict__ g, const int32_t* __restrict__ a
 }
 
 template <int MODE, int VEC>
-int launch_lpr(int lpr, const float* g, const int32_t* arg, const int32_t* ids, const int32_t* perm,
+int launch_lpr(int lpr, const float* g, const float* g2, const int32_t* arg, const int32_t* ids, const int32_t* perm,
                const int32_t* offsets, float* g_in, int64_t n, int C, int64_t m,
                cudaStream_t stream) {
   const int gpc = kCtaThreads / lpr;
   const unsigned blocks = unsigned(ceil_div(n, int64_t(gpc) * kRowsPerStep * kStepsPerGroup));
 #define TEXB_LAUNCH(L)                                                                   \
-  broadcast_back_kernel<MODE, VEC, L><<<blocks, kCtaThreads, 0, stream>>>(g, arg, ids,   \
+  broadcast_back_kernel<MODE, VEC, L><<<blocks, kCtaThreads, 0, stream>>>(g, g2, arg, ids, \
                                                                          perm, offsets, g_in, n, C, m)
   switch (lpr) {
     case 1: TEXB_LAUNCH(1); break;
@@ -167,35 +176,42 @@ int launch_lpr(int lpr, const float* g, const int32_t* arg, const int32_t* ids, 
 }
 
 template <int MODE>
-int launch_back(const float* g, const int32_t* arg, const int32_t* ids, const int32_t* perm,
+int launch_back(const float* g, const float* g2, const int32_t* arg, const int32_t* ids, const int32_t* perm,
                 const int32_t* offsets, float* g_in, int64_t n, int C, int64_t m, cudaStream_t stream) {
   if (n < 0 || m < 0 || C < 1) return fail(TEXB_ERR_INVALID_ARGUMENT, "backward: bad sizes");
   if (n == 0) return TEXB_OK;
-  if (!g_in || !ids || (m > 0 && !g) || (MODE == kModeMax && m > 0 && !arg) ||
-      (MODE == kModeMean && !offsets))
+  constexpr bool kArg = MODE == kModeMax || MODE == kModeMeanMax;
+  constexpr bool kDen = MODE == kModeMean || MODE == kModeMeanMax;
+  if (!g_in || !ids || (m > 0 && !g) || (kArg && m > 0 && !arg) || (kDen && !offsets) ||
+      (MODE == kModeMeanMax && m > 0 && !g2))
     return fail(TEXB_ERR_INVALID_ARGUMENT, "backward: NULL pointer");
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
-  const bool vec4 = (C % 4 == 0) && al(g) && al(g_in) && (MODE != kModeMax || al(arg));
+  const bool vec4 = (C % 4 == 0) && al(g) && al(g_in) && (!kArg || al(arg)) && (MODE != kModeMeanMax || al(g2));
   const int vec = vec4 ? 4 : 1;
   int lpr = 1;
   while (lpr < C / vec && lpr < 32) lpr <<= 1;
-  if (vec4) return launch_lpr<MODE, 4>(lpr, g, arg, ids, perm, offsets, g_in, n, C, m, stream);
-  return launch_lpr<MODE, 1>(lpr, g, arg, ids, perm, offsets, g_in, n, C, m, stream);
+  if (vec4) return launch_lpr<MODE, 4>(lpr, g, g2, arg, ids, perm, offsets, g_in, n, C, m, stream);
+  return launch_lpr<MODE, 1>(lpr, g, g2, arg, ids, perm, offsets, g_in, n, C, m, stream);
 }
 
 }  // namespace
 
 int sum_backward_impl(const float* g, const int32_t* ids, const int32_t* perm, float* g_in, int64_t n,
                       int C, int64_t m, cudaStream_t stream) {
-  return launch_back<kModeSum>(g, nullptr, ids, perm, nullptr, g_in, n, C, m, stream);
+  return launch_back<kModeSum>(g, nullptr, nullptr, ids, perm, nullptr, g_in, n, C, m, stream);
 }
 int mean_backward_impl(const float* g, const int32_t* ids, const int32_t* perm, const int32_t* offsets,
                        float* g_in, int64_t n, int C, int64_t m, cudaStream_t stream) {
-  return launch_back<kModeMean>(g, nullptr, ids, perm, offsets, g_in, n, C, m, stream);
+  return launch_back<kModeMean>(g, nullptr, nullptr, ids, perm, offsets, g_in, n, C, m, stream);
 }
 int max_backward_impl(const float* g, const int32_t* arg, const int32_t* ids, const int32_t* perm,
                       float* g_in, int64_t n, int C, int64_t m, cudaStream_t stream) {
-  return launch_back<kModeMax>(g, arg, ids, perm, nullptr, g_in, n, C, m, stream);
+  return launch_back<kModeMax>(g, nullptr, arg, ids, perm, nullptr, g_in, n, C, m, stream);
+}
+int mean_max_backward_impl(const float* g_mean, const float* g_max, const int32_t* arg, const int32_t* ids,
+                           const int32_t* perm, const int32_t* offsets, float* g_in, int64_t n, int C,
+                           int64_t m, cudaStream_t stream) {
+  return launch_back<kModeMeanMax>(g_mean, g_max, arg, ids, perm, offsets, g_in, n, C, m, stream);
 }
 
 }  // namespace texb

@@ -77,6 +77,8 @@ constexpr unsigned kOpenRight = 4u;  // segment continues after this range
 
 struct OpSumComp {  // fp32 sum + error-free two-sum: (s, c) with s + c the exact running sum
   static constexpr bool kIsMax = false;
+  static constexpr bool kHasSum = true;
+  static constexpr int kPlanes = 2;
   template <int VEC> struct State { float s[VEC]; float c[VEC]; };
   template <int VEC>
   static __device__ __forceinline__ void init(State<VEC>& x) {
@@ -133,14 +135,14 @@ struct OpSumComp {  // fp32 sum + error-free two-sum: (s, c) with s + c the exac
     }
   }
   template <int VEC>
-  static __device__ __forceinline__ void pack(const State<VEC>& x, uint32_t (&wa)[VEC], uint32_t (&wb)[VEC]) {
+  static __device__ __forceinline__ void pack(const State<VEC>& x, uint32_t (&w)[kPlanes][VEC]) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) { wa[k] = __float_as_uint(x.s[k]); wb[k] = __float_as_uint(x.c[k]); }
+    for (int k = 0; k < VEC; ++k) { w[0][k] = __float_as_uint(x.s[k]); w[1][k] = __float_as_uint(x.c[k]); }
   }
   template <int VEC>
-  static __device__ __forceinline__ void unpack(State<VEC>& x, const uint32_t (&wa)[VEC], const uint32_t (&wb)[VEC]) {
+  static __device__ __forceinline__ void unpack(State<VEC>& x, const uint32_t (&w)[kPlanes][VEC]) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) { x.s[k] = __uint_as_float(wa[k]); x.c[k] = __uint_as_float(wb[k]); }
+    for (int k = 0; k < VEC; ++k) { x.s[k] = __uint_as_float(w[0][k]); x.c[k] = __uint_as_float(w[1][k]); }
   }
   // An infinite running sum (infinite input or fp32 overflow) makes the error
   // term NaN; the sum itself is then the answer, as for a plain fp32 sum.
@@ -149,11 +151,15 @@ struct OpSumComp {  // fp32 sum + error-free two-sum: (s, c) with s + c the exac
     return (fabsf(x.s[k]) == INFINITY) ? x.s[k] : x.s[k] + x.c[k];
   }
   template <int VEC>
+  static __device__ __forceinline__ float sum_value(const State<VEC>& x, int k) { return value<VEC>(x, k); }
+  template <int VEC>
   static __device__ __forceinline__ int index(const State<VEC>&, int) { return 0; }
 };
 
 struct OpSumPlain {  // plain fp32 running sum (the "compensated" knob set to 0)
   static constexpr bool kIsMax = false;
+  static constexpr bool kHasSum = true;
+  static constexpr int kPlanes = 2;
   template <int VEC> struct State { float s[VEC]; };
   template <int VEC>
   static __device__ __forceinline__ void init(State<VEC>& x) {
@@ -171,17 +177,19 @@ struct OpSumPlain {  // plain fp32 running sum (the "compensated" knob set to 0)
     for (int k = 0; k < VEC; ++k) x.s[k] += y.s[k];
   }
   template <int VEC>
-  static __device__ __forceinline__ void pack(const State<VEC>& x, uint32_t (&wa)[VEC], uint32_t (&wb)[VEC]) {
+  static __device__ __forceinline__ void pack(const State<VEC>& x, uint32_t (&w)[kPlanes][VEC]) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) { wa[k] = __float_as_uint(x.s[k]); wb[k] = 0u; }
+    for (int k = 0; k < VEC; ++k) { w[0][k] = __float_as_uint(x.s[k]); w[1][k] = 0u; }
   }
   template <int VEC>
-  static __device__ __forceinline__ void unpack(State<VEC>& x, const uint32_t (&wa)[VEC], const uint32_t (&)[VEC]) {
+  static __device__ __forceinline__ void unpack(State<VEC>& x, const uint32_t (&w)[kPlanes][VEC]) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) x.s[k] = __uint_as_float(wa[k]);
+    for (int k = 0; k < VEC; ++k) x.s[k] = __uint_as_float(w[0][k]);
   }
   template <int VEC>
   static __device__ __forceinline__ float value(const State<VEC>& x, int k) { return x.s[k]; }
+  template <int VEC>
+  static __device__ __forceinline__ float sum_value(const State<VEC>& x, int k) { return x.s[k]; }
   template <int VEC>
   static __device__ __forceinline__ int index(const State<VEC>&, int) { return 0; }
 };
@@ -194,6 +202,8 @@ struct OpSumPlain {  // plain fp32 running sum (the "compensated" knob set to 0)
 // reports -FLT_MAX / -1, the reference's untouched state.  NaN and -inf never win.
 struct OpMax {
   static constexpr bool kIsMax = true;
+  static constexpr bool kHasSum = false;
+  static constexpr int kPlanes = 2;
   template <int VEC> struct State { float v[VEC]; int i[VEC]; };
   template <int VEC>
   static __device__ __forceinline__ void init(State<VEC>& x) {
@@ -213,14 +223,14 @@ struct OpMax {
       if (y.v[k] > x.v[k]) { x.v[k] = y.v[k]; x.i[k] = y.i[k]; }
   }
   template <int VEC>
-  static __device__ __forceinline__ void pack(const State<VEC>& x, uint32_t (&wa)[VEC], uint32_t (&wb)[VEC]) {
+  static __device__ __forceinline__ void pack(const State<VEC>& x, uint32_t (&w)[kPlanes][VEC]) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) { wa[k] = __float_as_uint(x.v[k]); wb[k] = uint32_t(x.i[k]); }
+    for (int k = 0; k < VEC; ++k) { w[0][k] = __float_as_uint(x.v[k]); w[1][k] = uint32_t(x.i[k]); }
   }
   template <int VEC>
-  static __device__ __forceinline__ void unpack(State<VEC>& x, const uint32_t (&wa)[VEC], const uint32_t (&wb)[VEC]) {
+  static __device__ __forceinline__ void unpack(State<VEC>& x, const uint32_t (&w)[kPlanes][VEC]) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) { x.v[k] = __uint_as_float(wa[k]); x.i[k] = int(wb[k]); }
+    for (int k = 0; k < VEC; ++k) { x.v[k] = __uint_as_float(w[0][k]); x.i[k] = int(w[1][k]); }
   }
   template <int VEC>
   static __device__ __forceinline__ float value(const State<VEC>& x, int k) {
@@ -228,6 +238,55 @@ struct OpMax {
   }
   template <int VEC>
   static __device__ __forceinline__ int index(const State<VEC>& x, int k) { return x.i[k]; }
+};
+
+// Sum (compensated) and maximum + row of the same rows in one pass: the state is
+// the two states side by side, and every step is the two operators' step.
+struct OpSumMax {
+  static constexpr bool kIsMax = true;
+  static constexpr bool kHasSum = true;
+  static constexpr int kPlanes = 4;
+  template <int VEC> struct State {
+    OpSumComp::State<VEC> sum;
+    OpMax::State<VEC> max;
+  };
+  template <int VEC>
+  static __device__ __forceinline__ void init(State<VEC>& x) {
+    OpSumComp::init<VEC>(x.sum);
+    OpMax::init<VEC>(x.max);
+  }
+  template <int VEC>
+  static __device__ __forceinline__ void add(State<VEC>& x, const float (&v)[VEC], int row) {
+    OpSumComp::add<VEC>(x.sum, v, row);
+    OpMax::add<VEC>(x.max, v, row);
+  }
+  template <int VEC>
+  static __device__ __forceinline__ void merge(State<VEC>& x, const State<VEC>& y) {
+    OpSumComp::merge<VEC>(x.sum, y.sum);
+    OpMax::merge<VEC>(x.max, y.max);
+  }
+  template <int VEC>
+  static __device__ __forceinline__ void pack(const State<VEC>& x, uint32_t (&w)[kPlanes][VEC]) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      w[0][k] = __float_as_uint(x.sum.s[k]); w[1][k] = __float_as_uint(x.sum.c[k]);
+      w[2][k] = __float_as_uint(x.max.v[k]); w[3][k] = uint32_t(x.max.i[k]);
+    }
+  }
+  template <int VEC>
+  static __device__ __forceinline__ void unpack(State<VEC>& x, const uint32_t (&w)[kPlanes][VEC]) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      x.sum.s[k] = __uint_as_float(w[0][k]); x.sum.c[k] = __uint_as_float(w[1][k]);
+      x.max.v[k] = __uint_as_float(w[2][k]); x.max.i[k] = int(w[3][k]);
+    }
+  }
+  template <int VEC>
+  static __device__ __forceinline__ float value(const State<VEC>& x, int k) { return OpMax::value<VEC>(x.max, k); }
+  template <int VEC>
+  static __device__ __forceinline__ int index(const State<VEC>& x, int k) { return x.max.i[k]; }
+  template <int VEC>
+  static __device__ __forceinline__ float sum_value(const State<VEC>& x, int k) { return OpSumComp::value<VEC>(x.sum, k); }
 };
 
 // ---- small device helpers -----------------------------------------------------
@@ -271,22 +330,23 @@ __device__ __forceinline__ void load_words(const uint32_t* p, uint32_t (&v)[VEC]
   }
 }
 
+// A state in memory: Op::kPlanes arrays ("planes") of `stride` words, this lane's VEC words at p.
 template <class Op, int VEC>
-__device__ __forceinline__ void store_state(uint32_t* pa, uint32_t* pb,
+__device__ __forceinline__ void store_state(uint32_t* p, int stride,
                                             const typename Op::template State<VEC>& x) {
-  uint32_t wa[VEC], wb[VEC];
-  Op::template pack<VEC>(x, wa, wb);
-  store_words<VEC>(pa, wa);
-  store_words<VEC>(pb, wb);
+  uint32_t w[Op::kPlanes][VEC];
+  Op::template pack<VEC>(x, w);
+#pragma unroll
+  for (int pl = 0; pl < Op::kPlanes; ++pl) store_words<VEC>(p + pl * stride, w[pl]);
 }
 
 template <class Op, int VEC>
-__device__ __forceinline__ void load_state(const uint32_t* pa, const uint32_t* pb,
+__device__ __forceinline__ void load_state(const uint32_t* p, int stride,
                                            typename Op::template State<VEC>& x) {
-  uint32_t wa[VEC], wb[VEC];
-  load_words<VEC>(pa, wa);
-  load_words<VEC>(pb, wb);
-  Op::template unpack<VEC>(x, wa, wb);
+  uint32_t w[Op::kPlanes][VEC];
+#pragma unroll
+  for (int pl = 0; pl < Op::kPlanes; ++pl) load_words<VEC>(p + pl * stride, w[pl]);
+  Op::template unpack<VEC>(x, w);
 }
 
 // Where results go besides the pointers: the offset added to reported rows and the
@@ -294,6 +354,7 @@ __device__ __forceinline__ void load_state(const uint32_t* pa, const uint32_t* p
 struct OutSpec {
   int arg_base;
   int num_segments;
+  float* out_sum;  // sum / mean rows of the two-output operator (its maxima go to `out`); else unused
 };
 
 // Number of indices found outside their range (a row of `perm` outside [0, n), a
@@ -301,6 +362,19 @@ struct OutSpec {
 // Such an index comes from a corrupt plan; the access is skipped and counted here
 // (sticky; read with texb_device_status) instead of faulting the GPU.
 __device__ int g_bad_indices = 0;
+
+template <int VEC>
+__device__ __forceinline__ void store_row(float* po, const float (&r)[VEC]) {
+  if constexpr (VEC == 4) {
+    *reinterpret_cast<float4*>(po) = make_float4(r[0], r[1], r[2], r[3]);
+  } else if constexpr (VEC == 8) {
+    reinterpret_cast<float4*>(po)[0] = make_float4(r[0], r[1], r[2], r[3]);
+    reinterpret_cast<float4*>(po)[1] = make_float4(r[4], r[5], r[6], r[7]);
+  } else {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) po[k] = r[k];
+  }
+}
 
 // Writes one finished segment row.  `ch` is this lane's first channel.
 template <class Op, int VEC>
@@ -313,19 +387,18 @@ __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __re
     return;
   }
   if (!lane_on) return;
-  float r[VEC];
+  if constexpr (Op::kHasSum) {  // sum or mean row: to `out`, or beside the maxima of the two-output operator
+    float r[VEC];
 #pragma unroll
-  for (int k = 0; k < VEC; ++k) r[k] = Op::template value<VEC>(x, k);
-  if (!Op::kIsMax && mean) divide_by_count<VEC>(r, cnt);
-  float* po = out + int64_t(seg) * C + ch;
-  if constexpr (VEC == 4) {
-    *reinterpret_cast<float4*>(po) = make_float4(r[0], r[1], r[2], r[3]);
-  } else if constexpr (VEC == 8) {
-    reinterpret_cast<float4*>(po)[0] = make_float4(r[0], r[1], r[2], r[3]);
-    reinterpret_cast<float4*>(po)[1] = make_float4(r[4], r[5], r[6], r[7]);
-  } else {
+    for (int k = 0; k < VEC; ++k) r[k] = Op::template sum_value<VEC>(x, k);
+    if (mean) divide_by_count<VEC>(r, cnt);
+    store_row<VEC>((Op::kIsMax ? ospec.out_sum : out) + int64_t(seg) * C + ch, r);
+  }
+  if constexpr (Op::kIsMax) {
+    float r[VEC];
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) po[k] = r[k];
+    for (int k = 0; k < VEC; ++k) r[k] = Op::template value<VEC>(x, k);
+    store_row<VEC>(out + int64_t(seg) * C + ch, r);
   }
   if constexpr (Op::kIsMax) {
     int32_t* pa = arg + int64_t(seg) * C + ch;
@@ -365,23 +438,14 @@ __device__ __forceinline__ void store_single(float* __restrict__ out, int32_t* _
     typename Op::template State<VEC> x;
     Op::template init<VEC>(x);
     Op::template add<VEC>(x, v, row);
-    store_out<Op, VEC>(out, arg, seg, C, ch, lane_on, x, 1, false, ospec);
+    store_out<Op, VEC>(out, arg, seg, C, ch, lane_on, x, 1, false, ospec);  // a mean over one row is the row
   } else {
     if (unsigned(seg) >= unsigned(ospec.num_segments)) {
       if (ch == 0) atomicAdd(&g_bad_indices, 1);
       return;
     }
     if (!lane_on) return;
-    float* po = out + int64_t(seg) * C + ch;
-    if constexpr (VEC == 4) {
-      *reinterpret_cast<float4*>(po) = make_float4(v[0], v[1], v[2], v[3]);
-    } else if constexpr (VEC == 8) {
-      reinterpret_cast<float4*>(po)[0] = make_float4(v[0], v[1], v[2], v[3]);
-      reinterpret_cast<float4*>(po)[1] = make_float4(v[4], v[5], v[6], v[7]);
-    } else {
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) po[k] = v[k];
-    }
+    store_row<VEC>(out + int64_t(seg) * C + ch, v);
   }
 }
 
@@ -390,7 +454,7 @@ __device__ __forceinline__ void store_single(float* __restrict__ out, int32_t* _
 // `a`, CPS words of `b` (CPS = LPR * VEC channels per slab) and an int4 of
 // meta {sid, row count, flags, 0}.
 struct Workspace {
-  uint32_t* vec;  // [num_slabs * num_ctas * 2][2 * CPS]
+  uint32_t* vec;  // [num_slabs * num_ctas * 2][planes of the operator * CPS]
   int4* meta;     // [num_slabs * num_ctas * 2]
 };
 
@@ -426,8 +490,8 @@ __device__ __forceinline__ void stitch_cta(const uint32_t* s_vec, const int* s_s
     const unsigned f = s_flag[slot];
     if (!(f & kValid)) continue;
     State x;
-    const uint32_t* pa = s_vec + slot * 2 * CPS + lane_g * VEC;
-    load_state<Op, VEC>(pa, pa + CPS, x);
+    const uint32_t* pa = s_vec + slot * Op::kPlanes * CPS + lane_g * VEC;
+    load_state<Op, VEC>(pa, CPS, x);
     if (!have) {
       cur = x;
       cur_sid = s_sid[slot];
@@ -442,8 +506,8 @@ __device__ __forceinline__ void stitch_cta(const uint32_t* s_vec, const int* s_s
       if (!cur_open_left) {
         store_out<Op, VEC>(out, arg, cur_sid, C, ch, lane_on, cur, cur_cnt, mean, ospec);
       } else {
-        uint32_t* ga = ws.vec + rec * 2 * CPS + lane_g * VEC;
-        store_state<Op, VEC>(ga, ga + CPS, cur);
+        uint32_t* ga = ws.vec + rec * Op::kPlanes * CPS + lane_g * VEC;
+        store_state<Op, VEC>(ga, CPS, cur);
         head_flag = kValid | kOpenLeft;
         if (lane_g == 0) ws.meta[rec] = make_int4(cur_sid, cur_cnt, int(head_flag), int(t_start));
       }
@@ -452,8 +516,8 @@ __device__ __forceinline__ void stitch_cta(const uint32_t* s_vec, const int* s_s
   }
   if (head_flag == 0u && lane_g == 0) ws.meta[rec] = make_int4(0, 0, 0, int(t_start));
   if (have) {
-    uint32_t* ga = ws.vec + (rec + 1) * 2 * CPS + lane_g * VEC;
-    store_state<Op, VEC>(ga, ga + CPS, cur);
+    uint32_t* ga = ws.vec + (rec + 1) * Op::kPlanes * CPS + lane_g * VEC;
+    store_state<Op, VEC>(ga, CPS, cur);
     const unsigned f = kValid | kOpenRight | (cur_open_left ? kOpenLeft : 0u);
     if (lane_g == 0) ws.meta[rec + 1] = make_int4(cur_sid, cur_cnt, int(f), int(global_timer_lo()));
   } else if (lane_g == 0) {
@@ -505,7 +569,7 @@ segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict
   constexpr int U = (LPR >= 8) ? 8 : LPR;          // row loads in flight per group
   constexpr int SLOTS = 2 * GPC;
 
-  __shared__ __align__(16) uint32_t s_vec[SLOTS * 2 * CPS];
+  __shared__ __align__(16) uint32_t s_vec[SLOTS * Op::kPlanes * CPS];
   __shared__ int s_sid[SLOTS];
   __shared__ int s_cnt[SLOTS];
   __shared__ unsigned s_flag[SLOTS];
@@ -551,8 +615,8 @@ segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict
         store_out<Op, VEC>(out, arg, cur_sid, C, ch, lane_on, acc, cnt, mean, ospec);
       } else {
         const int slot = 2 * group + (open_right ? 1 : 0);
-        uint32_t* pa = s_vec + slot * 2 * CPS + lane_g * VEC;
-        store_state<Op, VEC>(pa, pa + CPS, acc);
+        uint32_t* pa = s_vec + slot * Op::kPlanes * CPS + lane_g * VEC;
+        store_state<Op, VEC>(pa, CPS, acc);
         if (lane_g == 0) {
           s_sid[slot] = cur_sid;
           s_cnt[slot] = cnt;
@@ -693,10 +757,13 @@ constexpr int kStageTile = 32;    // positions per metadata tile
 // memory of the edge-run slots, so their ring has two batches to keep two CTAs per
 // SM; bf16 rows with 8-byte lanes are half as wide, and three batches (48 KB) let
 // three CTAs share an SM (measured: 82 us against 92 us with four batches and two CTAs).
-template <class In, int LB> constexpr int kStageDepthFor = (sizeof(In) == 4) ? 3 : (LB == 16 ? 2 : 3);
+// The two-output operator's edge-run slots are twice as large (four planes), so
+// its fp32 ring has two batches, again to keep two CTAs per SM.
+template <class In, int LB, int PLANES>
+constexpr int kStageDepthFor = (sizeof(In) == 4) ? (PLANES == 2 ? 3 : 2) : (LB == 16 ? 2 : (PLANES == 2 ? 3 : 4));
 template <int LB> constexpr int kStageSlotBytesFor = kCtaThreads * LB;  // one row slot for the whole CTA
-template <class In, int LB>
-constexpr int kStageRingBytesFor = kStageBatch * kStageDepthFor<In, LB> * kStageSlotBytesFor<LB>;
+template <class In, int LB, int PLANES>
+constexpr int kStageRingBytesFor = kStageBatch * kStageDepthFor<In, LB, PLANES> * kStageSlotBytesFor<LB>;
 
 template <int LB> struct LaneWord;
 template <> struct LaneWord<16> { using type = float4; };
@@ -739,7 +806,7 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
   constexpr int GPC = kCtaThreads / LPR;
   constexpr int CPS = LPR * VEC;
   constexpr int SLOTS = 2 * GPC;
-  constexpr int B = kStageBatch, S = kStageDepthFor<In, LB>, T = kStageTile;
+  constexpr int B = kStageBatch, S = kStageDepthFor<In, LB, Op::kPlanes>, T = kStageTile;
   constexpr int kStageSlotBytes = kStageSlotBytesFor<LB>;
   static_assert(BULK || LB == 16, "the cp.async ring copies 16 bytes per lane");
   constexpr int NREG = T / LPR;  // tile positions held per lane
@@ -747,7 +814,7 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
   static_assert(S >= 2 && (S - 1) * B <= T && T % B == 0 && LPR % B == 0, "the copy front must stay within two tiles");
 
   extern __shared__ __align__(16) unsigned char s_dyn[];  // the ring
-  __shared__ __align__(16) uint32_t s_vec[SLOTS * 2 * CPS];  // edge runs of the groups
+  __shared__ __align__(16) uint32_t s_vec[SLOTS * Op::kPlanes * CPS];  // edge runs of the groups
   __shared__ int s_sid[SLOTS];
   __shared__ int s_cnt[SLOTS];
   __shared__ unsigned s_flag[SLOTS];
@@ -904,8 +971,8 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
         store_out<Op, VEC>(out, arg, sid_now, C, ch, lane_on, acc, cnt, mean, ospec);
       } else {
         const int slot = 2 * group + (open_right ? 1 : 0);
-        uint32_t* pa = s_vec + slot * 2 * CPS + lane_g * VEC;
-        store_state<Op, VEC>(pa, pa + CPS, acc);
+        uint32_t* pa = s_vec + slot * Op::kPlanes * CPS + lane_g * VEC;
+        store_state<Op, VEC>(pa, CPS, acc);
         if (lane_g == 0) {
           s_sid[slot] = sid_now;
           s_cnt[slot] = cnt;
@@ -1043,7 +1110,7 @@ segment_fixup_kernel(Workspace ws, float* __restrict__ out, int32_t* __restrict_
   constexpr int GPC = kCtaThreads / LPR;
   constexpr int CPS = LPR * VEC;
 
-  __shared__ __align__(16) uint32_t s_vec[GPC * 2 * CPS];
+  __shared__ __align__(16) uint32_t s_vec[GPC * Op::kPlanes * CPS];
   __shared__ int s_cnt[GPC];
   __shared__ int s_last;
 
@@ -1099,8 +1166,8 @@ segment_fixup_kernel(Workspace ws, float* __restrict__ out, int32_t* __restrict_
     for (int u = 0; u < 4; ++u) {
       const int ii = min(i + u, i1 - 1);
       const int64_t rec = (rec_base + b + ii) * 2 + ((ii == K - 1) ? 0 : 1);
-      const uint32_t* ga = ws.vec + rec * 2 * CPS + lane_g * VEC;
-      load_state<Op, VEC>(ga, ga + CPS, x[u]);
+      const uint32_t* ga = ws.vec + rec * Op::kPlanes * CPS + lane_g * VEC;
+      load_state<Op, VEC>(ga, CPS, x[u]);
       c4[u] = ws.meta[rec].y;
     }
 #pragma unroll
@@ -1111,16 +1178,16 @@ segment_fixup_kernel(Workspace ws, float* __restrict__ out, int32_t* __restrict_
       }
     }
   }
-  uint32_t* pa = s_vec + group * 2 * CPS + lane_g * VEC;
-  store_state<Op, VEC>(pa, pa + CPS, acc);
+  uint32_t* pa = s_vec + group * Op::kPlanes * CPS + lane_g * VEC;
+  store_state<Op, VEC>(pa, CPS, acc);
   if (lane_g == 0) s_cnt[group] = cnt;
   __syncthreads();
   if (group == 0) {
     const int used = (K + per - 1) / per;  // groups that held at least one piece
     for (int g = 1; g < used; ++g) {
       State x;
-      const uint32_t* qa = s_vec + g * 2 * CPS + lane_g * VEC;
-      load_state<Op, VEC>(qa, qa + CPS, x);
+      const uint32_t* qa = s_vec + g * Op::kPlanes * CPS + lane_g * VEC;
+      load_state<Op, VEC>(qa, CPS, x);
       Op::template merge<VEC>(acc, x);
       cnt += s_cnt[g];
     }
@@ -1219,8 +1286,8 @@ Split make_split(int64_t n, const Layout& g, int ctas_per_sm) {
 
 constexpr int kMaxCtasPerSm = 8;  // 256-thread CTAs: the hardware limit of 2048 threads per SM
 
-size_t records_vec_bytes(const Layout& g, int num_ctas) {
-  return align_up(size_t(g.num_slabs) * num_ctas * 2 * 2 * g.cps * sizeof(uint32_t), 256);
+size_t records_vec_bytes(const Layout& g, int num_ctas, int planes) {
+  return align_up(size_t(g.num_slabs) * num_ctas * 2 * planes * g.cps * sizeof(uint32_t), 256);
 }
 size_t records_meta_bytes(const Layout& g, int num_ctas) {
   return size_t(g.num_slabs) * num_ctas * 2 * sizeof(int4);
@@ -1228,13 +1295,13 @@ size_t records_meta_bytes(const Layout& g, int num_ctas) {
 
 // Upper bound over both lane layouts (a caller may pass unaligned pointers) and
 // over every occupancy the launch may find.
-size_t reduce_workspace_bytes(int64_t n, int C) {
+size_t reduce_workspace_bytes(int64_t n, int C, int planes = 2) {
   size_t best = 0;
   for (int v = 0; v < 3; ++v) {
     if (v == 2 && C % 8 != 0) continue;
     const Layout g = (v == 2) ? make_layout(C, true, 2) : make_layout(C, v == 1);
     const Split s = make_split(n, g, kMaxCtasPerSm);
-    const size_t bytes = records_vec_bytes(g, s.num_ctas) + records_meta_bytes(g, s.num_ctas);
+    const size_t bytes = records_vec_bytes(g, s.num_ctas, planes) + records_meta_bytes(g, s.num_ctas);
     if (bytes > best) best = bytes;
   }
   return best + 512;
@@ -1245,6 +1312,7 @@ struct Call {
   const int32_t* sid;
   const int32_t* perm;
   float* out;
+  float* out_sum;  // second output of the two-output operator, else NULL
   int32_t* arg;
   void* workspace;
   size_t workspace_bytes;
@@ -1276,7 +1344,7 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
     s.balance = c.balance;
     s.balance_k = c.balance_k;
   }
-  const size_t vec_bytes = records_vec_bytes(g, s.num_ctas);
+  const size_t vec_bytes = records_vec_bytes(g, s.num_ctas, Op::kPlanes);
   const size_t need = vec_bytes + records_meta_bytes(g, s.num_ctas);
   const uintptr_t base = align_up(reinterpret_cast<uintptr_t>(c.workspace), 256);
   const size_t pad = base - reinterpret_cast<uintptr_t>(c.workspace);
@@ -1300,11 +1368,11 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<const In*>(c.feats), c.sid, c.perm, c.out,
-                                       c.arg, ws, c.n, c.C, s, c.mean, OutSpec{c.arg_base, c.m});
+                                       c.arg, ws, c.n, c.C, s, c.mean, OutSpec{c.arg_base, c.m, c.out_sum});
     if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "segment reduce launch: %s", cudaGetErrorString(e));
   } else {
     kernel<<<grid, kCtaThreads, dyn_smem, c.stream>>>(static_cast<const In*>(c.feats), c.sid, c.perm, c.out,
-                                                      c.arg, ws, c.n, c.C, s, c.mean, OutSpec{c.arg_base, c.m});
+                                                      c.arg, ws, c.n, c.C, s, c.mean, OutSpec{c.arg_base, c.m, c.out_sum});
   }
   int st = check_launch("segment reduce kernel");
   if (st != TEXB_OK || s.num_ctas <= 1) return st;
@@ -1321,12 +1389,12 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, segment_fixup_kernel<Op, VEC, LPR>, ws, c.out, c.arg,
-                                       s.num_ctas, c.C, c.mean, OutSpec{c.arg_base, c.m});
+                                       s.num_ctas, c.C, c.mean, OutSpec{c.arg_base, c.m, c.out_sum});
     if (e != cudaSuccess)
       return fail(TEXB_ERR_CUDA, "segment_fixup_kernel launch: %s", cudaGetErrorString(e));
   } else {
     segment_fixup_kernel<Op, VEC, LPR><<<grid, kCtaThreads, 0, c.stream>>>(ws, c.out, c.arg, s.num_ctas,
-                                                                           c.C, c.mean, OutSpec{c.arg_base, c.m});
+                                                                           c.C, c.mean, OutSpec{c.arg_base, c.m, c.out_sum});
   }
   return check_launch("segment_fixup_kernel");
 }
@@ -1335,7 +1403,7 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
 template <class Op, class In, int LB, int LPR, bool HAS_PERM>
 int launch_staged(const Layout& g, const Call& c) {
   constexpr int VEC = LB / sizeof(In);
-  constexpr int kRing = kStageRingBytesFor<In, LB>;
+  constexpr int kRing = kStageRingBytesFor<In, LB, Op::kPlanes>;
   // The shared-memory attribute is per device: set it on every call (a host-side table write).
   auto staged_launch = [&](auto kernel, int* resident) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);
@@ -1375,8 +1443,13 @@ int dispatch_layout(const Layout& g, const Call& c) {
     using H = __nv_bfloat16;
     if (g.lane_bytes == 8 && g.lpr == 32)
       return c.perm ? launch_staged<Op, H, 8, 32, true>(g, c) : launch_staged<Op, H, 8, 32, false>(g, c);
-    if (g.lane_bytes == 16 && g.lpr == 32)
-      return c.perm ? launch_staged<Op, H, 16, 32, true>(g, c) : launch_staged<Op, H, 16, 32, false>(g, c);
+    if constexpr (Op::kPlanes == 2) {  // the two-output operator's edge-run slots would not fit beside 16-byte bf16 lanes
+      if (g.lane_bytes == 16 && g.lpr == 32)
+        return c.perm ? launch_staged<Op, H, 16, 32, true>(g, c) : launch_staged<Op, H, 16, 32, false>(g, c);
+    } else if (g.lane_bytes == 16) {
+      return fail(TEXB_ERR_UNSUPPORTED, "the two-output reduction takes bf16 rows of up to 128 channels (got %d); "
+                  "convert wider rows to fp32", c.C);
+    }
     return fail(TEXB_ERR_UNSUPPORTED, "bf16 features need at least 128 channels (got %d lanes per row)", g.lpr);
   }
   if (g.vec == 4) {
@@ -1402,21 +1475,27 @@ int dispatch_layout(const Layout& g, const Call& c) {
 
 }  // namespace
 
+// `out_sum` selects the two-output form: op (sum or mean) goes to out_sum, the
+// maxima and their rows to out / arg, from one pass over the features.
 int segment_reduce_impl(int op, const void* feats, int in_bytes, const int32_t* sid, const int32_t* perm,
                         const int32_t* offsets, int has_empty, const int32_t* balance,
                         int balance_len, int64_t n, int C, int64_t m, float* out, int32_t* arg,
-                        int32_t arg_base, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                        int32_t arg_base, void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                        float* out_sum) {
+  const bool pair = out_sum != nullptr;
   if (in_bytes != 4 && in_bytes != 2)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "features must be fp32 (4 bytes) or bf16 (2 bytes)");
   if (op != TEXB_OP_SUM && op != TEXB_OP_MEAN && op != TEXB_OP_MAX)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "unknown reduce op %d", op);
+  if (pair && op == TEXB_OP_MAX)
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "the two-output reduction pairs the maximum with sum or mean");
   if (n < 0 || m < 0 || C < 1)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "bad sizes n=%lld channel=%d num_segments=%lld",
                 (long long)n, C, (long long)m);
   if (n >= (int64_t(1) << 31) - 65536 || m >= (int64_t(1) << 31) - 65536)
     return fail(TEXB_ERR_UNSUPPORTED, "n and num_segments must be below 2^31 - 65536");
   if (m > 0 && !out) return fail(TEXB_ERR_INVALID_ARGUMENT, "out is NULL");
-  if (m > 0 && op == TEXB_OP_MAX && !arg) return fail(TEXB_ERR_INVALID_ARGUMENT, "arg is NULL");
+  if (m > 0 && (op == TEXB_OP_MAX || pair) && !arg) return fail(TEXB_ERR_INVALID_ARGUMENT, "arg is NULL");
   if (n > 0 && (!feats || !sid)) return fail(TEXB_ERR_INVALID_ARGUMENT, "feats or sid is NULL");
   if ((has_empty || n == 0) && m > 0 && !offsets)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "offsets is required when has_empty is set or n == 0");
@@ -1426,12 +1505,14 @@ int segment_reduce_impl(int op, const void* feats, int in_bytes, const int32_t* 
     const int64_t total = m * C;
     const int64_t want = ceil_div(total, 256);
     const int blocks = int(want < 148 * 16 ? want : 148 * 16);
-    fill_empty_kernel<<<blocks, 256, 0, stream>>>(offsets, out, arg, m, C, op == TEXB_OP_MAX);
+    fill_empty_kernel<<<blocks, 256, 0, stream>>>(offsets, out, arg, m, C, op == TEXB_OP_MAX || pair);
+    if (pair) fill_empty_kernel<<<blocks, 256, 0, stream>>>(offsets, out_sum, nullptr, m, C, false);
     int st = check_launch("fill_empty_kernel");
     if (st != TEXB_OK || n == 0) return st;
   }
 
-  const bool vec_ok = aligned16(feats) && aligned16(out) && (op != TEXB_OP_MAX || aligned16(arg));
+  const bool vec_ok = aligned16(feats) && aligned16(out) && ((op != TEXB_OP_MAX && !pair) || aligned16(arg)) &&
+                      (!pair || aligned16(out_sum));
   if (in_bytes == 2 && (!vec_ok || C % 8 != 0 || C < 128))
     return fail(TEXB_ERR_UNSUPPORTED,
                 "bf16 features need 16-byte aligned pointers and a channel count that is a multiple of 8 "
@@ -1439,8 +1520,9 @@ int segment_reduce_impl(int op, const void* feats, int in_bytes, const int32_t* 
   const Layout g = make_layout(C, vec_ok, in_bytes);
   if (balance && balance_len < 2)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "balance table needs at least 2 entries");
-  Call c = {feats, sid, perm, out, arg, workspace, workspace_bytes, int(n), C, op == TEXB_OP_MEAN, stream,
+  Call c = {feats, sid, perm, out, out_sum, arg, workspace, workspace_bytes, int(n), C, op == TEXB_OP_MEAN, stream,
             balance, balance ? balance_len - 1 : 0, int(arg_base), int(m)};
+  if (pair) return dispatch_layout<OpSumMax>(g, c);
   if (op == TEXB_OP_MAX) return dispatch_layout<OpMax>(g, c);
   if (tuning().compensated) return dispatch_layout<OpSumComp>(g, c);
   return dispatch_layout<OpSumPlain>(g, c);
@@ -1454,6 +1536,7 @@ int expand_offsets_impl(const int32_t* offsets, int32_t* sid, int64_t n, int64_t
 }
 
 size_t reduce_workspace_bytes_impl(int64_t n, int C) { return reduce_workspace_bytes(n, C); }
+size_t reduce_pair_workspace_bytes_impl(int64_t n, int C) { return reduce_workspace_bytes(n, C, OpSumMax::kPlanes); }
 
 // ---- reduce without a caller workspace -------------------------------------------------
 // Some callers may not allocate device memory at all once they are running: a
@@ -1501,7 +1584,7 @@ int segment_reduce_static_impl(int op, const float* feats, const int32_t* sid, c
     scratch = device_ptr[dev];
   }
   return segment_reduce_impl(op, feats, 4, sid, perm, offsets, has_empty, balance, balance_len, n, C, m, out,
-                             arg, arg_base, scratch, kStaticScratchBytes, stream);
+                             arg, arg_base, scratch, kStaticScratchBytes, stream, nullptr);
 }
 
 int device_status_impl(int* wait_timeouts, int* bad_indices) {

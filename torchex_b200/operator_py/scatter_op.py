@@ -299,6 +299,41 @@ def _reduce(op: int, feats: torch.Tensor, data: ScatterData, want_arg: bool, arg
     return out, arg
 
 
+def _reduce_pair(op: int, feats: torch.Tensor, data: ScatterData, arg_base: int = 0):
+    """(sum or mean, max, arg) of the same rows from one pass over ``feats``."""
+    feats = _as_feats(feats)
+    n, c = feats.shape
+    if feats.dtype == torch.bfloat16 and (c % 8 != 0 or c != 128 or feats.data_ptr() % 16 != 0):
+        feats = feats.float()  # the two-output bf16 kernel covers aligned 128-channel rows
+    if n != data.unq_inv.numel():
+        raise RuntimeError(f"feats has {n} rows but ScatterData was built for {data.unq_inv.numel()}")
+    dev = feats.device
+    if dev != data.sid.device:
+        raise RuntimeError("feats and ScatterData live on different devices")
+    if c < 1:
+        raise RuntimeError("feats needs at least one channel")
+    lib = _native.lib()
+    m = data.num_unq
+    out_sum = torch.empty((m, c), dtype=torch.float32, device=dev)
+    out_max = torch.empty((m, c), dtype=torch.float32, device=dev)
+    arg = torch.empty((m, c), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        stream = _stream()
+        key = (c, stream, "pair")
+        ws = data._workspaces.get(key)
+        if ws is None or ws.numel() < lib.texb_reduce_pair_workspace_bytes(n, c):
+            ws = _scratch(lib.texb_reduce_pair_workspace_bytes(n, c), dev)
+            data._workspaces[key] = ws
+        _native.check(
+            lib.texb_segment_reduce_pair(op, feats.data_ptr(), feats.element_size(), data.sid.data_ptr(),
+                                         data._perm_ptr, data.preSum.data_ptr(), int(data.has_empty or n == 0),
+                                         data.balance.data_ptr(), data.balance.numel(), n, c, m,
+                                         out_sum.data_ptr(), out_max.data_ptr(), arg.data_ptr(), int(arg_base),
+                                         ws.data_ptr(), ws.numel(), stream),
+            "texb_segment_reduce_pair")
+    return out_sum, out_max, arg
+
+
 def _grad(g: torch.Tensor) -> torch.Tensor:
     # Autograd may hand over an expanded or strided gradient; the C ABI wants rows.
     return g.contiguous() if g.dtype == torch.float32 else g.float().contiguous()
@@ -377,6 +412,37 @@ class ScatterMaxFunction(Function):
         return _broadcast_back("max", ctx.plan, g_out, arg).to(ctx.in_dtype), None
 
 
+class ScatterMeanMaxFunction(Function):
+
+    @staticmethod
+    def forward(ctx, feats: torch.Tensor, data: ScatterData):
+        """(mean, max, arg) of one pass over feats: what ScatterMeanFunction and
+        ScatterMaxFunction return, reading the features once.  No counterpart in
+        the reference, whose callers run the two one after the other
+        (scatter_op.py:56-103)."""
+        mean, mx, arg = _reduce_pair(_native.OP_MEAN, feats, data)
+        ctx.save_for_backward(arg)
+        ctx.mark_non_differentiable(arg)
+        ctx.plan, ctx.in_dtype = data, feats.dtype
+        return mean, mx, arg
+
+    @staticmethod
+    def backward(ctx, g_mean, g_max, g_arg):
+        (arg,) = ctx.saved_tensors
+        data = ctx.plan
+        g_mean, g_max = _grad(g_mean), _grad(g_max)
+        n, c, m = data.unq_inv.numel(), g_mean.shape[1], data.num_unq
+        g_input = g_mean.new_empty((n, c))
+        perm = None if data.perm is None else data.perm.data_ptr()
+        with torch.cuda.device(g_mean.device):
+            _native.check(
+                _native.lib().texb_scatter_mean_max_backward(
+                    g_mean.data_ptr(), g_max.data_ptr(), arg.data_ptr(), data.sid.data_ptr(), perm,
+                    data.preSum.data_ptr(), g_input.data_ptr(), n, c, m, _stream()),
+                "texb_scatter_mean_max_backward")
+        return g_input.to(ctx.in_dtype), None
+
+
 class GetPreSumFunction(Function):
 
     @staticmethod
@@ -425,6 +491,14 @@ def scatter_max(feats: torch.Tensor, data: ScatterData):
     if _wants_grad(feats):
         return ScatterMaxFunction.apply(feats, data)
     return _reduce(_native.OP_MAX, feats, data, want_arg=True)
+
+
+def scatter_mean_max(feats: torch.Tensor, data: ScatterData):
+    """``(mean, max, arg)``: ``scatter_mean`` and ``scatter_max`` of the same
+    features from one pass over them."""
+    if _wants_grad(feats):
+        return ScatterMeanMaxFunction.apply(feats, data)
+    return _reduce_pair(_native.OP_MEAN, feats, data)
 
 
 getPreSum = GetPreSumFunction.apply
