@@ -396,7 +396,29 @@ def other_configs(dev):
         torch.cuda.synchronize()
         return a.elapsed_time(b) / reps * 1e3
 
-    def forward(ids, cnt, feat, label, note):
+    def graph_timed(call, reps=20, replays=10):
+        """Device time per call when `reps` calls are captured in a CUDA graph and the
+        graph is replayed: what a launch-bound configuration costs without the host."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            call(side.cuda_stream)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            capturing = torch.cuda.current_stream().cuda_stream
+            for _ in range(reps):
+                call(capturing)
+        graph.replay()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(replays):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / (reps * replays) * 1e3
+
+    def forward(ids, cnt, feat, label, note, graph=False):
         n, c = feat.shape
         m = cnt.numel()
         data = ScatterData(ids.to(dev), cnt.to(dev))
@@ -407,11 +429,16 @@ def other_configs(dev):
         b = algorithmic_bytes(n, c, m)
         res = {"points": n, "channels": c, "segments": m, "note": note}
         for name, op in (("sum", _native.OP_SUM), ("mean", _native.OP_MEAN), ("max", _native.OP_MAX)):
-            us = timed(lambda: lib.texb_segment_reduce(op, feat.data_ptr(), data.sid.data_ptr(), perm,
-                                                       data.preSum.data_ptr(), 0, data.balance.data_ptr(),
-                                                       data.balance.numel(), n, c, m, out.data_ptr(), arg.data_ptr(), 0,
-                                                       ws.data_ptr(), ws.numel(), stream), 50)
+            def call(on_stream):
+                st = lib.texb_segment_reduce(op, feat.data_ptr(), data.sid.data_ptr(), perm, data.preSum.data_ptr(), 0,
+                                             data.balance.data_ptr(), data.balance.numel(), n, c, m, out.data_ptr(),
+                                             arg.data_ptr(), 0, ws.data_ptr(), ws.numel(), on_stream)
+                if st != 0:
+                    raise RuntimeError(_native.last_error())
+            us = timed(lambda: call(stream), 50)
             res[name] = {"us": round(us, 2), "GBps": round(b[name] / us / 1e3, 1), "Mpoints_per_s": round(n / us, 1)}
+            if graph:
+                res[name]["us_in_cuda_graph"] = round(graph_timed(call), 2)
         return res, data, arg
 
     table = {}
@@ -452,10 +479,12 @@ def other_configs(dev):
     del feat16, feat32, data, out, out2, arg
     ids, cnt = W.uniform_ids(20_000, 2_000, SEED)
     table["uniform_20k_c16"], _, _ = forward(ids, cnt, W.features(20_000, 16, SEED, device=dev), "c1",
-                                             "1.3 MB of features: L2-resident and launch-bound")
+                                             "1.3 MB of features: L2-resident and launch-bound "
+                                             "(us: launched from Python; us_in_cuda_graph: 20 calls replayed from a CUDA graph)",
+                                             graph=True)
     ids, cnt = W.voxel_frame(200_000, SEED)
     table["voxel_200k_c64"], _, _ = forward(ids, cnt, W.features(200_000, 64, SEED, device=dev), "c2",
-                                            "51 MB of features: L2-resident across repetitions")
+                                            "51 MB of features: L2-resident across repetitions", graph=True)
     ids, cnt, feat, grad = W.small_segments_with_ties(500_000, 128, SEED, device=dev)
     fw, data, arg = forward(ids, cnt, feat, "c4", "256 MB of features; 10 % duplicated rows (ties)")
     n, c, m = 500_000, 128, cnt.numel()

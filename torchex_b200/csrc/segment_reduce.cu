@@ -306,6 +306,8 @@ template <int VEC>
 __device__ __forceinline__ void store_words(uint32_t* p, const uint32_t (&v)[VEC]) {
   if constexpr (VEC == 4) {
     *reinterpret_cast<uint4*>(p) = make_uint4(v[0], v[1], v[2], v[3]);
+  } else if constexpr (VEC == 2) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(v[0], v[1]);
   } else if constexpr (VEC == 8) {
     reinterpret_cast<uint4*>(p)[0] = make_uint4(v[0], v[1], v[2], v[3]);
     reinterpret_cast<uint4*>(p)[1] = make_uint4(v[4], v[5], v[6], v[7]);
@@ -320,6 +322,9 @@ __device__ __forceinline__ void load_words(const uint32_t* p, uint32_t (&v)[VEC]
   if constexpr (VEC == 4) {
     uint4 t = *reinterpret_cast<const uint4*>(p);
     v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else if constexpr (VEC == 2) {
+    uint2 t = *reinterpret_cast<const uint2*>(p);
+    v[0] = t.x; v[1] = t.y;
   } else if constexpr (VEC == 8) {
     const uint4 t = reinterpret_cast<const uint4*>(p)[0], u = reinterpret_cast<const uint4*>(p)[1];
     v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
@@ -367,6 +372,8 @@ template <int VEC>
 __device__ __forceinline__ void store_row(float* po, const float (&r)[VEC]) {
   if constexpr (VEC == 4) {
     *reinterpret_cast<float4*>(po) = make_float4(r[0], r[1], r[2], r[3]);
+  } else if constexpr (VEC == 2) {
+    *reinterpret_cast<float2*>(po) = make_float2(r[0], r[1]);
   } else if constexpr (VEC == 8) {
     reinterpret_cast<float4*>(po)[0] = make_float4(r[0], r[1], r[2], r[3]);
     reinterpret_cast<float4*>(po)[1] = make_float4(r[4], r[5], r[6], r[7]);
@@ -402,29 +409,22 @@ __device__ __forceinline__ void store_out(float* __restrict__ out, int32_t* __re
   }
   if constexpr (Op::kIsMax) {
     int32_t* pa = arg + int64_t(seg) * C + ch;
+    int ix[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {  // rows are reported relative to ospec; "no row" stays -1
+      const int i = Op::template index<VEC>(x, k);
+      ix[k] = i < 0 ? i : i + ospec.arg_base;
+    }
     if constexpr (VEC == 4) {
-      int ix[VEC];
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) {  // rows are reported relative to ospec; "no row" stays -1
-        const int i = Op::template index<VEC>(x, k);
-        ix[k] = i < 0 ? i : i + ospec.arg_base;
-      }
       *reinterpret_cast<int4*>(pa) = make_int4(ix[0], ix[1], ix[2], ix[3]);
+    } else if constexpr (VEC == 2) {
+      *reinterpret_cast<int2*>(pa) = make_int2(ix[0], ix[1]);
     } else if constexpr (VEC == 8) {
-      int ix[VEC];
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        const int i = Op::template index<VEC>(x, k);
-        ix[k] = i < 0 ? i : i + ospec.arg_base;
-      }
       reinterpret_cast<int4*>(pa)[0] = make_int4(ix[0], ix[1], ix[2], ix[3]);
       reinterpret_cast<int4*>(pa)[1] = make_int4(ix[4], ix[5], ix[6], ix[7]);
     } else {
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        const int i = Op::template index<VEC>(x, k);
-        pa[k] = i < 0 ? i : i + ospec.arg_base;
-      }
+      for (int k = 0; k < VEC; ++k) pa[k] = ix[k];
     }
   }
 }
@@ -466,9 +466,15 @@ __device__ __forceinline__ unsigned global_timer_lo() {
   return t;
 }
 
-// Stitches the edge runs a CTA left in shared memory, in position order (group
-// 0 only).  Segments that live inside the CTA are written to `out`; a run open
-// at the CTA's left or right edge becomes the CTA's head or tail record.
+// Stitches the edge runs a CTA left in shared memory.  The valid slots, taken in
+// slot order, form chains: a slot that is open to the right is continued by the
+// next valid slot.  A chain is folded in position order by the group that owns
+// its first slot, so the chains of a CTA (usually one per pair of neighbouring
+// groups) are folded side by side and the result does not depend on who folds.
+// A chain that closes inside the CTA is a finished segment and goes to `out`;
+// the chain that enters from the left edge becomes the CTA's head record, the
+// one that leaves through the right edge its tail record.  Every thread of the
+// CTA must call this, after a barrier that follows the last slot write.
 template <class Op, int VEC, int LPR>
 __device__ __forceinline__ void stitch_cta(const uint32_t* s_vec, const int* s_sid, const int* s_cnt,
                                            const unsigned* s_flag, float* __restrict__ out,
@@ -479,49 +485,71 @@ __device__ __forceinline__ void stitch_cta(const uint32_t* s_vec, const int* s_s
   constexpr int GPC = kCtaThreads / LPR;
   constexpr int CPS = LPR * VEC;
   constexpr int SLOTS = 2 * GPC;
-  if (group != 0) return;
-  const int64_t rec = (int64_t(blockIdx.y) * gridDim.x + blockIdx.x) * 2;
-  bool have = false, cur_open_left = false;
-  int cur_sid = 0, cur_cnt = 0;
-  unsigned head_flag = 0u;
-  State cur;
-  Op::template init<VEC>(cur);
-  for (int slot = 0; slot < SLOTS; ++slot) {
-    const unsigned f = s_flag[slot];
-    if (!(f & kValid)) continue;
-    State x;
-    const uint32_t* pa = s_vec + slot * Op::kPlanes * CPS + lane_g * VEC;
-    load_state<Op, VEC>(pa, CPS, x);
-    if (!have) {
-      cur = x;
-      cur_sid = s_sid[slot];
-      cur_cnt = s_cnt[slot];
-      cur_open_left = (f & kOpenLeft) != 0u;
-      have = true;
-    } else {
-      Op::template merge<VEC>(cur, x);
-      cur_cnt += s_cnt[slot];
-    }
-    if (!(f & kOpenRight)) {
-      if (!cur_open_left) {
-        store_out<Op, VEC>(out, arg, cur_sid, C, ch, lane_on, cur, cur_cnt, mean, ospec);
-      } else {
-        uint32_t* ga = ws.vec + rec * Op::kPlanes * CPS + lane_g * VEC;
-        store_state<Op, VEC>(ga, CPS, cur);
-        head_flag = kValid | kOpenLeft;
-        if (lane_g == 0) ws.meta[rec] = make_int4(cur_sid, cur_cnt, int(head_flag), int(t_start));
-      }
-      have = false;
+  __shared__ int s_first_valid, s_last_valid;
+  if (threadIdx.x == 0) {
+    s_first_valid = SLOTS;
+    s_last_valid = -1;
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < SLOTS; t += kCtaThreads) {
+    if (s_flag[t] & kValid) {
+      atomicMin(&s_first_valid, t);
+      atomicMax(&s_last_valid, t);
     }
   }
-  if (head_flag == 0u && lane_g == 0) ws.meta[rec] = make_int4(0, 0, 0, int(t_start));
-  if (have) {
-    uint32_t* ga = ws.vec + (rec + 1) * Op::kPlanes * CPS + lane_g * VEC;
-    store_state<Op, VEC>(ga, CPS, cur);
-    const unsigned f = kValid | kOpenRight | (cur_open_left ? kOpenLeft : 0u);
-    if (lane_g == 0) ws.meta[rec + 1] = make_int4(cur_sid, cur_cnt, int(f), int(global_timer_lo()));
-  } else if (lane_g == 0) {
-    ws.meta[rec + 1] = make_int4(0, 0, 0, int(global_timer_lo()));
+  __syncthreads();
+  const int first = s_first_valid, last = s_last_valid;
+  const int64_t rec = (int64_t(blockIdx.y) * gridDim.x + blockIdx.x) * 2;
+  if (threadIdx.x == 0) {  // records this CTA does not produce are marked empty
+    if (first >= SLOTS || !(s_flag[first] & kOpenLeft)) ws.meta[rec] = make_int4(0, 0, 0, int(t_start));
+    if (last < 0 || !(s_flag[last] & kOpenRight)) ws.meta[rec + 1] = make_int4(0, 0, 0, int(global_timer_lo()));
+  }
+#pragma unroll 1
+  for (int which = 0; which < 2; ++which) {
+    const int slot = 2 * group + which;
+    const unsigned f = s_flag[slot];
+    if (!(f & kValid)) continue;
+    const bool from_left = (f & kOpenLeft) != 0u;
+    if (from_left && slot != first) continue;  // part of a chain that an earlier slot starts
+    State cur;
+    const uint32_t* pa = s_vec + slot * Op::kPlanes * CPS + lane_g * VEC;
+    load_state<Op, VEC>(pa, CPS, cur);
+    const int cur_sid = s_sid[slot];
+    int cur_cnt = s_cnt[slot];
+    unsigned fs = f;
+    int at = slot;
+    bool leaves = false;  // the chain runs past the CTA's right edge
+    while (fs & kOpenRight) {
+      int t = at + 1;
+      while (t < SLOTS && !(s_flag[t] & kValid)) ++t;
+      if (t >= SLOTS) {
+        leaves = true;
+        break;
+      }
+      State x;
+      const uint32_t* pb = s_vec + t * Op::kPlanes * CPS + lane_g * VEC;
+      load_state<Op, VEC>(pb, CPS, x);
+      Op::template merge<VEC>(cur, x);
+      cur_cnt += s_cnt[t];
+      fs = s_flag[t];
+      at = t;
+    }
+    if (!leaves && !from_left) {
+      store_out<Op, VEC>(out, arg, cur_sid, C, ch, lane_on, cur, cur_cnt, mean, ospec);
+    } else if (!leaves) {
+      uint32_t* ga = ws.vec + rec * Op::kPlanes * CPS + lane_g * VEC;
+      store_state<Op, VEC>(ga, CPS, cur);
+      if (lane_g == 0) ws.meta[rec] = make_int4(cur_sid, cur_cnt, int(kValid | kOpenLeft), int(t_start));
+    } else {
+      uint32_t* ga = ws.vec + (rec + 1) * Op::kPlanes * CPS + lane_g * VEC;
+      store_state<Op, VEC>(ga, CPS, cur);
+      const unsigned ft = kValid | kOpenRight | (from_left ? kOpenLeft : 0u);
+      if (lane_g == 0) {
+        ws.meta[rec + 1] = make_int4(cur_sid, cur_cnt, int(ft), int(global_timer_lo()));
+        // one run from edge to edge: it is the tail record, and there is no head record
+        if (from_left) ws.meta[rec] = make_int4(0, 0, 0, int(t_start));
+      }
+    }
   }
 }
 
@@ -760,7 +788,7 @@ constexpr int kStageTile = 32;    // positions per metadata tile
 // The two-output operator's edge-run slots are twice as large (four planes), so
 // its fp32 ring has two batches, again to keep two CTAs per SM.
 template <class In, int LB, int PLANES>
-constexpr int kStageDepthFor = (sizeof(In) == 4) ? (PLANES == 2 ? 3 : 2) : (LB == 16 ? 2 : (PLANES == 2 ? 3 : 4));
+constexpr int kStageDepthFor = (LB == 8) ? (PLANES == 2 ? 3 : 4) : (sizeof(In) == 4) ? (PLANES == 2 ? 3 : 2) : 2;
 template <int LB> constexpr int kStageSlotBytesFor = kCtaThreads * LB;  // one row slot for the whole CTA
 template <class In, int LB, int PLANES>
 constexpr int kStageRingBytesFor = kStageBatch * kStageDepthFor<In, LB, PLANES> * kStageSlotBytesFor<LB>;
@@ -785,17 +813,28 @@ __device__ __forceinline__ void unpack_lane(const float4& t4, float (&v)[VEC]) {
 }
 template <class In, int VEC>
 __device__ __forceinline__ void unpack_lane(const float2& t2, float (&v)[VEC]) {
-  static_assert(sizeof(In) == 2 && VEC == 4, "8-byte lanes hold four bf16 channels");
-  const unsigned w[2] = {__float_as_uint(t2.x), __float_as_uint(t2.y)};
+  if constexpr (sizeof(In) == 4) {  // 8-byte lanes: two fp32 channels
+    static_assert(VEC == 2, "8-byte lanes hold two fp32 channels");
+    v[0] = t2.x; v[1] = t2.y;
+  } else {                          // or four bf16 channels
+    static_assert(VEC == 4, "8-byte lanes hold four bf16 channels");
+    const unsigned w[2] = {__float_as_uint(t2.x), __float_as_uint(t2.y)};
 #pragma unroll
-  for (int k = 0; k < 2; ++k) {
-    v[2 * k] = __uint_as_float(w[k] << 16);
-    v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+    for (int k = 0; k < 2; ++k) {
+      v[2 * k] = __uint_as_float(w[k] << 16);
+      v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+    }
   }
 }
 
+// Resident CTAs per SM the staged kernel is compiled for: three where the ring and
+// the edge-run slots leave room (bf16 rows on 8-byte lanes, single-output operators),
+// otherwise two.  (8-byte lanes: bf16 rows of up to 128 channels, fp32 rows of up to 64.)
+template <class Op, class In, int LB>
+constexpr int kStagedCtasPerSm = (LB == 8 && Op::kPlanes == 2) ? 3 : 2;
+
 template <class Op, class In, int LB, int LPR, bool HAS_PERM, bool BULK>
-__global__ void __launch_bounds__(kCtaThreads, 2)
+__global__ void __launch_bounds__(kCtaThreads, kStagedCtasPerSm<Op, In, LB>)
 segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __restrict__ sid,
                              const int32_t* __restrict__ perm, float* __restrict__ out,
                              int32_t* __restrict__ arg, Workspace ws, int n, int C,
@@ -1242,13 +1281,29 @@ int sm_count() {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-Layout make_layout(int C, bool allow_vec4, int in_bytes = 4) {
+#ifndef TEXB_SMALL_BYTES
+#define TEXB_SMALL_BYTES (8 << 20)
+#endif
+
+// `force_vec` (workspace sizing only) names the channels per lane instead of choosing them.
+Layout make_layout(int C, bool allow_vec4, int in_bytes = 4, int64_t n = -1, int force_vec = 0) {
   Layout g;
   g.in_bytes = in_bytes;
   g.vec = (allow_vec4 && C % 4 == 0) ? 4 : 1;
+  // A few megabytes of narrow rows are bound by latency, not bandwidth: with
+  // 128-bit lanes a row of 16 channels is 4 lanes, a CTA holds 64 groups that
+  // each fetch ids, rows and features in dependent steps of 4 positions, and one
+  // group then stitches 128 edge runs.  One lane per channel makes a group a
+  // warp: 32 positions per step and 16 edge runs per CTA.
+  if (in_bytes == 4 && C <= 32 && n >= 0 && n * C * 4 <= int64_t(TEXB_SMALL_BYTES)) g.vec = 1;
+  // fp32 rows of 36..64 channels: 8-byte lanes, so that a row spans a whole warp
+  // (with 16-byte lanes two groups share a warp and each waits while the other
+  // closes its runs); needs the bulk-copy ring.
+  if (in_bytes == 4 && g.vec == 4 && C > 32 && C <= 64 && tuning().staged == 2) g.vec = 2;
   // bf16 (the caller has checked C % 8 == 0 and the alignment): rows of up to 128
   // channels take 8-byte lanes so that one row spans a warp; wider rows 16-byte lanes.
   if (in_bytes == 2) g.vec = (C <= 128) ? 4 : 8;
+  if (force_vec) g.vec = force_vec;
   g.lane_bytes = g.vec * in_bytes;
   const int lanes = C / g.vec;
   int lpr = 1;
@@ -1258,7 +1313,7 @@ Layout make_layout(int C, bool allow_vec4, int in_bytes = 4) {
   g.cps = g.lpr * g.vec;
   g.num_slabs = (C + g.cps - 1) / g.cps;
   g.gpc = kCtaThreads / g.lpr;
-  g.staged = (g.vec >= 4 && g.lpr >= 16) ? tuning().staged : 0;
+  g.staged = ((g.vec >= 4 && g.lpr >= 16) || g.vec == 2) ? tuning().staged : 0;
   if (in_bytes == 2 && g.staged == 0) g.staged = 2;  // bf16 rows exist only in the staged kernel
   return g;
 }
@@ -1297,9 +1352,15 @@ size_t records_meta_bytes(const Layout& g, int num_ctas) {
 // over every occupancy the launch may find.
 size_t reduce_workspace_bytes(int64_t n, int C, int planes = 2) {
   size_t best = 0;
-  for (int v = 0; v < 3; ++v) {
-    if (v == 2 && C % 8 != 0) continue;
-    const Layout g = (v == 2) ? make_layout(C, true, 2) : make_layout(C, v == 1);
+  // every lane layout a launch may pick for this channel count: fp32 with 1, 4 or 2
+  // channels per lane, bf16 with 4 or 8
+  const int cand[5][2] = {{4, 1}, {4, 4}, {4, 2}, {2, 4}, {2, 8}};
+  for (int v = 0; v < 5; ++v) {
+    const int in_bytes = cand[v][0], vec = cand[v][1];
+    if (in_bytes == 4 && vec == 4 && C % 4 != 0) continue;
+    if (in_bytes == 4 && vec == 2 && (C % 4 != 0 || C <= 32 || C > 64)) continue;
+    if (in_bytes == 2 && (C % 8 != 0 || (vec == 4 && C > 128))) continue;
+    const Layout g = make_layout(C, true, in_bytes, -1, vec);
     const Split s = make_split(n, g, kMaxCtasPerSm);
     const size_t bytes = records_vec_bytes(g, s.num_ctas, planes) + records_meta_bytes(g, s.num_ctas);
     if (bytes > best) best = bytes;
@@ -1452,6 +1513,8 @@ int dispatch_layout(const Layout& g, const Call& c) {
     }
     return fail(TEXB_ERR_UNSUPPORTED, "bf16 features need at least 128 channels (got %d lanes per row)", g.lpr);
   }
+  if (g.vec == 2)  // make_layout chooses this only for the bulk-copy ring and 32 lanes per row
+    return c.perm ? launch_staged<Op, float, 8, 32, true>(g, c) : launch_staged<Op, float, 8, 32, false>(g, c);
   if (g.vec == 4) {
     switch (g.lpr) {
       case 1: return dispatch_perm<Op, 4, 1>(g, c);
@@ -1517,7 +1580,7 @@ int segment_reduce_impl(int op, const void* feats, int in_bytes, const int32_t* 
     return fail(TEXB_ERR_UNSUPPORTED,
                 "bf16 features need 16-byte aligned pointers and a channel count that is a multiple of 8 "
                 "and at least 128 (got %d); convert to fp32 for other shapes", C);
-  const Layout g = make_layout(C, vec_ok, in_bytes);
+  const Layout g = make_layout(C, vec_ok, in_bytes, n);
   if (balance && balance_len < 2)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "balance table needs at least 2 entries");
   Call c = {feats, sid, perm, out, out_sum, arg, workspace, workspace_bytes, int(n), C, op == TEXB_OP_MEAN, stream,
