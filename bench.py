@@ -44,7 +44,7 @@ HBM_FALLBACK_GBS = 6650.0         # earlier copy measurement on this pool, used 
 # DRAM bytes of one reduce launch on this workload (dram__bytes_read.sum +
 # dram__bytes_write.sum of one ncu capture of this script; summary in
 # profiles/reduce_kernel_skewed_1m_c128.txt).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 543_200_000
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 541_800_000
 
 
 def algorithmic_bytes(n, c, m, feature_bytes=4):
