@@ -35,6 +35,8 @@ class _CpuData:
 
 
 def _cpu_reduce(op, feats, data, row_base=0):
+    if op == "mean_max":
+        return (_cpu_reduce("mean", feats, data),) + _cpu_reduce("max", feats, data, row_base)
     if op == "max":
         mx, arg = O.spec_scatter_max(feats, data.ids, data.m)
         arg = np.where(arg >= 0, arg + row_base, arg).astype(np.int32)
@@ -70,6 +72,7 @@ def _worker(rank, world, port, frames, per_frame, channels, out_dir):
         res["mean_all"] = shard.scatter("mean", feats, replicated=True)
         mx, arg = shard.scatter("max", feats, replicated=True)
         res["max_all"], res["arg_all"] = mx, arg
+        res["pair_mean"], res["pair_max"], res["pair_arg"] = shard.scatter("mean_max", feats, replicated=True)
         torch.save({k: v.clone() for k, v in res.items()}, os.path.join(out_dir, f"rank{rank}.pt"))
     finally:
         dist.destroy_process_group()
@@ -96,4 +99,7 @@ def test_two_rank_shards_reproduce_the_single_process_result(tmp_path):
         assert np.array_equal(out["mean_all"].numpy(), want_mean)
         assert np.array_equal(out["max_all"].numpy(), want_max)
         assert np.array_equal(out["arg_all"].numpy(), want_arg)          # global row numbers
+        assert np.array_equal(out["pair_mean"].numpy(), want_mean)
+        assert np.array_equal(out["pair_max"].numpy(), want_max)
+        assert np.array_equal(out["pair_arg"].numpy(), want_arg)
         assert np.array_equal(out["sum_local"].numpy(), want_sum[seg_off[r]:seg_off[r + 1]])

@@ -136,3 +136,19 @@ def test_pair_backward_is_the_sum_of_the_two_backwards():
     mx.backward(g_max)
     assert np.array_equal(x.grad.cpu().numpy(),
                           O.spec_max_backward(torch.roll(grad, 1, 0), want_arg, ids.numel()))
+
+
+def test_pair_reports_rows_relative_to_arg_base_in_a_frame_shard():
+    from torchex_b200 import frames as F
+    per_frame, frames = 4_000, 3
+    all_frames = [W.voxel_frame(per_frame, 600 + f) for f in range(frames)]
+    segs = [int(c.numel()) for _, c in all_frames]
+    layout = F.shard_layout(segs, [per_frame] * frames, 1, 2)   # the second of two ranks
+    lo, hi = layout.frames
+    shard = F.FrameShard([i for i, _ in all_frames[lo:hi]], [c for _, c in all_frames[lo:hi]], layout, DEV)
+    feats = W.features(layout.row_count, 32, 601).to(DEV)
+    mean, mx, arg = shard.scatter("mean_max", feats)
+    one_mx, one_arg = shard.scatter("max", feats)
+    assert torch.equal(mx, one_mx) and torch.equal(arg, one_arg)
+    assert int(arg.min()) >= layout.row_base and int(arg.max()) < layout.row_base + layout.row_count
+    assert torch.allclose(mean, shard.scatter("mean", feats), rtol=REL, atol=ABS)

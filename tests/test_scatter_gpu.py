@@ -504,3 +504,42 @@ def test_operators_replay_from_a_cuda_graph():
     d_max, d_arg = scatter_max(fresh, data)
     assert torch.equal(g_max, d_max) and torch.equal(g_arg, d_arg)
     assert _native.device_wait_timeouts() == 0
+
+
+def test_more_than_2_to_the_31_feature_elements():
+    """N * C above 2^31: the reference indexes features with a 32-bit product
+    (scatter_kernel.cu:115,147) and cannot run this shape; here row offsets are
+    64-bit.  Checked through size-independent properties and by recomputing
+    segments that hold the highest rows directly with torch."""
+    n, c, m = 16_900_000, 128, 1_000_000
+    assert n * c > 2**31
+    g = torch.Generator(device=DEV).manual_seed(91)
+    feat = torch.randn((n, c), device=DEV, generator=g)
+    ids = torch.randint(0, m, (n,), device=DEV, generator=g)
+    ids[-5:] = m - 1                      # the very last rows share a segment
+    ids[:m] = torch.arange(m, device=DEV)  # every segment is present
+    cnt = torch.bincount(ids, minlength=m)
+    data = ScatterData(ids, cnt)
+    s = scatter_sum(feat, data)
+    mx, arg = scatter_max(feat, data)
+    mean = scatter_mean(feat, data)
+    # linearity: the segment sums add up to the column sums
+    col = feat.sum(0, dtype=torch.float64)
+    assert torch.allclose(s.sum(0, dtype=torch.float64), col, rtol=0, atol=5e-3)
+    # the maxima of the maxima are the column maxima, and arg points at rows that hold them
+    assert torch.equal(mx.max(0).values, feat.max(0).values)
+    assert int(arg.min()) >= 0 and int(arg.max()) < n and int(arg.max()) > 2**31 // c
+    cols = torch.arange(c, device=DEV).expand(m, c)
+    assert torch.equal(feat[arg.long(), cols], mx)
+    assert torch.equal(ids[arg.long()], torch.arange(m, device=DEV)[:, None].expand(m, c))
+    # segments of the highest rows, recomputed directly
+    for seg in torch.unique(ids[-40:]).tolist():
+        rows = (ids == seg).nonzero().flatten()
+        block = feat[rows]
+        want = block.sum(0, dtype=torch.float64)
+        assert torch.allclose(s[seg].double(), want, rtol=REL, atol=ABS)
+        assert torch.allclose(mean[seg].double(), want / rows.numel(), rtol=REL, atol=ABS)
+        assert torch.equal(mx[seg], block.max(0).values)
+        first = (block == block.max(0).values).int().argmax(0)  # lowest row among equal maxima
+        assert torch.equal(arg[seg].long(), rows[first])
+    assert _native.device_wait_timeouts() == 0 and _native.device_bad_indices() == 0

@@ -131,9 +131,14 @@ class FrameShard:
 
     def scatter(self, op: str, feats: torch.Tensor, replicated: bool = False, group=None):
         """Reduces this rank's points.  Returns the shard's ``[seg_count, C]``
-        result (for ``max`` also ``arg`` holding GLOBAL row numbers), or with
+        result (for ``max`` also ``arg`` holding GLOBAL row numbers; for
+        ``mean_max`` the triple ``(mean, max, arg)``), or with
         ``replicated=True`` the full ``[seg_total, C]`` tensors on every rank."""
         res = self._reduce(op, feats, self.data, self.layout.row_base)
+        if op == "mean_max":  # (mean, max, arg) from one pass over feats
+            if replicated:
+                return tuple(gather_shards(t, self.layout, group) for t in res)
+            return res
         if op == "max":
             out, arg = res
             if replicated:
@@ -146,8 +151,10 @@ def _cuda_reduce(op: str, feats: torch.Tensor, data, row_base: int = 0):
     """The CUDA operators; for ``max`` the kernel itself reports rows as
     ``row_base + local row`` (global rows of the batch)."""
     from .operator_py import scatter_mean, scatter_sum
-    from .operator_py.scatter_op import _reduce
+    from .operator_py.scatter_op import _reduce, _reduce_pair
     from . import _native
+    if op == "mean_max":
+        return _reduce_pair(_native.OP_MEAN, feats, data, arg_base=row_base)
     if op == "max":
         return _reduce(_native.OP_MAX, feats, data, want_arg=True, arg_base=row_base)
     return {"sum": scatter_sum, "mean": scatter_mean}[op](feats, data)
