@@ -23,6 +23,7 @@ def _check_against_oracle(feat, ids, m, mean, mx, arg):
 @pytest.mark.parametrize("channel", [1, 3, 4, 20, 32, 64, 128, 136, 256])
 @pytest.mark.parametrize("shuffled", [False, True])
 def test_pair_matches_oracle_and_single_output_operators(channel, shuffled):
+    bad_before = _native.device_bad_indices()  # sticky; other tests feed corrupt plans on purpose
     g = torch.Generator().manual_seed(900 + channel)
     sizes = torch.randint(1, 40, (300,), generator=g)
     sizes[7], sizes[123] = 700, 2500
@@ -37,7 +38,7 @@ def test_pair_matches_oracle_and_single_output_operators(channel, shuffled):
     assert torch.equal(mx, one_mx) and torch.equal(arg, one_arg)
     one_mean = scatter_mean(feat.to(DEV), data)
     assert O.within_tolerance(mean.cpu().numpy(), one_mean.cpu().numpy().astype(np.float64), REL, ABS).all()
-    assert _native.device_wait_timeouts() == 0 and _native.device_bad_indices() == 0
+    assert _native.device_wait_timeouts() == 0 and _native.device_bad_indices() == bad_before
 
 
 @pytest.mark.parametrize("shuffled", [False, True])

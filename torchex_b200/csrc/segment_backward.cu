@@ -122,6 +122,7 @@ broadcast_back_kernel(const float* __restrict__ g, const float* __restrict__ g2,
     if (more) load_meta<MODE>(nxt, e0 + kRowsPerStep, ids, perm, offsets, n, m);
     for (int ch = lane_g * VEC; ch < C; ch += LPR * VEC) {
       Pack<VEC> val[kRowsPerStep];
+      Pack<VEC> quotient;  // g / count of the entry before: neighbours mostly share their segment
 #pragma unroll
       for (int k = 0; k < kRowsPerStep; ++k) {
         if (cur.s[k] >= 0) {
@@ -132,7 +133,16 @@ broadcast_back_kernel(const float* __restrict__ g, const float* __restrict__ g2,
             for (int q = 0; q < VEC; ++q)
               if (a.v[q] != cur.row[k]) val[k].v[q] = 0.f;
           }
-          if constexpr (MODE == kModeMean || MODE == kModeMeanMax) divide_by_count<VEC>(val[k].v, cur.den[k]);
+          if constexpr (MODE == kModeMean || MODE == kModeMeanMax) {
+            // the walk is in sorted order, so the division is done once per run of equal
+            // segments in a step and copied for the entries that follow
+            if (k > 0 && cur.s[k] == cur.s[k > 0 ? k - 1 : 0]) {
+              val[k] = quotient;
+            } else {
+              divide_by_count<VEC>(val[k].v, cur.den[k]);
+              quotient = val[k];
+            }
+          }
           if constexpr (MODE == kModeMeanMax) {
             const Pack<VEC> gm = load_f<VEC>(g2 + int64_t(cur.s[k]) * C + ch);
             const PackI<VEC> a = load_i<VEC>(arg + int64_t(cur.s[k]) * C + ch);
