@@ -74,11 +74,28 @@ __global__ void inspect_ids_kernel(const IdT* __restrict__ ids, int64_t n, int32
     lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
     hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
   }
+  // One set of atomics per CTA: every atomic of the grid lands on the same four
+  // words, and ten thousand of them (one set per warp) took longer than the read.
+  __shared__ int s_unsorted, s_runs, s_lo, s_hi;
+  if (threadIdx.x == 0) {
+    s_unsorted = 0;
+    s_runs = 0;
+    s_lo = INT_MAX;
+    s_hi = INT_MIN;
+  }
+  __syncthreads();
   if ((threadIdx.x & 31) == 0) {
-    if (unsorted) atomicAnd(&stats[0], 0);
-    if (lo != INT_MAX) atomicMin(&stats[1], lo);
-    if (hi != INT_MIN) atomicMax(&stats[2], hi);
-    if (runs) atomicAdd(&stats[3], runs);
+    if (unsorted) atomicOr(&s_unsorted, 1);
+    if (runs) atomicAdd(&s_runs, runs);
+    atomicMin(&s_lo, lo);
+    atomicMax(&s_hi, hi);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (s_unsorted) atomicAnd(&stats[0], 0);
+    if (s_lo != INT_MAX) atomicMin(&stats[1], s_lo);
+    if (s_hi != INT_MIN) atomicMax(&stats[2], s_hi);
+    if (s_runs) atomicAdd(&stats[3], s_runs);
   }
 }
 
@@ -115,9 +132,20 @@ __global__ void plan_stats_kernel(const int32_t* __restrict__ offsets, int m, in
     mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     empty += __shfl_xor_sync(0xffffffffu, empty, o);
   }
+  __shared__ int s_mx, s_empty;
+  if (threadIdx.x == 0) {
+    s_mx = 0;
+    s_empty = 0;
+  }
+  __syncthreads();
   if ((threadIdx.x & 31) == 0) {
-    if (mx) atomicMax(&plan_stats[0], mx);
-    if (empty) atomicAdd(&plan_stats[1], empty);
+    if (mx) atomicMax(&s_mx, mx);
+    if (empty) atomicAdd(&s_empty, empty);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (s_mx) atomicMax(&plan_stats[0], s_mx);
+    if (s_empty) atomicAdd(&plan_stats[1], s_empty);
   }
 }
 
@@ -215,17 +243,69 @@ __global__ void __launch_bounds__(1024) exclusive_scan_kernel(uint32_t* data, in
   }
 }
 
+// Positions of one digit pass.  The keys of digit d and tile t go to
+//   (keys of smaller digits) + (keys of digit d in earlier tiles) + rank within the tile.
+// CTA d turns row d of ghist (one count per tile) into its exclusive prefix, in place,
+// and leaves the row's total in totals[d]; the scatter kernel adds the prefix of the
+// 256 totals itself.  256 CTAs of a few hundred counts each instead of one CTA walking
+// every count of the pass (34 us per pass at 1 M keys).
+__global__ void __launch_bounds__(kSortThreads)
+digit_prefix_kernel(uint32_t* __restrict__ ghist, uint32_t* __restrict__ totals, int num_tiles) {
+  __shared__ uint32_t s_warp[kSortWarps];
+  __shared__ uint32_t s_total;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t* row = ghist + int64_t(blockIdx.x) * num_tiles;
+  uint32_t carry = 0u;
+  for (int base = 0; base < num_tiles; base += kSortThreads) {
+    const int t = base + threadIdx.x;
+    const uint32_t v = (t < num_tiles) ? row[t] : 0u;
+    uint32_t incl = v;
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t u = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += u;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      const uint32_t w = (lane < kSortWarps) ? s_warp[lane] : 0u;
+      uint32_t wi = w;
+      for (int o = 1; o < kSortWarps; o <<= 1) {
+        const uint32_t u = __shfl_up_sync(0xffffffffu, wi, o);
+        if (lane >= o) wi += u;
+      }
+      if (lane < kSortWarps) s_warp[lane] = wi - w;  // exclusive base of each warp
+      if (lane == kSortWarps - 1) s_total = wi;
+    }
+    __syncthreads();
+    if (t < num_tiles) row[t] = carry + s_warp[warp] + (incl - v);
+    carry += s_total;
+    __syncthreads();  // s_warp / s_total are rewritten by the next slab
+  }
+  if (threadIdx.x == 0) totals[blockIdx.x] = carry;
+}
+
 // Stable scatter of one digit pass.  Within a warp, item k of lane l is key
 // tile0 + warp * kWarpTile + k * 32 + l, so (warp, k, lane) order is key order.
 template <typename IdT, bool FIRST>
 __global__ void __launch_bounds__(kSortThreads)
 radix_scatter_kernel(const void* __restrict__ keys_in, const int32_t* __restrict__ vals_in,
                      int32_t* __restrict__ keys_out, int32_t* __restrict__ vals_out, int n, int shift,
-                     const uint32_t* __restrict__ ghist, int num_tiles) {
+                     const uint32_t* __restrict__ ghist, const uint32_t* __restrict__ totals,
+                     int num_tiles) {
+  static_assert(kRadix == kSortThreads, "one digit per thread in the prefix of the digit totals");
   __shared__ uint32_t s_wcount[kSortWarps][kRadix];
   __shared__ uint32_t s_gbase[kRadix];
+  __shared__ uint32_t s_wsum[kSortWarps];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < kSortWarps * kRadix; i += kSortThreads) (&s_wcount[0][0])[i] = 0u;
+  // exclusive prefix of the 256 digit totals (thread d owns digit d), kept for the end
+  const uint32_t my_total = totals[threadIdx.x];
+  uint32_t digit_incl = my_total;
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t u = __shfl_up_sync(0xffffffffu, digit_incl, o);
+    if (lane >= o) digit_incl += u;
+  }
+  if (lane == 31) s_wsum[warp] = digit_incl;
   __syncthreads();
 
   const int64_t w0 = int64_t(blockIdx.x) * kSortTile + int64_t(warp) * kWarpTile;
@@ -259,7 +339,9 @@ radix_scatter_kernel(const void* __restrict__ keys_in, const int32_t* __restrict
       s_wcount[w][d] = run;
       run += c;
     }
-    s_gbase[d] = ghist[int64_t(d) * num_tiles + blockIdx.x];
+    uint32_t digit_base = digit_incl - my_total;  // d == threadIdx.x
+    for (int w = 0; w < warp; ++w) digit_base += s_wsum[w];
+    s_gbase[d] = digit_base + ghist[int64_t(d) * num_tiles + blockIdx.x];
   }
   __syncthreads();
 #pragma unroll
@@ -296,7 +378,7 @@ SortWorkspace carve_sort_workspace(void* ws, int64_t n) {
   SortWorkspace s;
   const size_t arr = align_up(size_t(n) * sizeof(int32_t), 256);
   const int64_t tiles = ceil_div(n, kSortTile);
-  const size_t hist = align_up(size_t(tiles) * kRadix * sizeof(uint32_t), 256);
+  const size_t hist = align_up((size_t(tiles) + 1) * kRadix * sizeof(uint32_t), 256);  // counts + digit totals
   uintptr_t base = align_up(reinterpret_cast<uintptr_t>(ws), 256);
   s.tmp_keys = reinterpret_cast<int32_t*>(base);
   s.tmp_vals = reinterpret_cast<int32_t*>(base + arr);
@@ -322,13 +404,14 @@ int run_sort(const void* ids, int64_t n, int64_t m, int32_t* sid_out, int32_t* p
     } else {
       radix_histogram_kernel<int32_t><<<tiles, kSortThreads, 0, stream>>>(src_k, int(n), shift, sw.ghist, tiles);
     }
-    exclusive_scan_kernel<<<1, 1024, 0, stream>>>(sw.ghist, int64_t(tiles) * kRadix);
+    uint32_t* totals = sw.ghist + int64_t(tiles) * kRadix;
+    digit_prefix_kernel<<<kRadix, kSortThreads, 0, stream>>>(sw.ghist, totals, tiles);
     if (p == 0) {
       radix_scatter_kernel<IdT, true><<<tiles, kSortThreads, 0, stream>>>(
-          src_k, src_v, dst_k, dst_v, int(n), shift, sw.ghist, tiles);
+          src_k, src_v, dst_k, dst_v, int(n), shift, sw.ghist, totals, tiles);
     } else {
       radix_scatter_kernel<int32_t, false><<<tiles, kSortThreads, 0, stream>>>(
-          src_k, src_v, dst_k, dst_v, int(n), shift, sw.ghist, tiles);
+          src_k, src_v, dst_k, dst_v, int(n), shift, sw.ghist, totals, tiles);
     }
     int st = check_launch("radix sort pass");
     if (st != TEXB_OK) return st;
@@ -366,7 +449,7 @@ int ids_inspect_impl(const void* ids, int id_bytes, int64_t n, int32_t* stats_de
   init_inspect_stats_kernel<<<1, 32, 0, stream>>>(stats_dev);
   if (n > 0) {
     int64_t blocks = ceil_div(n, 256 * 4);
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > 148 * 4) blocks = 148 * 4;
     if (id_bytes == 4)
       inspect_ids_kernel<int32_t><<<unsigned(blocks), 256, 0, stream>>>(
           static_cast<const int32_t*>(ids), n, stats_dev);

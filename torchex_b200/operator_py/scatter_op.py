@@ -25,8 +25,35 @@ from torch.autograd import Function
 from .. import _native
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """Handle of the current stream of the current device.  The raw getter skips
+    the construction of a ``torch.cuda.Stream`` object (about 15 us per call,
+    which is more than a small reduction takes on the GPU)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
+
+
+class _on_device:
+    """``torch.cuda.device(dev)`` that does nothing when ``dev`` is already current."""
+
+    def __init__(self, dev):
+        self.idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+        return False
 
 
 def _scratch(nbytes: int, device) -> torch.Tensor:
@@ -59,6 +86,27 @@ class ScatterData:
     synchronises with the device twice (id statistics, plan statistics).
     """
 
+    _unq_inv = None
+    _ids64 = None
+
+    @property
+    def unq_inv(self) -> torch.Tensor:
+        """int32 ids in the caller's order (scatter_op.py:12 of the reference).  The
+        kernels work from ``sid`` / ``perm``, so int64 ids are only narrowed on demand."""
+        if self._unq_inv is None and self._ids64 is not None:
+            self._unq_inv = self._ids64.int()
+            self._ids64 = None
+        return self._unq_inv
+
+    @unq_inv.setter
+    def unq_inv(self, value: torch.Tensor) -> None:
+        self._unq_inv = value
+
+    @property
+    def num_total(self) -> int:
+        """Number of points the plan was built for."""
+        return int(self.sid.numel())
+
     def __init__(self, unq_inv: torch.Tensor, unq_cnts: torch.Tensor) -> None:
         assert unq_inv.ndim in (1, 2), \
             f"unq_inv in ScatterData should be 1 or 2-dims, but got {unq_inv.ndim}-dims"
@@ -77,11 +125,11 @@ class ScatterData:
         lib = _native.lib()
         id_bytes = ids.element_size()
 
-        with torch.cuda.device(dev):
+        with _on_device(dev):
             stats = torch.empty(4, dtype=torch.int32, device=dev)
             _native.check(lib.texb_ids_inspect(ids.data_ptr(), id_bytes, n, stats.data_ptr(), _stream()),
                           "texb_ids_inspect")
-            is_sorted, id_min, id_max, _runs = (int(v) for v in stats.cpu())
+            is_sorted, id_min, id_max, _runs = stats.tolist()
             if n > 0 and (id_min < 0 or id_max >= m):
                 raise ValueError(f"unq_inv holds ids in [{id_min}, {id_max}] but unq_cnts "
                                  f"describes {m} segments")
@@ -110,8 +158,8 @@ class ScatterData:
             elif self.is_sorted:
                 self.unq_inv = self.sid
             else:
-                self.unq_inv = ids.int()
-            max_cnt, num_empty, bad_ids, _ = (int(v) for v in plan_stats.cpu())
+                self._ids64 = ids  # narrowed to int32 when ``unq_inv`` is first read
+            max_cnt, num_empty, bad_ids, _ = plan_stats.tolist()
         if bad_ids:
             raise ValueError(f"{bad_ids} ids of unq_inv lie outside [0, {m})")
         self.max_cnt = max_cnt
@@ -131,11 +179,11 @@ def _plan_from_keys(cls, keys: torch.Tensor):
     keys = keys.contiguous()
     n, dev, lib = keys.numel(), keys.device, _native.lib()
     self = cls.__new__(cls)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         stats = torch.empty(4, dtype=torch.int32, device=dev)
         _native.check(lib.texb_ids_inspect(keys.data_ptr(), keys.element_size(), n, stats.data_ptr(), _stream()),
                       "texb_ids_inspect")
-        is_sorted, k_min, k_max, _ = (int(v) for v in stats.cpu())
+        is_sorted, k_min, k_max, _ = stats.tolist()
         if n > 0 and (k_min < 0 or k_max >= 2 ** 31 - 1):
             raise ValueError(f"keys must lie in [0, 2^31 - 1); got [{k_min}, {k_max}]")
         bound = k_max + 1 if n > 0 else 1
@@ -146,7 +194,7 @@ def _plan_from_keys(cls, keys: torch.Tensor):
                                             sorted_keys.data_ptr(), None if perm is None else perm.data_ptr(),
                                             stats.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
                       "texb_unique_count")
-        m = int(stats.cpu()[0])
+        m = stats.tolist()[0]
         self.sid = torch.empty(n, dtype=torch.int32, device=dev)
         self.preSum = torch.empty(m + 1, dtype=torch.int32, device=dev)
         self.unq_inv = torch.empty(n, dtype=torch.int32, device=dev)
@@ -162,7 +210,7 @@ def _plan_from_keys(cls, keys: torch.Tensor):
         _native.check(lib.texb_plan_balance(self.sid.data_ptr(), n, self.balance.data_ptr(),
                                             self.balance.numel(), _stream()), "texb_plan_balance")
         self.unq_cnts = (self.preSum[1:] - self.preSum[:-1]).long().unsqueeze(-1)
-        self.max_cnt = int(plan_stats.cpu()[0])
+        self.max_cnt = plan_stats.tolist()[0]
     self.has_empty = False
     self.num_unq = m
     self._perm_ptr = None if self.perm is None else self.perm.data_ptr()
@@ -224,9 +272,9 @@ ScatterData.from_coords = classmethod(_from_coords)
 def ingroup_rank(data: ScatterData) -> torch.Tensor:
     """Index of every point inside its segment (int64 [num_total]), in increasing
     row order, from an existing plan."""
-    n = data.unq_inv.numel()
+    n = data.num_total
     out = torch.empty(n, dtype=torch.int64, device=data.sid.device)
-    with torch.cuda.device(out.device):
+    with _on_device(out.device):
         _native.check(_native.lib().texb_segment_rank(data.sid.data_ptr(), data._perm_ptr, data.preSum.data_ptr(),
                                                       n, out.data_ptr(), _stream()), "texb_segment_rank")
     return out
@@ -261,8 +309,8 @@ def _reduce(op: int, feats: torch.Tensor, data: ScatterData, want_arg: bool, arg
     n, c = feats.shape
     if feats.dtype == torch.bfloat16 and (c % 8 != 0 or c < 128 or feats.data_ptr() % 16 != 0):
         feats = feats.float()  # the bf16 kernel covers wide, aligned rows; others are widened first
-    if n != data.unq_inv.numel():
-        raise RuntimeError(f"feats has {n} rows but ScatterData was built for {data.unq_inv.numel()}")
+    if n != data.num_total:
+        raise RuntimeError(f"feats has {n} rows but ScatterData was built for {data.num_total}")
     dev = feats.device
     if dev != data.sid.device:
         raise RuntimeError("feats and ScatterData live on different devices")
@@ -305,8 +353,8 @@ def _reduce_pair(op: int, feats: torch.Tensor, data: ScatterData, arg_base: int 
     n, c = feats.shape
     if feats.dtype == torch.bfloat16 and (c % 8 != 0 or c != 128 or feats.data_ptr() % 16 != 0):
         feats = feats.float()  # the two-output bf16 kernel covers aligned 128-channel rows
-    if n != data.unq_inv.numel():
-        raise RuntimeError(f"feats has {n} rows but ScatterData was built for {data.unq_inv.numel()}")
+    if n != data.num_total:
+        raise RuntimeError(f"feats has {n} rows but ScatterData was built for {data.num_total}")
     dev = feats.device
     if dev != data.sid.device:
         raise RuntimeError("feats and ScatterData live on different devices")
@@ -317,7 +365,7 @@ def _reduce_pair(op: int, feats: torch.Tensor, data: ScatterData, arg_base: int 
     out_sum = torch.empty((m, c), dtype=torch.float32, device=dev)
     out_max = torch.empty((m, c), dtype=torch.float32, device=dev)
     arg = torch.empty((m, c), dtype=torch.int32, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         stream = _stream()
         key = (c, stream, "pair")
         ws = data._workspaces.get(key)
@@ -343,11 +391,11 @@ def _broadcast_back(mode: str, data: "ScatterData", g: torch.Tensor, arg) -> tor
     """Gradient of the input rows: one fused pass in segment-sorted order (the
     plan's ``sid`` / ``perm``), so each row of ``g`` is fetched once per segment."""
     g = _grad(g)
-    n, c, m = data.unq_inv.numel(), g.shape[1], data.num_unq
+    n, c, m = data.num_total, g.shape[1], data.num_unq
     g_input = g.new_empty((n, c))
     lib = _native.lib()
     perm = None if data.perm is None else data.perm.data_ptr()
-    with torch.cuda.device(g.device):
+    with _on_device(g.device):
         if mode == "sum":
             st = lib.texb_scatter_sum_backward(g.data_ptr(), data.sid.data_ptr(), perm, g_input.data_ptr(),
                                                n, c, m, _stream())
@@ -431,10 +479,10 @@ class ScatterMeanMaxFunction(Function):
         (arg,) = ctx.saved_tensors
         data = ctx.plan
         g_mean, g_max = _grad(g_mean), _grad(g_max)
-        n, c, m = data.unq_inv.numel(), g_mean.shape[1], data.num_unq
+        n, c, m = data.num_total, g_mean.shape[1], data.num_unq
         g_input = g_mean.new_empty((n, c))
         perm = None if data.perm is None else data.perm.data_ptr()
-        with torch.cuda.device(g_mean.device):
+        with _on_device(g_mean.device):
             _native.check(
                 _native.lib().texb_scatter_mean_max_backward(
                     g_mean.data_ptr(), g_max.data_ptr(), arg.data_ptr(), data.sid.data_ptr(), perm,
@@ -455,7 +503,7 @@ class GetPreSumFunction(Function):
         unq_inv = unq_inv.contiguous()
         num_unq = int(unq_inv[-1]) + 1 if unq_inv.numel() else 0
         pre_sum = unq_inv.new_empty(num_unq + 1)
-        with torch.cuda.device(unq_inv.device):
+        with _on_device(unq_inv.device):
             _native.check(_native.lib().texb_get_pre_sum(unq_inv.data_ptr(), pre_sum.data_ptr(),
                                                          unq_inv.numel(), num_unq, _stream()),
                           "texb_get_pre_sum")
