@@ -102,6 +102,34 @@ class ScatterData:
     def unq_inv(self, value: torch.Tensor) -> None:
         self._unq_inv = value
 
+    _unq_cnts = None
+    _max_cnt = None
+    _plan_stats = None
+
+    @property
+    def unq_cnts(self) -> torch.Tensor:
+        """Rows per segment, [num_unq, 1] (scatter_op.py:13-15 of the reference).  A plan
+        built from keys derives it from the offsets when first read."""
+        if self._unq_cnts is None:
+            self._unq_cnts = (self.preSum[1:] - self.preSum[:-1]).long().unsqueeze(-1)
+        return self._unq_cnts
+
+    @unq_cnts.setter
+    def unq_cnts(self, value: torch.Tensor) -> None:
+        self._unq_cnts = value
+
+    @property
+    def max_cnt(self) -> int:
+        """Rows of the largest segment (scatter_op.py:19 of the reference; nothing here
+        depends on it).  A plan built from keys copies it from the device when first read."""
+        if self._max_cnt is None:
+            self._max_cnt = self._plan_stats.tolist()[0]
+        return self._max_cnt
+
+    @max_cnt.setter
+    def max_cnt(self, value: int) -> None:
+        self._max_cnt = int(value)
+
     @property
     def num_total(self) -> int:
         """Number of points the plan was built for."""
@@ -209,8 +237,7 @@ def _plan_from_keys(cls, keys: torch.Tensor):
         self.balance = torch.empty(_native.BALANCE_PIECES + 1, dtype=torch.int32, device=dev)
         _native.check(lib.texb_plan_balance(self.sid.data_ptr(), n, self.balance.data_ptr(),
                                             self.balance.numel(), _stream()), "texb_plan_balance")
-        self.unq_cnts = (self.preSum[1:] - self.preSum[:-1]).long().unsqueeze(-1)
-        self.max_cnt = plan_stats.tolist()[0]
+        self._plan_stats = plan_stats  # max_cnt is read from the device when first asked for
     self.has_empty = False
     self.num_unq = m
     self._perm_ptr = None if self.perm is None else self.perm.data_ptr()
@@ -252,17 +279,34 @@ def _from_coords(cls, coors: torch.Tensor, grid_size=None):
         total *= int(g)
     if total >= 2 ** 31 - 1:
         raise ValueError(f"grid of {total} cells does not fit the 31-bit key space")
-    key = torch.zeros(coors.shape[0], dtype=torch.int64, device=coors.device)
-    for j in range(d):
-        key = key * int(grid_size[j]) + c64[:, j]
+    # key = sum_j coors[:, j] * (product of the extents after j): one fused multiply-add per column
+    stride = [1] * d
+    for j in range(d - 2, -1, -1):
+        stride[j] = stride[j + 1] * int(grid_size[j + 1])
+    key = c64[:, 0] * stride[0]
+    for j in range(1, d):
+        key.add_(c64[:, j], alpha=stride[j])
     self = _plan_from_keys(cls, key)
-    rest = self.unq_keys.long()
-    cols = []
-    for j in reversed(range(d)):
-        cols.append(rest % int(grid_size[j]))
-        rest = rest // int(grid_size[j])
-    self.unq_coors = torch.stack(list(reversed(cols)), 1).to(coors.dtype)
+    self._coor_grid, self._coor_dtype = [int(g) for g in grid_size], coors.dtype
     return self
+
+
+def _decode_unq_coors(self) -> torch.Tensor:
+    """Distinct coordinate rows [num_unq, D] of a plan built by ``from_coords``
+    (decoded from the distinct keys when first read)."""
+    if self._unq_coors is None and self._coor_grid is not None:
+        rest = self.unq_keys.long()
+        cols = []
+        for g in reversed(self._coor_grid):
+            cols.append(rest % g)
+            rest = rest // g
+        self._unq_coors = torch.stack(list(reversed(cols)), 1).to(self._coor_dtype)
+    return self._unq_coors
+
+
+ScatterData._unq_coors = None
+ScatterData._coor_grid = None
+ScatterData.unq_coors = property(_decode_unq_coors)
 
 
 ScatterData.from_keys = classmethod(_from_keys)
