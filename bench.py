@@ -154,6 +154,13 @@ def run_ours(args):
         workload = (f"voxel frames: {args.frames} x 200,000 points, C={c} fp32, M={m:,} voxels from torch.unique "
                     "(ids unsorted); step = scatter_sum + scatter_mean + scatter_max forward with a prebuilt plan "
                     "[secondary workload]")
+    elif args.workload == "uniform":
+        # ids drawn uniformly from M segments (every segment present): M = 1 is one run,
+        # M = N / 2 is the two-rows-per-segment regime of voxel pooling
+        ids, cnt = W.uniform_ids(n, m, SEED + rank)
+        workload = (f"uniform segments: N={n:,} points, C={c} fp32, M={m:,} segments of about {n / m:.1f} points, "
+                    "ids in random order; step = scatter_sum + scatter_mean + scatter_max forward with a prebuilt plan "
+                    "[secondary workload]")
     else:
         ids, cnt = W.skewed_ids(n, m, seed=SEED + rank, giant=n // 10)
         workload = (f"skewed segments: N={n:,} points, C={c} fp32, M={m:,} segments "
@@ -686,7 +693,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--e2e-steps", type=int, default=10)
-    ap.add_argument("--workload", choices=["skewed", "voxel"], default="skewed",
+    ap.add_argument("--workload", choices=["skewed", "voxel", "uniform"], default="skewed",
                     help="skewed = the headline configuration; voxel = concatenated dynamic-voxelisation frames")
     ap.add_argument("--features", choices=["fp32", "bf16"], default="fp32",
                     help="bf16: the same reductions on bf16 feature rows (secondary; the headline is fp32)")
