@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from oracle import scatter_oracle as O
-from torchex_b200 import ScatterData, _native, scatter_max, scatter_mean, scatter_sum, workloads as W
+from torchex_b200 import ScatterData, _native, scatter_max, scatter_mean, scatter_mean_max, scatter_sum, workloads as W
 from tests.gpu_util import ABS, DEV, REL, check_forward
 
 pytestmark = pytest.mark.gpu
@@ -197,6 +197,9 @@ def test_golden_hand_checkable_cases():
         assert np.array_equal(s, d[f"{name}.sum"].astype(np.float32)), name      # small integers / infinities: exact
         mean = scatter_mean(feat, data).cpu().numpy()
         assert np.array_equal(mean, d[f"{name}.mean"].astype(np.float32)), name
+        p_mean, p_max, p_arg = scatter_mean_max(feat, data)  # the one-pass form, same fixtures
+        assert np.array_equal(p_mean.cpu().numpy(), d[f"{name}.mean"].astype(np.float32)), name
+        assert np.array_equal(p_max.cpu().numpy(), want_max) and np.array_equal(p_arg.cpu().numpy(), d[f"{name}.arg"]), name
 
 
 def test_mean_is_the_sum_divided_like_torch_divides():
