@@ -162,9 +162,11 @@ def run_ours(args):
                     "ids in random order; step = scatter_sum + scatter_mean + scatter_max forward with a prebuilt plan "
                     "[secondary workload]")
     else:
-        ids, cnt = W.skewed_ids(n, m, seed=SEED + rank, giant=n // 10)
+        ids, cnt = W.skewed_ids(n, m, seed=SEED + rank, giant=n // 10, shuffled=not args.sorted_ids)
         workload = (f"skewed segments: N={n:,} points, C={c} fp32, M={m:,} segments "
-                    f"(Zipf 1.2 sizes + one {n // 10:,}-point segment), ids randomly permuted; "
+                    f"(Zipf 1.2 sizes + one {n // 10:,}-point segment), "
+                    + ("ids sorted (the layout the reference requires) [secondary workload]; " if args.sorted_ids
+                       else "ids randomly permuted; ") +
                     "step = scatter_sum + scatter_mean + scatter_max forward with a prebuilt plan"
                     + ("" if (n, c, m) == (N_POINTS, CHANNELS, N_SEGMENTS) else " [reduced size, for profiling only]"))
     bf16 = args.features == "bf16"
@@ -267,7 +269,7 @@ def run_ours(args):
                 "bracketed_in_timed_region": {"us_per_launch": round(sum_ms * 1e3, 2), "launches": len(ev_sum),
                                               "achieved": round(bracketed, 1), "frac": round(bracketed / peak, 4)},
                 "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (n, c, m) == (N_POINTS, CHANNELS, N_SEGMENTS)
-                and args.workload == "skewed" and not bf16 else None}
+                and args.workload == "skewed" and not bf16 and not args.sorted_ids else None}
 
     # ---- end to end through the public operators, host buffers in pinned memory
     e2e = None
@@ -697,6 +699,8 @@ def main():
                     help="skewed = the headline configuration; voxel = concatenated dynamic-voxelisation frames")
     ap.add_argument("--features", choices=["fp32", "bf16"], default="fp32",
                     help="bf16: the same reductions on bf16 feature rows (secondary; the headline is fp32)")
+    ap.add_argument("--sorted-ids", action="store_true",
+                    help="skewed workload with ids already sorted (secondary; the headline has them permuted)")
     ap.add_argument("--frames", type=int, default=4, help="frames of the voxel workload")
     ap.add_argument("--points", type=int, default=N_POINTS, help="reduced sizes are for profiling only")
     ap.add_argument("--segments", type=int, default=N_SEGMENTS)
