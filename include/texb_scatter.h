@@ -189,7 +189,16 @@ size_t texb_reduce_workspace_bytes(int64_t n, int channel);
  *                 larger batch; "no row" stays -1); ties go to the lowest row;
  *                 NaN never wins (as in the reference, scatter_kernel.cu:146-151).
  * No floating-point atomics: results are bit-reproducible run to run.
- * Limits: n < 2^31, channel >= 1. */
+ * Limits: n < 2^31, channel >= 1.
+ * Stream order: the kernels are programmatic dependent launches.  feats is read
+ * and every output is written only after all earlier work of the stream has
+ * completed, as for any kernel.  The plan arrays (sid, perm, offsets, balance)
+ * may be read while the kernel that directly precedes this call in the stream
+ * is still finishing, if that kernel releases its dependents early; they must
+ * therefore be complete before that kernel starts -- which holds for arrays
+ * built by texb_plan_build / texb_plan_balance / texb_unique_fill (those kernels
+ * never release dependents early) and for anything ordered by an event or a
+ * synchronisation. */
 int texb_segment_reduce(int op, const float* feats, const int32_t* sid,
                         const int32_t* perm, const int32_t* offsets,
                         int has_empty, const int32_t* balance, int balance_len,

@@ -859,16 +859,21 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
   __shared__ unsigned s_flag[SLOTS];
   __shared__ __align__(8) unsigned long long s_bar[BULK ? GPC * S : 1];  // one mbarrier per (group, stage)
 
-#if __CUDA_ARCH__ >= 900
-  // Let the dependent fix-up grid be scheduled now (it parks at its own
-  // griddepcontrol.wait until this grid has finished); a no-op for a plain launch.
-  // This grid may itself be a dependent launch of whatever kernel precedes it in
+  // This grid may be a programmatic dependent launch of whatever kernel precedes it in
   // the stream (typically the fix-up of the previous reduction): its CTAs are then
-  // placed while that kernel drains, and the wait below holds them until all of
-  // its memory operations are visible, before anything is read.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // placed while that kernel drains.  Everything up to wait_for_stream() below reads
+  // only the plan (sid, perm, balance) -- arrays that were complete before that kernel
+  // began, since the plan kernels never release their dependents early -- and
+  // writes only this CTA's shared memory; the features are read and global memory is
+  // written after it.  A no-op for a plain launch.
+  auto wait_for_stream = [] {
+#if __CUDA_ARCH__ >= 900
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Let the dependent fix-up grid be scheduled now (it parks at its own wait until
+    // this grid has finished).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #endif
+  };
   const unsigned t_start = global_timer_lo();
   const int lane_g = threadIdx.x & (LPR - 1);
   const int group = threadIdx.x / LPR;
@@ -1043,6 +1048,7 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
     // (at the start of the range: unless the first run continues from the left).
     unsigned carry = first_open_left ? 0u : 1u;
 
+    wait_for_stream();
 #pragma unroll
     for (int bb = 0; bb < S - 1; ++bb) issue(bb, bb);
     int stage_c = 0;        // ring stage of the batch being reduced
@@ -1128,6 +1134,8 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
       const int sid_now = __shfl_sync(gmask, tile_reg(cur_sid_r, jl & ~(B - 1)), jl & (LPR - 1), LPR);
       close_run(sid_now, L - run_start, true);
     }
+  } else {
+    wait_for_stream();
   }
   if constexpr (!BULK) cp_async_wait<0>();
   __syncthreads();
