@@ -79,3 +79,42 @@ def test_random_case_against_the_oracle(case):
     if empty.any():
         assert (s.cpu().numpy()[empty] == 0).all() and (arg.cpu().numpy()[empty] == -1).all(), label
     assert _native.device_wait_timeouts() == 0 and _native.device_bad_indices() == bad_before, label
+
+
+@pytest.mark.parametrize("case", range(16))
+def test_random_backward_against_the_oracle(case):
+    rng = np.random.default_rng(5000 + case)
+    c = int(rng.choice([1, 3, 4, 8, 20, 32, 64, 100, 128, 136, 256]))
+    m = int(rng.integers(1, 600))
+    sizes = rng.integers(0 if case % 2 else 1, 12, m)
+    if sizes.sum() == 0:
+        sizes[0] = 3
+    ids = np.repeat(np.arange(m), sizes)
+    n = ids.size
+    if case % 3:
+        ids = ids[rng.permutation(n)]
+    t_ids, cnt = torch.from_numpy(ids), torch.from_numpy(sizes)
+    feat = W.features(n, c, 6000 + case)
+    if n > 2:
+        feat[n - 1] = feat[0]  # a possible tie
+    g1, g2 = W.features(m, c, 7000 + case), W.features(m, c, 8000 + case)
+    data = ScatterData(t_ids.to(DEV), cnt.to(DEV))
+    _, want_arg = O.spec_scatter_max(feat, t_ids, m)
+    label = f"case {case}: n={n} c={c} m={m}"
+
+    x = feat.to(DEV).requires_grad_(True)
+    scatter_sum(x, data).backward(g1.to(DEV))
+    assert np.array_equal(x.grad.cpu().numpy(), O.spec_sum_backward(g1, t_ids)), label
+    x.grad = None
+    scatter_mean(x, data).backward(g1.to(DEV))
+    want_mean = O.spec_mean_backward(g1, t_ids, cnt)
+    assert np.array_equal(x.grad.cpu().numpy(), want_mean), label
+    x.grad = None
+    mx, _ = scatter_max(x, data)
+    mx.backward(g2.to(DEV))
+    want_max = O.spec_max_backward(g2, want_arg, n)
+    assert np.array_equal(x.grad.cpu().numpy(), want_max), label
+    x.grad = None
+    mean, mx, _ = scatter_mean_max(x, data)
+    torch.autograd.backward([mean, mx], [g1.to(DEV), g2.to(DEV)])
+    assert np.array_equal(x.grad.cpu().numpy(), want_mean + want_max), label
