@@ -39,6 +39,12 @@ extern "C" {
 #define TEXB_OP_MEAN 1
 #define TEXB_OP_MAX 2
 
+/* bits of the plan_flags argument of the reduce entry points (0 and 1 keep the
+ * meaning of the former has_empty argument) */
+#define TEXB_PLAN_HAS_EMPTY 1 /* some segment may have no rows: fill their output rows */
+#define TEXB_PLAN_SETTLED 2   /* the plan arrays were complete, and the host had synchronised
+                                 with their stream, before this call (see "Stream order") */
+
 /* Library version (major * 100 + minor). */
 int texb_version(void);
 
@@ -150,10 +156,12 @@ int texb_unique_fill(const int32_t* sorted_keys, const int32_t* perm, int64_t n,
  * row order, from a plan (sid, perm or NULL, offsets).  The deterministic form of
  * TorchEx's ingroup_inds, whose kernel hands out the indices with an atomic
  * counter in arrival order (torchex/src/ingroup_inds/ingroup_inds_kernel.cu:17-30):
- * both give each segment the set {0 .. count-1}. */
+ * both give each segment the set {0 .. count-1}.  A segment id outside
+ * [0, num_segments) or a perm entry outside [0, n) is skipped and counted
+ * (texb_device_status) instead of being used as an address. */
 int texb_segment_rank(const int32_t* sid, const int32_t* perm,
-                      const int32_t* offsets, int64_t n, int64_t* rank_out,
-                      void* stream);
+                      const int32_t* offsets, int64_t n, int64_t num_segments,
+                      int64_t* rank_out, void* stream);
 
 /* Drop-in for getPreSum_launcher(unq_inv, preSum, num_total)
  * (torchex/src/scatter/scatter.cpp:18, scatter_kernel.cu:173-175): sorted
@@ -177,9 +185,10 @@ size_t texb_reduce_workspace_bytes(int64_t n, int channel);
  * segment order; it must list the rows of one segment in increasing order
  * (texb_plan_build does) for the lowest-row tie rule of TEXB_OP_MAX to hold.
  * balance / balance_len: the table of texb_plan_balance, or NULL / 0 for an
- * even split of the rows.  offsets may be NULL when has_empty == 0; otherwise the rows
- * of empty segments are filled (0 for sum/mean; -FLT_MAX and -1 for max, what
- * the reference kernel writes for an empty range).
+ * even split of the rows.  plan_flags: TEXB_PLAN_* bits.  offsets may be NULL unless
+ * TEXB_PLAN_HAS_EMPTY is set; with it the rows of empty segments are filled (0 for
+ * sum/mean; -FLT_MAX and -1 for max, what the reference kernel writes for an empty
+ * range).  Setting the bit when no segment is empty only costs the check.
  *   TEXB_OP_SUM : fp32 sum, compensated (error-free transformation) so that
  *                 long segments stay within 1e-6 + 1e-5*|x| of the exact sum.
  *   TEXB_OP_MEAN: that sum divided (IEEE fp32 division) by the row count.
@@ -190,18 +199,22 @@ size_t texb_reduce_workspace_bytes(int64_t n, int channel);
  *                 NaN never wins (as in the reference, scatter_kernel.cu:146-151).
  * No floating-point atomics: results are bit-reproducible run to run.
  * Limits: n < 2^31, channel >= 1.
- * Stream order: the kernels are programmatic dependent launches.  feats is read
- * and every output is written only after all earlier work of the stream has
- * completed, as for any kernel.  The plan arrays (sid, perm, offsets, balance)
- * may be read while the kernel that directly precedes this call in the stream
- * is still finishing, if that kernel releases its dependents early; they must
- * therefore be complete before that kernel starts -- which holds for arrays
- * built by texb_plan_build / texb_plan_balance / texb_unique_fill (those kernels
- * never release dependents early) and for anything ordered by an event or a
- * synchronisation. */
+ * Stream order: the kernels are programmatic dependent launches: their CTAs may
+ * be placed while the kernel that precedes the call in the stream is still
+ * finishing, and they wait (griddepcontrol.wait) until all earlier work of the
+ * stream has completed and its memory is visible before they read or write
+ * anything -- so the call behaves like any kernel launch.  With
+ * TEXB_PLAN_SETTLED the kernels read the plan arrays (sid, perm, balance) BEFORE
+ * that wait, which hides about 1.5 us of prologue per call in a sequence of
+ * reductions.  Only set the bit when the plan arrays were completely written and
+ * the host has since synchronised with the stream (or device) that wrote them --
+ * e.g. a plan built once and reused, after any cudaStreamSynchronize /
+ * cudaEventSynchronize that followed its construction.  Work merely ordered
+ * earlier in the same stream is NOT enough: its writes become visible at the
+ * wait, not before. */
 int texb_segment_reduce(int op, const float* feats, const int32_t* sid,
                         const int32_t* perm, const int32_t* offsets,
-                        int has_empty, const int32_t* balance, int balance_len,
+                        int plan_flags, const int32_t* balance, int balance_len,
                         int64_t n, int channel, int64_t num_segments,
                         float* out, int32_t* arg, int32_t arg_base,
                         void* workspace, size_t workspace_bytes, void* stream);
@@ -216,7 +229,7 @@ int texb_segment_reduce(int op, const float* feats, const int32_t* sid,
  * Workspace: texb_reduce_workspace_bytes, as for fp32. */
 int texb_segment_reduce_bf16(int op, const void* feats_bf16, const int32_t* sid,
                              const int32_t* perm, const int32_t* offsets,
-                             int has_empty, const int32_t* balance,
+                             int plan_flags, const int32_t* balance,
                              int balance_len, int64_t n, int channel,
                              int64_t num_segments, float* out, int32_t* arg,
                              int32_t arg_base, void* workspace,
@@ -237,12 +250,32 @@ int texb_segment_reduce_bf16(int op, const void* feats_bf16, const int32_t* sid,
 size_t texb_reduce_pair_workspace_bytes(int64_t n, int channel);
 int texb_segment_reduce_pair(int op, const void* feats, int feature_bytes,
                              const int32_t* sid, const int32_t* perm,
-                             const int32_t* offsets, int has_empty,
+                             const int32_t* offsets, int plan_flags,
                              const int32_t* balance, int balance_len, int64_t n,
                              int channel, int64_t num_segments, float* out_sum,
                              float* out_max, int32_t* arg, int32_t arg_base,
                              void* workspace, size_t workspace_bytes,
                              void* stream);
+
+/* One-launch reduction for small inputs made of short segments: one warp per
+ * segment, straight from offsets[num_segments + 1] (TorchEx's preSum) and, for
+ * unsorted ids, perm[n]; no workspace, no fix-up launch, no sid / balance arrays,
+ * and empty segments are written by the kernel itself (0 for sum/mean, -FLT_MAX
+ * and -1 for max).  It takes the place of scatter_sum_launcher /
+ * scatter_max_launcher (torchex/src/scatter/scatter.cpp:12-16) on inputs of a
+ * megabyte or so, where one launch of the reference's kernel used to beat the
+ * launch pair of texb_segment_reduce.  Same arithmetic as texb_segment_reduce
+ * (compensated sums, IEEE division, lowest row on ties, NaN never wins); max and
+ * argmax are bit-identical to it, sums may differ in the last bit.
+ * The result is correct for every input, but a segment is walked by a single
+ * warp: use it when texb_segment_reduce_small_ok(n, channel, max_cnt) returns 1
+ * (features of at most 8 MB, largest segment at most 128 rows; max_cnt < 0 =
+ * unknown gives 0). */
+int texb_segment_reduce_small_ok(int64_t n, int channel, int64_t max_cnt);
+int texb_segment_reduce_small(int op, const float* feats, const int32_t* offsets,
+                              const int32_t* perm, int64_t n, int channel,
+                              int64_t num_segments, float* out, int32_t* arg,
+                              int32_t arg_base, void* stream);
 
 /* texb_segment_reduce for callers that cannot allocate device memory.
  * No counterpart in the reference.
@@ -275,7 +308,7 @@ int texb_segment_reduce_pair(int op, const void* feats, int feature_bytes,
 size_t texb_static_scratch_bytes(void);
 int texb_segment_reduce_static(int op, const float* feats, const int32_t* sid,
                                const int32_t* perm, const int32_t* offsets,
-                               int has_empty, const int32_t* balance,
+                               int plan_flags, const int32_t* balance,
                                int balance_len, int64_t n, int channel,
                                int64_t num_segments, float* out, int32_t* arg,
                                int32_t arg_base, void* stream);
@@ -286,9 +319,11 @@ size_t texb_scatter_compat_workspace_bytes(int64_t num_total, int channel);
 
 /* Drop-in for scatter_sum_launcher(feats, preSum, out, channel, num_unq,
  * max_cnt) (torchex/src/scatter/scatter.cpp:12-13): feats in segment order.
- * max_cnt is accepted and ignored (the reference sizes its thread blocks from
- * it, scatter_kernel.cu:177-183).  num_total = feats rows, which the reference
- * takes from the tensor. */
+ * max_cnt (the reference sizes its thread blocks from it,
+ * scatter_kernel.cu:177-183) only selects the path here: a small input whose
+ * largest segment is short (texb_segment_reduce_small_ok) takes the one-launch
+ * kernel and touches no workspace; pass 0 or a negative value if it is not
+ * known.  num_total = feats rows, which the reference takes from the tensor. */
 int texb_scatter_sum(const float* feats, const int32_t* pre_sum, float* out,
                      int channel, int num_unq, int max_cnt, int64_t num_total,
                      void* workspace, size_t workspace_bytes, void* stream);

@@ -15,6 +15,8 @@ void scatter_sum_launcher(const float* const feats, const int* const preSum, flo
 void scatter_max_launcher(const float* const feats, const int* const preSum, float* const out,
                           int* const arg, int channel, int num_unq, int max_cnt);
 void getPreSum_launcher(const int* const unq_inv, int* const preSum, int num_total);
+// torchex/src/ingroup_inds/ingroup_inds.cpp:14-19 declares it like this
+void ingroup_inds_launcher(const long* group_inds, long* out_inds, int N, int max_group_id);
 
 namespace {
 int block_x(int max_cnt) {
@@ -68,6 +70,15 @@ int torchex_ref_scatter_max(const float* feats, const int* pre_sum, float* out, 
 int torchex_ref_get_pre_sum(const int* unq_inv, int* pre_sum, int num_total) {
   if (num_total < 1) return 1;
   getPreSum_launcher(unq_inv, pre_sum, num_total);
+  return finish();
+}
+
+// The reference's ingroup_inds (ingroup_inds_kernel.cu:17-59): out_inds[i] = arrival
+// number of element i inside its group (an atomic counter per group, so the order
+// within a group is not defined).  It allocates and frees its own counters.
+int torchex_ref_ingroup_inds(const long* group_inds, long* out_inds, int n, int max_group_id) {
+  if (n < 1 || max_group_id < 0) return 1;
+  ingroup_inds_launcher(group_inds, out_inds, n, max_group_id);
   return finish();
 }
 

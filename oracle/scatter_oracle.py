@@ -24,6 +24,7 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "liboracle_scatter.so")
 REF_SO = os.path.join(HERE, "_ref", "libtorchex_scatter_ref.so")
+REF_OP_PYC = os.path.join(HERE, "_ref", "torchex_scatter_op.pyc")
 FLT_MAX = float(np.finfo(np.float32).max)
 
 _c = ctypes
@@ -31,10 +32,24 @@ _oracle = None
 _ref = None
 
 
+def _make_vars():
+    """``REFERENCE=...`` for make when the environment names the reference tree
+    (TORCHEX_REFERENCE); otherwise the Makefile's own default applies."""
+    ref = os.environ.get("TORCHEX_REFERENCE")
+    return [f"REFERENCE={ref}"] if ref else []
+
+
+def reference_sources_present() -> bool:
+    """True when the reference tree the Makefile would compile from exists here."""
+    proc = subprocess.run(["make", "-s", "-C", HERE, *_make_vars(), "print-ref-src"], capture_output=True, text=True)
+    path = proc.stdout.strip().splitlines()[-1] if proc.returncode == 0 and proc.stdout.strip() else ""
+    return bool(path) and os.path.exists(path)
+
+
 def build(reference: bool = True) -> None:
     """Compiles the C oracle (and the reference kernels when their sources exist)."""
     target = [] if reference else ["liboracle_scatter.so"]
-    proc = subprocess.run(["make", "-C", HERE, *target], capture_output=True, text=True)
+    proc = subprocess.run(["make", "-C", HERE, *_make_vars(), *target], capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError("oracle build failed:\n" + proc.stdout + proc.stderr)
 
@@ -63,7 +78,34 @@ def reference_lib() -> ctypes.CDLL:
         _ref.torchex_ref_scatter_max.argtypes = [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                                  _c.c_int, _c.c_int, _c.c_int, _c.c_int64]
         _ref.torchex_ref_get_pre_sum.argtypes = [_c.c_void_p, _c.c_void_p, _c.c_int]
+        if hasattr(_ref, "torchex_ref_ingroup_inds"):
+            _ref.torchex_ref_ingroup_inds.argtypes = [_c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int]
     return _ref
+
+
+def reference_operator_module(scatter_ext_module):
+    """TorchEx's own operator_py/scatter_op.py, byte-compiled unmodified from the
+    reference tree into oracle/_ref, loaded with ``scatter_ext_module`` standing where
+    it imports its native module (``import scatter_ext``, scatter_op.py:4).  Returns
+    None when the byte-compiled file was not built."""
+    import importlib.machinery
+    import importlib.util
+    import sys
+    if not os.path.exists(REF_OP_PYC):
+        return None
+    previous = sys.modules.get("scatter_ext")
+    sys.modules["scatter_ext"] = scatter_ext_module
+    try:
+        loader = importlib.machinery.SourcelessFileLoader("torchex_reference_scatter_op", REF_OP_PYC)
+        spec = importlib.util.spec_from_loader(loader.name, loader)
+        module = importlib.util.module_from_spec(spec)
+        loader.exec_module(module)
+    finally:
+        if previous is None:
+            sys.modules.pop("scatter_ext", None)
+        else:
+            sys.modules["scatter_ext"] = previous
+    return module
 
 
 def _ptr(a: np.ndarray):

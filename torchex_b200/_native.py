@@ -33,7 +33,11 @@ _SIGNATURES = {
                                      _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
     "texb_unique_fill": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_void_p,
                                     _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
-    "texb_segment_rank": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p]),
+    "texb_segment_rank": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p,
+                                     _c.c_void_p]),
+    "texb_segment_reduce_small_ok": (_c.c_int, [_c.c_int64, _c.c_int, _c.c_int64]),
+    "texb_segment_reduce_small": (_c.c_int, [_c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int,
+                                             _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_int32, _c.c_void_p]),
     "texb_get_pre_sum": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p]),
     "texb_reduce_workspace_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int]),
     "texb_plan_balance": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_int, _c.c_void_p]),
@@ -72,6 +76,7 @@ _SIGNATURES = {
 }
 
 OP_SUM, OP_MEAN, OP_MAX = 0, 1, 2
+PLAN_HAS_EMPTY, PLAN_SETTLED = 1, 2  # bits of the plan_flags argument of the reduce entry points
 BALANCE_PIECES = 131072  # pieces of the plan's balance table (see texb_plan_balance)
 
 

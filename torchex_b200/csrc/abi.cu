@@ -28,7 +28,10 @@ int unique_count_impl(const void*, int, int64_t, int64_t, int, int32_t*, int32_t
                       cudaStream_t);
 int unique_fill_impl(const int32_t*, const int32_t*, int64_t, int64_t, int32_t*, int32_t*, int32_t*, int32_t*,
                      int32_t*, void*, size_t, cudaStream_t);
-int segment_rank_impl(const int32_t*, const int32_t*, const int32_t*, int64_t, int64_t*, cudaStream_t);
+int segment_rank_impl(const int32_t*, const int32_t*, const int32_t*, int64_t, int64_t, int64_t*, cudaStream_t);
+bool segment_small_ok_impl(int64_t, int, int64_t);
+int segment_small_impl(int, const float*, const int32_t*, const int32_t*, int64_t, int, int64_t, float*, int32_t*,
+                       int32_t, cudaStream_t);
 int segment_reduce_static_impl(int, const float*, const int32_t*, const int32_t*, const int32_t*, int,
                                const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, int32_t,
                                cudaStream_t);
@@ -135,7 +138,7 @@ using namespace texb;
 
 extern "C" {
 
-int texb_version(void) { return 100; }
+int texb_version(void) { return 200; }
 
 const char* texb_last_error(void) { return t_error; }
 
@@ -215,26 +218,37 @@ int texb_unique_fill(const int32_t* sorted_keys, const int32_t* perm, int64_t n,
 }
 
 int texb_segment_rank(const int32_t* sid, const int32_t* perm, const int32_t* offsets, int64_t n,
-                      int64_t* rank_out, void* stream) {
-  return segment_rank_impl(sid, perm, offsets, n, rank_out, static_cast<cudaStream_t>(stream));
+                      int64_t num_segments, int64_t* rank_out, void* stream) {
+  return segment_rank_impl(sid, perm, offsets, n, num_segments, rank_out, static_cast<cudaStream_t>(stream));
+}
+
+int texb_segment_reduce_small_ok(int64_t n, int channel, int64_t max_cnt) {
+  return segment_small_ok_impl(n, channel, max_cnt) ? 1 : 0;
+}
+
+int texb_segment_reduce_small(int op, const float* feats, const int32_t* offsets, const int32_t* perm,
+                              int64_t n, int channel, int64_t num_segments, float* out, int32_t* arg,
+                              int32_t arg_base, void* stream) {
+  return segment_small_impl(op, feats, offsets, perm, n, channel, num_segments, out, arg, arg_base,
+                            static_cast<cudaStream_t>(stream));
 }
 
 int texb_segment_reduce(int op, const float* feats, const int32_t* sid, const int32_t* perm,
-                        const int32_t* offsets, int has_empty, const int32_t* balance,
+                        const int32_t* offsets, int plan_flags, const int32_t* balance,
                         int balance_len, int64_t n, int channel, int64_t num_segments, float* out,
                         int32_t* arg, int32_t arg_base, void* workspace, size_t workspace_bytes,
                         void* stream) {
-  return segment_reduce_impl(op, feats, 4, sid, perm, offsets, has_empty, balance, balance_len, n,
+  return segment_reduce_impl(op, feats, 4, sid, perm, offsets, plan_flags, balance, balance_len, n,
                              channel, num_segments, out, arg, arg_base, workspace, workspace_bytes,
                              static_cast<cudaStream_t>(stream));
 }
 
 int texb_segment_reduce_bf16(int op, const void* feats_bf16, const int32_t* sid, const int32_t* perm,
-                             const int32_t* offsets, int has_empty, const int32_t* balance,
+                             const int32_t* offsets, int plan_flags, const int32_t* balance,
                              int balance_len, int64_t n, int channel, int64_t num_segments, float* out,
                              int32_t* arg, int32_t arg_base, void* workspace, size_t workspace_bytes,
                              void* stream) {
-  return segment_reduce_impl(op, feats_bf16, 2, sid, perm, offsets, has_empty, balance, balance_len, n,
+  return segment_reduce_impl(op, feats_bf16, 2, sid, perm, offsets, plan_flags, balance, balance_len, n,
                              channel, num_segments, out, arg, arg_base, workspace, workspace_bytes,
                              static_cast<cudaStream_t>(stream));
 }
@@ -245,13 +259,13 @@ size_t texb_reduce_pair_workspace_bytes(int64_t n, int channel) {
 }
 
 int texb_segment_reduce_pair(int op, const void* feats, int feature_bytes, const int32_t* sid,
-                             const int32_t* perm, const int32_t* offsets, int has_empty,
+                             const int32_t* perm, const int32_t* offsets, int plan_flags,
                              const int32_t* balance, int balance_len, int64_t n, int channel,
                              int64_t num_segments, float* out_sum, float* out_max, int32_t* arg,
                              int32_t arg_base, void* workspace, size_t workspace_bytes, void* stream) {
   if (num_segments > 0 && !out_sum) return fail(TEXB_ERR_INVALID_ARGUMENT, "out_sum is NULL");
   if (num_segments == 0) return TEXB_OK;
-  return segment_reduce_impl(op, feats, feature_bytes, sid, perm, offsets, has_empty, balance, balance_len, n,
+  return segment_reduce_impl(op, feats, feature_bytes, sid, perm, offsets, plan_flags, balance, balance_len, n,
                              channel, num_segments, out_max, arg, arg_base, workspace, workspace_bytes,
                              static_cast<cudaStream_t>(stream), out_sum);
 }
@@ -259,10 +273,10 @@ int texb_segment_reduce_pair(int op, const void* feats, int feature_bytes, const
 size_t texb_static_scratch_bytes(void) { return static_scratch_bytes_impl(); }
 
 int texb_segment_reduce_static(int op, const float* feats, const int32_t* sid, const int32_t* perm,
-                               const int32_t* offsets, int has_empty, const int32_t* balance,
+                               const int32_t* offsets, int plan_flags, const int32_t* balance,
                                int balance_len, int64_t n, int channel, int64_t num_segments,
                                float* out, int32_t* arg, int32_t arg_base, void* stream) {
-  return segment_reduce_static_impl(op, feats, sid, perm, offsets, has_empty, balance, balance_len, n,
+  return segment_reduce_static_impl(op, feats, sid, perm, offsets, plan_flags, balance, balance_len, n,
                                     channel, num_segments, out, arg, arg_base,
                                     static_cast<cudaStream_t>(stream));
 }
@@ -274,11 +288,14 @@ size_t texb_scatter_compat_workspace_bytes(int64_t num_total, int channel) {
 }
 
 static int compat_reduce(int op, const float* feats, const int32_t* pre_sum, float* out,
-                         int32_t* arg, int channel, int num_unq, int64_t num_total, void* workspace,
-                         size_t workspace_bytes, cudaStream_t stream) {
+                         int32_t* arg, int channel, int num_unq, int max_cnt, int64_t num_total,
+                         void* workspace, size_t workspace_bytes, cudaStream_t stream) {
   if (num_total < 0 || num_unq < 0 || channel < 1)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "scatter: bad sizes");
   if (!pre_sum) return fail(TEXB_ERR_INVALID_ARGUMENT, "scatter: preSum is NULL");
+  // a small input of short segments: one launch straight from preSum, no workspace
+  if (max_cnt > 0 && segment_small_ok_impl(num_total, channel, max_cnt))
+    return segment_small_impl(op, feats, pre_sum, nullptr, num_total, channel, num_unq, out, arg, 0, stream);
   if (num_total >= (int64_t(1) << 31) - 65536)
     return fail(TEXB_ERR_UNSUPPORTED, "scatter: num_total must be below 2^31 - 65536");
   const size_t sid_bytes = align_up(size_t(num_total) * sizeof(int32_t), 256);
@@ -291,7 +308,7 @@ static int compat_reduce(int op, const float* feats, const int32_t* pre_sum, flo
   int st = expand_offsets_impl(pre_sum, sid, num_total, num_unq, stream);
   if (st != TEXB_OK) return st;
   // The reference kernels write every row, including those of empty ranges.
-  return segment_reduce_impl(op, feats, 4, sid, nullptr, pre_sum, /*has_empty=*/1, nullptr, 0, num_total, channel,
+  return segment_reduce_impl(op, feats, 4, sid, nullptr, pre_sum, TEXB_PLAN_HAS_EMPTY, nullptr, 0, num_total, channel,
                              num_unq, out, arg, /*arg_base=*/0, reinterpret_cast<void*>(base + sid_bytes),
                              workspace_bytes - pad - sid_bytes, stream);
 }
@@ -299,16 +316,14 @@ static int compat_reduce(int op, const float* feats, const int32_t* pre_sum, flo
 int texb_scatter_sum(const float* feats, const int32_t* pre_sum, float* out, int channel,
                      int num_unq, int max_cnt, int64_t num_total, void* workspace,
                      size_t workspace_bytes, void* stream) {
-  (void)max_cnt;
-  return compat_reduce(TEXB_OP_SUM, feats, pre_sum, out, nullptr, channel, num_unq, num_total,
+  return compat_reduce(TEXB_OP_SUM, feats, pre_sum, out, nullptr, channel, num_unq, max_cnt, num_total,
                        workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int texb_scatter_max(const float* feats, const int32_t* pre_sum, float* out, int32_t* arg,
                      int channel, int num_unq, int max_cnt, int64_t num_total, void* workspace,
                      size_t workspace_bytes, void* stream) {
-  (void)max_cnt;
-  return compat_reduce(TEXB_OP_MAX, feats, pre_sum, out, arg, channel, num_unq, num_total,
+  return compat_reduce(TEXB_OP_MAX, feats, pre_sum, out, arg, channel, num_unq, max_cnt, num_total,
                        workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 

@@ -691,24 +691,45 @@ int plan_balance_impl(const int32_t* sid, int64_t n, int32_t* table, int table_l
   return check_launch("balance_table_kernel");
 }
 
+// Plan entries found outside their range by segment_rank_kernel (a segment id outside
+// [0, num_segments), a perm entry outside [0, n)): the entry is skipped and counted
+// (sticky; part of texb_device_status) instead of being used as an address.
+__device__ int g_plan_bad_indices = 0;
+
 // rank[row of position p] = p - offsets[sid[p]]: the index of every point inside
 // its segment, in increasing row order (the plan's sort is stable).
 __global__ void segment_rank_kernel(const int32_t* __restrict__ sid, const int32_t* __restrict__ perm,
-                                    const int32_t* __restrict__ offsets, int n, int64_t* __restrict__ rank) {
+                                    const int32_t* __restrict__ offsets, int n, int m,
+                                    int64_t* __restrict__ rank) {
   const int p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= n) return;
   const int row = perm ? perm[p] : p;
-  if (row >= 0 && row < n) rank[row] = int64_t(p - offsets[sid[p]]);
+  const int s = sid[p];
+  if (unsigned(row) >= unsigned(n) || unsigned(s) >= unsigned(m)) {
+    atomicAdd(&g_plan_bad_indices, 1);
+    return;
+  }
+  rank[row] = int64_t(p - offsets[s]);
 }
 
 int segment_rank_impl(const int32_t* sid, const int32_t* perm, const int32_t* offsets, int64_t n,
-                      int64_t* rank_out, cudaStream_t stream) {
-  if (n < 0 || (n > 0 && (!sid || !offsets || !rank_out)))
+                      int64_t num_segments, int64_t* rank_out, cudaStream_t stream) {
+  if (n < 0 || num_segments < 0 || (n > 0 && (!sid || !offsets || !rank_out)))
     return fail(TEXB_ERR_INVALID_ARGUMENT, "segment_rank: bad pointer or size");
-  if (n > INT_MAX - 65536) return fail(TEXB_ERR_UNSUPPORTED, "segment_rank: n must be below 2^31 - 65536");
+  if (n > INT_MAX - 65536 || num_segments > INT_MAX - 65536)
+    return fail(TEXB_ERR_UNSUPPORTED, "segment_rank: n and num_segments must be below 2^31 - 65536");
   if (n == 0) return TEXB_OK;
-  segment_rank_kernel<<<unsigned(ceil_div(n, 256)), 256, 0, stream>>>(sid, perm, offsets, int(n), rank_out);
+  segment_rank_kernel<<<unsigned(ceil_div(n, 256)), 256, 0, stream>>>(sid, perm, offsets, int(n),
+                                                                      int(num_segments), rank_out);
   return check_launch("segment_rank_kernel");
+}
+
+int plan_bad_indices_impl(int* count) {
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_plan_bad_indices, sizeof(int));
+  if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "cudaMemcpyFromSymbol: %s", cudaGetErrorString(e));
+  *count = v;
+  return TEXB_OK;
 }
 
 int get_pre_sum_impl(const int32_t* unq_inv, int32_t* pre_sum, int64_t num_total, int64_t num_unq,

@@ -64,230 +64,14 @@
 #define TEXB_PACKED_F32X2 1
 #endif
 
+#include "reduce_ops.cuh"
+
 namespace texb {
 namespace {
 
 constexpr unsigned kValid = 1u;
 constexpr unsigned kOpenLeft = 2u;   // segment began before this range
 constexpr unsigned kOpenRight = 4u;  // segment continues after this range
-
-// ---- operators --------------------------------------------------------------
-// State<VEC> lives in registers; pack / unpack move it through two arrays of
-// VEC 32-bit words (shared memory or the workspace).
-
-struct OpSumComp {  // fp32 sum + error-free two-sum: (s, c) with s + c the exact running sum
-  static constexpr bool kIsMax = false;
-  static constexpr bool kHasSum = true;
-  static constexpr int kPlanes = 2;
-  template <int VEC> struct State { float s[VEC]; float c[VEC]; };
-  template <int VEC>
-  static __device__ __forceinline__ void init(State<VEC>& x) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) { x.s[k] = 0.f; x.c[k] = 0.f; }
-  }
-  // Knuth's TwoSum: t + e == s + v exactly, whatever the magnitudes.
-  static __device__ __forceinline__ void two_sum(float s, float v, float& t, float& e) {
-    t = s + v;
-    const float bp = t - s;
-    e = (s - (t - bp)) + (v - bp);
-  }
-  // The same TwoSum on two channels at once with the packed fp32x2 instructions of
-  // sm_100 (each half rounds exactly like the scalar instruction, so the result is
-  // bit-identical); a - b is written fma(b, -1, a), which rounds a - b once.
-  static __device__ __forceinline__ void two_sum2(float2 s, float2 v, float2& t, float2& e) {
-    const float2 m1 = make_float2(-1.f, -1.f);
-    t = __fadd2_rn(s, v);
-    const float2 bp = __ffma2_rn(s, m1, t);                 // t - s
-    const float2 a = __ffma2_rn(__ffma2_rn(bp, m1, t), m1, s);  // s - (t - bp)
-    e = __fadd2_rn(a, __ffma2_rn(bp, m1, v));               // + (v - bp)
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void add(State<VEC>& x, const float (&v)[VEC], int) {
-#if TEXB_PACKED_F32X2
-    if constexpr (VEC % 2 == 0) {
-#pragma unroll
-      for (int k = 0; k < VEC; k += 2) {
-        float2 t, e;
-        two_sum2(make_float2(x.s[k], x.s[k + 1]), make_float2(v[k], v[k + 1]), t, e);
-        const float2 c = __fadd2_rn(make_float2(x.c[k], x.c[k + 1]), e);
-        x.s[k] = t.x; x.s[k + 1] = t.y;
-        x.c[k] = c.x; x.c[k + 1] = c.y;
-      }
-      return;
-    }
-#endif
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-      float t, e;
-      two_sum(x.s[k], v[k], t, e);
-      x.c[k] += e;
-      x.s[k] = t;
-    }
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void merge(State<VEC>& x, const State<VEC>& y) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-      float t, e;
-      two_sum(x.s[k], y.s[k], t, e);
-      x.c[k] = (x.c[k] + y.c[k]) + e;
-      x.s[k] = t;
-    }
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void pack(const State<VEC>& x, uint32_t (&w)[kPlanes][VEC]) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) { w[0][k] = __float_as_uint(x.s[k]); w[1][k] = __float_as_uint(x.c[k]); }
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void unpack(State<VEC>& x, const uint32_t (&w)[kPlanes][VEC]) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) { x.s[k] = __uint_as_float(w[0][k]); x.c[k] = __uint_as_float(w[1][k]); }
-  }
-  // An infinite running sum (infinite input or fp32 overflow) makes the error
-  // term NaN; the sum itself is then the answer, as for a plain fp32 sum.
-  template <int VEC>
-  static __device__ __forceinline__ float value(const State<VEC>& x, int k) {
-    return (fabsf(x.s[k]) == INFINITY) ? x.s[k] : x.s[k] + x.c[k];
-  }
-  template <int VEC>
-  static __device__ __forceinline__ float sum_value(const State<VEC>& x, int k) { return value<VEC>(x, k); }
-  template <int VEC>
-  static __device__ __forceinline__ int index(const State<VEC>&, int) { return 0; }
-};
-
-struct OpSumPlain {  // plain fp32 running sum (the "compensated" knob set to 0)
-  static constexpr bool kIsMax = false;
-  static constexpr bool kHasSum = true;
-  static constexpr int kPlanes = 2;
-  template <int VEC> struct State { float s[VEC]; };
-  template <int VEC>
-  static __device__ __forceinline__ void init(State<VEC>& x) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) x.s[k] = 0.f;
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void add(State<VEC>& x, const float (&v)[VEC], int) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) x.s[k] += v[k];
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void merge(State<VEC>& x, const State<VEC>& y) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) x.s[k] += y.s[k];
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void pack(const State<VEC>& x, uint32_t (&w)[kPlanes][VEC]) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) { w[0][k] = __float_as_uint(x.s[k]); w[1][k] = 0u; }
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void unpack(State<VEC>& x, const uint32_t (&w)[kPlanes][VEC]) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) x.s[k] = __uint_as_float(w[0][k]);
-  }
-  template <int VEC>
-  static __device__ __forceinline__ float value(const State<VEC>& x, int k) { return x.s[k]; }
-  template <int VEC>
-  static __device__ __forceinline__ float sum_value(const State<VEC>& x, int k) { return x.s[k]; }
-  template <int VEC>
-  static __device__ __forceinline__ int index(const State<VEC>&, int) { return 0; }
-};
-
-// Maximum + row.  Rows reach `add` and pieces reach `merge` in increasing row
-// order within a segment (the plan's permutation is stable), so a strict ">"
-// keeps the lowest row on ties.  The running value starts at -inf so that a row
-// equal to -FLT_MAX still records its index, like the reference's ">=" against
-// its -FLT_MAX start (scatter_kernel.cu:139-151); a channel no row claimed
-// reports -FLT_MAX / -1, the reference's untouched state.  NaN and -inf never win.
-struct OpMax {
-  static constexpr bool kIsMax = true;
-  static constexpr bool kHasSum = false;
-  static constexpr int kPlanes = 2;
-  template <int VEC> struct State { float v[VEC]; int i[VEC]; };
-  template <int VEC>
-  static __device__ __forceinline__ void init(State<VEC>& x) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) { x.v[k] = -INFINITY; x.i[k] = -1; }
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void add(State<VEC>& x, const float (&v)[VEC], int row) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k)
-      if (v[k] > x.v[k]) { x.v[k] = v[k]; x.i[k] = row; }
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void merge(State<VEC>& x, const State<VEC>& y) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k)
-      if (y.v[k] > x.v[k]) { x.v[k] = y.v[k]; x.i[k] = y.i[k]; }
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void pack(const State<VEC>& x, uint32_t (&w)[kPlanes][VEC]) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) { w[0][k] = __float_as_uint(x.v[k]); w[1][k] = uint32_t(x.i[k]); }
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void unpack(State<VEC>& x, const uint32_t (&w)[kPlanes][VEC]) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) { x.v[k] = __uint_as_float(w[0][k]); x.i[k] = int(w[1][k]); }
-  }
-  template <int VEC>
-  static __device__ __forceinline__ float value(const State<VEC>& x, int k) {
-    return x.i[k] < 0 ? -FLT_MAX : x.v[k];
-  }
-  template <int VEC>
-  static __device__ __forceinline__ int index(const State<VEC>& x, int k) { return x.i[k]; }
-};
-
-// Sum (compensated) and maximum + row of the same rows in one pass: the state is
-// the two states side by side, and every step is the two operators' step.
-struct OpSumMax {
-  static constexpr bool kIsMax = true;
-  static constexpr bool kHasSum = true;
-  static constexpr int kPlanes = 4;
-  template <int VEC> struct State {
-    OpSumComp::State<VEC> sum;
-    OpMax::State<VEC> max;
-  };
-  template <int VEC>
-  static __device__ __forceinline__ void init(State<VEC>& x) {
-    OpSumComp::init<VEC>(x.sum);
-    OpMax::init<VEC>(x.max);
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void add(State<VEC>& x, const float (&v)[VEC], int row) {
-    OpSumComp::add<VEC>(x.sum, v, row);
-    OpMax::add<VEC>(x.max, v, row);
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void merge(State<VEC>& x, const State<VEC>& y) {
-    OpSumComp::merge<VEC>(x.sum, y.sum);
-    OpMax::merge<VEC>(x.max, y.max);
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void pack(const State<VEC>& x, uint32_t (&w)[kPlanes][VEC]) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-      w[0][k] = __float_as_uint(x.sum.s[k]); w[1][k] = __float_as_uint(x.sum.c[k]);
-      w[2][k] = __float_as_uint(x.max.v[k]); w[3][k] = uint32_t(x.max.i[k]);
-    }
-  }
-  template <int VEC>
-  static __device__ __forceinline__ void unpack(State<VEC>& x, const uint32_t (&w)[kPlanes][VEC]) {
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-      x.sum.s[k] = __uint_as_float(w[0][k]); x.sum.c[k] = __uint_as_float(w[1][k]);
-      x.max.v[k] = __uint_as_float(w[2][k]); x.max.i[k] = int(w[3][k]);
-    }
-  }
-  template <int VEC>
-  static __device__ __forceinline__ float value(const State<VEC>& x, int k) { return OpMax::value<VEC>(x.max, k); }
-  template <int VEC>
-  static __device__ __forceinline__ int index(const State<VEC>& x, int k) { return x.max.i[k]; }
-  template <int VEC>
-  static __device__ __forceinline__ float sum_value(const State<VEC>& x, int k) { return OpSumComp::value<VEC>(x.sum, k); }
-};
 
 // ---- small device helpers -----------------------------------------------------
 
@@ -561,6 +345,7 @@ struct Split {
   const int32_t* balance;  // NULL: even split
   int balance_k;
   int stream_hint;         // 1: feature rows are copied with an L2 evict-first policy
+  int plan_settled;        // 1: the plan arrays may be read before the stream's earlier work is visible
   int rows_per_cta, rows_per_group, num_ctas;
 };
 
@@ -861,12 +646,18 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
 
   // This grid may be a programmatic dependent launch of whatever kernel precedes it in
   // the stream (typically the fix-up of the previous reduction): its CTAs are then
-  // placed while that kernel drains.  Everything up to wait_for_stream() below reads
-  // only the plan (sid, perm, balance) -- arrays that were complete before that kernel
-  // began, since the plan kernels never release their dependents early -- and
-  // writes only this CTA's shared memory; the features are read and global memory is
-  // written after it.  A no-op for a plain launch.
-  auto wait_for_stream = [] {
+  // placed while that kernel drains, and memory written by earlier work of the stream
+  // is only guaranteed to be visible after griddepcontrol.wait.  By default the wait
+  // therefore comes first, before anything is read.  When the caller states that the
+  // plan is settled (its arrays were complete and the host had synchronised with the
+  // stream before this launch), the prologue that reads only the plan (sid, perm,
+  // balance) and writes only this CTA's shared memory runs ahead of the wait, under
+  // the tail of the previous kernel; the features are read and global memory is
+  // written after it either way.  A no-op for a plain launch.
+  bool waited = false;
+  auto wait_for_stream = [&waited] {
+    if (waited) return;
+    waited = true;
 #if __CUDA_ARCH__ >= 900
     asm volatile("griddepcontrol.wait;" ::: "memory");
     // Let the dependent fix-up grid be scheduled now (it parks at its own wait until
@@ -874,6 +665,7 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #endif
   };
+  if (!sp.plan_settled) wait_for_stream();
   const unsigned t_start = global_timer_lo();
   const int lane_g = threadIdx.x & (LPR - 1);
   const int group = threadIdx.x / LPR;
@@ -1334,6 +1126,7 @@ Split make_split(int64_t n, const Layout& g, int ctas_per_sm) {
   s.balance = nullptr;
   s.balance_k = 0;
   s.stream_hint = tuning().l2_stream_hint;
+  s.plan_settled = 0;
   int64_t rows = tuning().rows_per_cta;
   if (rows <= 0) {
     const int64_t resident = int64_t(sm_count()) * ctas_per_sm;
@@ -1392,6 +1185,7 @@ struct Call {
   int balance_k;
   int arg_base;
   int m;
+  bool plan_settled;
 };
 
 // Resident CTAs per SM of one kernel instantiation (asked once per process).
@@ -1413,6 +1207,7 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
     s.balance = c.balance;
     s.balance_k = c.balance_k;
   }
+  s.plan_settled = c.plan_settled ? 1 : 0;
   const size_t vec_bytes = records_vec_bytes(g, s.num_ctas, Op::kPlanes);
   const size_t need = vec_bytes + records_meta_bytes(g, s.num_ctas);
   const uintptr_t base = align_up(reinterpret_cast<uintptr_t>(c.workspace), 256);
@@ -1549,11 +1344,13 @@ int dispatch_layout(const Layout& g, const Call& c) {
 // `out_sum` selects the two-output form: op (sum or mean) goes to out_sum, the
 // maxima and their rows to out / arg, from one pass over the features.
 int segment_reduce_impl(int op, const void* feats, int in_bytes, const int32_t* sid, const int32_t* perm,
-                        const int32_t* offsets, int has_empty, const int32_t* balance,
+                        const int32_t* offsets, int plan_flags, const int32_t* balance,
                         int balance_len, int64_t n, int C, int64_t m, float* out, int32_t* arg,
                         int32_t arg_base, void* workspace, size_t workspace_bytes, cudaStream_t stream,
                         float* out_sum) {
   const bool pair = out_sum != nullptr;
+  const bool has_empty = (plan_flags & TEXB_PLAN_HAS_EMPTY) != 0;
+  const bool plan_settled = (plan_flags & TEXB_PLAN_SETTLED) != 0;
   if (in_bytes != 4 && in_bytes != 2)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "features must be fp32 (4 bytes) or bf16 (2 bytes)");
   if (op != TEXB_OP_SUM && op != TEXB_OP_MEAN && op != TEXB_OP_MAX)
@@ -1592,7 +1389,7 @@ int segment_reduce_impl(int op, const void* feats, int in_bytes, const int32_t* 
   if (balance && balance_len < 2)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "balance table needs at least 2 entries");
   Call c = {feats, sid, perm, out, out_sum, arg, workspace, workspace_bytes, int(n), C, op == TEXB_OP_MEAN, stream,
-            balance, balance ? balance_len - 1 : 0, int(arg_base), int(m)};
+            balance, balance ? balance_len - 1 : 0, int(arg_base), int(m), plan_settled};
   if (pair) return dispatch_layout<OpSumMax>(g, c);
   if (op == TEXB_OP_MAX) return dispatch_layout<OpMax>(g, c);
   if (tuning().compensated) return dispatch_layout<OpSumComp>(g, c);
@@ -1623,13 +1420,19 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 size_t static_scratch_bytes_impl() { return kStaticScratchBytes; }
 
 int segment_reduce_static_impl(int op, const float* feats, const int32_t* sid, const int32_t* perm,
-                               const int32_t* offsets, int has_empty, const int32_t* balance,
+                               const int32_t* offsets, int plan_flags, const int32_t* balance,
                                int balance_len, int64_t n, int C, int64_t m, float* out, int32_t* arg,
                                int32_t arg_base, cudaStream_t stream) {
   constexpr int kMaxDevices = 64;
   static std::mutex mu;
   static void* device_ptr[kMaxDevices] = {};
-  if (n < 0 || C < 1) return fail(TEXB_ERR_INVALID_ARGUMENT, "bad sizes n=%lld channel=%d", (long long)n, C);
+  // Sizes are validated before the scratch requirement is computed from them, so that a
+  // nonsensical size is reported as such and not as "scratch too small".
+  if (n < 0 || m < 0 || C < 1)
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "bad sizes n=%lld channel=%d num_segments=%lld", (long long)n, C,
+                (long long)m);
+  if (n >= (int64_t(1) << 31) - 65536 || m >= (int64_t(1) << 31) - 65536)
+    return fail(TEXB_ERR_UNSUPPORTED, "n and num_segments must be below 2^31 - 65536");
   const size_t need = reduce_workspace_bytes(n, C);
   if (need > kStaticScratchBytes)
     return fail(TEXB_ERR_UNSUPPORTED,
@@ -1645,7 +1448,9 @@ int segment_reduce_static_impl(int op, const float* feats, const int32_t* sid, c
     std::lock_guard<std::mutex> lock(mu);
     if (!device_ptr[dev]) {
       // In host code the array's name is only a handle: ask the runtime for the
-      // address the array has on the current device, once per device.
+      // address the array has on the current device, once per device.  The address
+      // is kept for the life of the process: a caller that destroys the device's
+      // context (cudaDeviceReset) must not use this entry point afterwards.
       void* p = nullptr;
       e = cudaGetSymbolAddress(&p, g_static_scratch);
       if (e != cudaSuccess || !p)
@@ -1654,17 +1459,23 @@ int segment_reduce_static_impl(int op, const float* feats, const int32_t* sid, c
     }
     scratch = device_ptr[dev];
   }
-  return segment_reduce_impl(op, feats, 4, sid, perm, offsets, has_empty, balance, balance_len, n, C, m, out,
+  return segment_reduce_impl(op, feats, 4, sid, perm, offsets, plan_flags, balance, balance_len, n, C, m, out,
                              arg, arg_base, scratch, kStaticScratchBytes, stream, nullptr);
 }
 
+int small_bad_indices_impl(int* count);  // segment_small.cu
+int plan_bad_indices_impl(int* count);   // segment_plan.cu
+
 int device_status_impl(int* wait_timeouts, int* bad_indices) {
-  int v = 0, w = 0;
+  int v = 0, w = 0, w_small = 0, w_plan = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, g_wait_timeouts, sizeof(int));
   if (e == cudaSuccess) e = cudaMemcpyFromSymbol(&w, g_bad_indices, sizeof(int));
   if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "cudaMemcpyFromSymbol: %s", cudaGetErrorString(e));
+  int st = small_bad_indices_impl(&w_small);
+  if (st == TEXB_OK) st = plan_bad_indices_impl(&w_plan);
+  if (st != TEXB_OK) return st;
   if (wait_timeouts) *wait_timeouts = v;
-  if (bad_indices) *bad_indices = w;
+  if (bad_indices) *bad_indices = w + w_small + w_plan;
   return TEXB_OK;
 }
 

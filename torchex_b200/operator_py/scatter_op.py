@@ -23,6 +23,7 @@ import torch
 from torch.autograd import Function
 
 from .. import _native
+from .. import scatter_ext as _ext
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
@@ -60,16 +61,6 @@ def _scratch(nbytes: int, device) -> torch.Tensor:
     return torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=device)
 
 
-def _as_feats(feats: torch.Tensor) -> torch.Tensor:
-    if not feats.is_cuda:
-        raise RuntimeError("feats must be a CUDAtensor")
-    if feats.dtype not in (torch.float32, torch.bfloat16):
-        raise RuntimeError(f"feats must be float32 (or bfloat16), got {feats.dtype}")
-    if feats.ndim != 2:
-        raise RuntimeError(f"feats must be [num_total, channel], got {tuple(feats.shape)}")
-    return feats.contiguous()
-
-
 class ScatterData:
     """Segment plan shared by every reduction over the same ``unq_inv``.
 
@@ -83,7 +74,12 @@ class ScatterData:
 
     ``num_unq`` is ``len(unq_cnts)``; the reference derives it from the last id
     with a device-to-host copy (scatter_op.py:125-126).  Construction
-    synchronises with the device twice (id statistics, plan statistics).
+    synchronises with the device once (sortedness and range of the ids; the
+    reference synchronises three times, scatter_op.py:19-20, 125).  The plan's
+    statistics (``max_cnt``, whether a segment is empty) travel to pinned host
+    memory asynchronously: reading ``max_cnt`` or ``has_empty`` before they have
+    arrived waits for them, and the operators simply treat the plan
+    conservatively until then.
     """
 
     _unq_inv = None
@@ -104,7 +100,9 @@ class ScatterData:
 
     _unq_cnts = None
     _max_cnt = None
-    _plan_stats = None
+    _has_empty = None
+    _pending = None      # (pinned host copy of the plan statistics, event recorded after the copy)
+    _plan = None         # scatter_ext.Plan: the device arrays and what the host knows about them
 
     @property
     def unq_cnts(self) -> torch.Tensor:
@@ -118,17 +116,52 @@ class ScatterData:
     def unq_cnts(self, value: torch.Tensor) -> None:
         self._unq_cnts = value
 
+    def _poll(self, wait: bool = False) -> None:
+        """Takes over the plan statistics once their copy to the host has finished
+        (``wait``: block until it has).  From then on the host also knows that the plan
+        arrays are complete, which lets the reduce kernels read them early."""
+        if self._pending is None:
+            return
+        host, done = self._pending
+        if wait:
+            done.synchronize()
+        elif not done.query():
+            return
+        max_cnt, num_empty, _bad, _ = host.tolist()
+        self._pending = None
+        self._max_cnt = max_cnt
+        if self._has_empty is None:
+            self._has_empty = num_empty > 0
+        plan = self._plan
+        plan.max_cnt = max_cnt
+        plan.has_empty = bool(self._has_empty)
+        plan.settled = True
+
+    def _watch_stats(self, plan_stats: torch.Tensor) -> None:
+        host = torch.empty(4, dtype=torch.int32, pin_memory=True)
+        host.copy_(plan_stats, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        self._pending = (host, done)
+
     @property
     def max_cnt(self) -> int:
-        """Rows of the largest segment (scatter_op.py:19 of the reference; nothing here
-        depends on it).  A plan built from keys copies it from the device when first read."""
+        """Rows of the largest segment (scatter_op.py:19 of the reference; here it only
+        selects the kernel path for small inputs)."""
         if self._max_cnt is None:
-            self._max_cnt = self._plan_stats.tolist()[0]
+            self._poll(wait=True)
         return self._max_cnt
 
     @max_cnt.setter
     def max_cnt(self, value: int) -> None:
         self._max_cnt = int(value)
+
+    @property
+    def has_empty(self) -> bool:
+        """True when some segment has no rows (ids that skip a value)."""
+        if self._has_empty is None:
+            self._poll(wait=True)
+        return self._has_empty
 
     @property
     def num_total(self) -> int:
@@ -140,15 +173,18 @@ class ScatterData:
             f"unq_inv in ScatterData should be 1 or 2-dims, but got {unq_inv.ndim}-dims"
         assert unq_cnts.ndim in (1, 2), \
             f"unq_cnts in ScatterData should be 1 or 2-dims, but got {unq_cnts.ndim}-dims"
+        self.unq_cnts = unq_cnts.unsqueeze(-1) if unq_cnts.ndim == 1 else unq_cnts
+        self._build(unq_inv, int(self.unq_cnts.shape[0]))
+
+    def _build(self, unq_inv: torch.Tensor, m) -> None:
+        """Builds the plan for ``unq_inv`` with ``m`` segments (``None``: the largest id + 1)."""
         if not unq_inv.is_cuda:
             raise RuntimeError("unq_inv must be a CUDAtensor")
         ids = unq_inv.reshape(-1)
         if ids.dtype not in (torch.int32, torch.int64):
             ids = ids.long()
         ids = ids.contiguous()
-        self.unq_cnts = unq_cnts.unsqueeze(-1) if unq_cnts.ndim == 1 else unq_cnts
         n = ids.numel()
-        m = int(self.unq_cnts.shape[0])
         dev = ids.device
         lib = _native.lib()
         id_bytes = ids.element_size()
@@ -157,11 +193,16 @@ class ScatterData:
             stats = torch.empty(4, dtype=torch.int32, device=dev)
             _native.check(lib.texb_ids_inspect(ids.data_ptr(), id_bytes, n, stats.data_ptr(), _stream()),
                           "texb_ids_inspect")
-            is_sorted, id_min, id_max, _runs = stats.tolist()
+            is_sorted, id_min, id_max, runs = stats.tolist()  # the one synchronisation
+            if m is None:
+                m = id_max + 1 if n > 0 else 0
             if n > 0 and (id_min < 0 or id_max >= m):
                 raise ValueError(f"unq_inv holds ids in [{id_min}, {id_max}] but unq_cnts "
                                  f"describes {m} segments")
             self.is_sorted = bool(is_sorted)
+            # sorted ids: as many runs as segments means no segment is empty; unsorted ids:
+            # known once the plan statistics have reached the host
+            self._has_empty = (runs != m) if self.is_sorted else None
             self.preSum = torch.empty(m + 1, dtype=torch.int32, device=dev)
             plan_stats = torch.empty(4, dtype=torch.int32, device=dev)
             if self.is_sorted:
@@ -187,14 +228,11 @@ class ScatterData:
                 self.unq_inv = self.sid
             else:
                 self._ids64 = ids  # narrowed to int32 when ``unq_inv`` is first read
-            max_cnt, num_empty, bad_ids, _ = plan_stats.tolist()
-        if bad_ids:
-            raise ValueError(f"{bad_ids} ids of unq_inv lie outside [0, {m})")
-        self.max_cnt = max_cnt
-        self.has_empty = num_empty > 0
+            self._watch_stats(plan_stats)
         self.num_unq = m
         self._perm_ptr = None if self.perm is None else self.perm.data_ptr()
-        self._workspaces = {}
+        self._plan = _ext.make_plan(self.sid, self.perm, self.preSum, self.balance, m,
+                                    True if self._has_empty is None else self._has_empty, -1, False)
 
 
 def _plan_from_keys(cls, keys: torch.Tensor):
@@ -237,11 +275,11 @@ def _plan_from_keys(cls, keys: torch.Tensor):
         self.balance = torch.empty(_native.BALANCE_PIECES + 1, dtype=torch.int32, device=dev)
         _native.check(lib.texb_plan_balance(self.sid.data_ptr(), n, self.balance.data_ptr(),
                                             self.balance.numel(), _stream()), "texb_plan_balance")
-        self._plan_stats = plan_stats  # max_cnt is read from the device when first asked for
-    self.has_empty = False
+        self._has_empty = False  # dense ids: every segment has rows
+        self._watch_stats(plan_stats)  # max_cnt reaches the host asynchronously
     self.num_unq = m
     self._perm_ptr = None if self.perm is None else self.perm.data_ptr()
-    self._workspaces = {}
+    self._plan = _ext.make_plan(self.sid, self.perm, self.preSum, self.balance, m, False, -1, False)
     return self
 
 
@@ -269,9 +307,10 @@ def _from_coords(cls, coors: torch.Tensor, grid_size=None):
         if coors.shape[0] == 0:
             grid_size = [1] * d
         else:
-            if int(c64.min()) < 0:
+            lo_hi = torch.cat([c64.min(0).values, c64.max(0).values]).tolist()  # one copy to the host
+            if min(lo_hi[:d]) < 0:
                 raise ValueError("coors must be non-negative")
-            grid_size = [int(v) + 1 for v in c64.max(0).values.cpu()]
+            grid_size = [int(v) + 1 for v in lo_hi[d:]]
     if len(grid_size) != d:
         raise ValueError("grid_size needs one extent per coordinate column")
     total = 1
@@ -316,26 +355,24 @@ ScatterData.from_coords = classmethod(_from_coords)
 def ingroup_rank(data: ScatterData) -> torch.Tensor:
     """Index of every point inside its segment (int64 [num_total]), in increasing
     row order, from an existing plan."""
-    n = data.num_total
-    out = torch.empty(n, dtype=torch.int64, device=data.sid.device)
-    with _on_device(out.device):
-        _native.check(_native.lib().texb_segment_rank(data.sid.data_ptr(), data._perm_ptr, data.preSum.data_ptr(),
-                                                      n, out.data_ptr(), _stream()), "texb_segment_rank")
-    return out
+    return _ext.segment_rank(data._plan)
 
 
-def ingroup_inds(group_inds: torch.Tensor) -> torch.Tensor:
+def ingroup_inds(group_inds: torch.Tensor, num_groups=None) -> torch.Tensor:
     """Same call as TorchEx's ``ingroup_inds`` (torchex/operator_py/ingroup_inds_op.py:10-29):
     for ids ``group_inds`` [N] returns each element's index inside its group.  The
     reference numbers the members in the arrival order of an atomic counter; here
-    they are numbered in increasing position, so the result is reproducible."""
+    they are numbered in increasing position, so the result is reproducible.
+    ``num_groups`` (optional) is an upper bound of the ids + 1; without it the largest
+    id comes from the plan's own inspection pass, so either way the call synchronises
+    with the device once (the reference: once, ingroup_inds_op.py:16)."""
     if not group_inds.is_cuda:
         raise RuntimeError("group_inds must be a CUDAtensor")
     flat = group_inds.reshape(-1)
     if flat.numel() == 0:
         return torch.empty_like(group_inds, dtype=torch.int64)
-    num_groups = int(flat.max()) + 1
-    data = ScatterData(flat, torch.empty(num_groups, dtype=torch.int64, device=flat.device))
+    data = ScatterData.__new__(ScatterData)
+    data._build(flat, None if num_groups is None else int(num_groups))
     return ingroup_rank(data).reshape(group_inds.shape)
 
 
@@ -349,108 +386,27 @@ def gather_back(values: torch.Tensor, data: ScatterData) -> torch.Tensor:
 
 
 def _reduce(op: int, feats: torch.Tensor, data: ScatterData, want_arg: bool, arg_base: int = 0):
-    feats = _as_feats(feats)
-    n, c = feats.shape
-    if feats.dtype == torch.bfloat16 and (c % 8 != 0 or c < 128 or feats.data_ptr() % 16 != 0):
-        feats = feats.float()  # the bf16 kernel covers wide, aligned rows; others are widened first
-    if n != data.num_total:
-        raise RuntimeError(f"feats has {n} rows but ScatterData was built for {data.num_total}")
-    dev = feats.device
-    if dev != data.sid.device:
-        raise RuntimeError("feats and ScatterData live on different devices")
-    if c < 1:
-        raise RuntimeError("feats needs at least one channel")
-    lib = _native.lib()
-    m = data.num_unq
-    out = torch.empty((m, c), dtype=torch.float32, device=dev)
-    arg = torch.empty((m, c), dtype=torch.int32, device=dev) if want_arg else None
-    switch = torch.cuda.current_device() != dev.index
-    if switch:
-        prev = torch.cuda.current_device()
-        torch.cuda.set_device(dev)
-    try:
-        stream = _stream()
-        # The workspace is kept with the plan, one per (channel count, stream): calls on
-        # one stream are ordered, calls on different streams get different scratch.
-        key = (c, stream)
-        ws = data._workspaces.get(key)
-        if ws is None or ws.numel() < lib.texb_reduce_workspace_bytes(n, c):
-            ws = _scratch(lib.texb_reduce_workspace_bytes(n, c), dev)
-            data._workspaces[key] = ws
-        entry = lib.texb_segment_reduce_bf16 if feats.dtype == torch.bfloat16 else lib.texb_segment_reduce
-        _native.check(
-            entry(op, feats.data_ptr(), data.sid.data_ptr(), data._perm_ptr,
-                  data.preSum.data_ptr(), int(data.has_empty or n == 0),
-                  data.balance.data_ptr(), data.balance.numel(), n, c, m,
-                  out.data_ptr(), None if arg is None else arg.data_ptr(), int(arg_base),
-                  ws.data_ptr(), ws.numel(), stream),
-            "texb_segment_reduce")
-    finally:
-        if switch:
-            torch.cuda.set_device(prev)
-    return out, arg
+    """One trip into the compiled module: it checks ``feats``, allocates the outputs,
+    picks the kernel path and launches on the current stream of ``feats``' device."""
+    if data._pending is not None:
+        data._poll()
+    return _ext.reduce(data._plan, op, feats, arg_base)
 
 
 def _reduce_pair(op: int, feats: torch.Tensor, data: ScatterData, arg_base: int = 0):
     """(sum or mean, max, arg) of the same rows from one pass over ``feats``."""
-    feats = _as_feats(feats)
-    n, c = feats.shape
-    if feats.dtype == torch.bfloat16 and (c % 8 != 0 or c != 128 or feats.data_ptr() % 16 != 0):
-        feats = feats.float()  # the two-output bf16 kernel covers aligned 128-channel rows
-    if n != data.num_total:
-        raise RuntimeError(f"feats has {n} rows but ScatterData was built for {data.num_total}")
-    dev = feats.device
-    if dev != data.sid.device:
-        raise RuntimeError("feats and ScatterData live on different devices")
-    if c < 1:
-        raise RuntimeError("feats needs at least one channel")
-    lib = _native.lib()
-    m = data.num_unq
-    out_sum = torch.empty((m, c), dtype=torch.float32, device=dev)
-    out_max = torch.empty((m, c), dtype=torch.float32, device=dev)
-    arg = torch.empty((m, c), dtype=torch.int32, device=dev)
-    with _on_device(dev):
-        stream = _stream()
-        key = (c, stream, "pair")
-        ws = data._workspaces.get(key)
-        if ws is None or ws.numel() < lib.texb_reduce_pair_workspace_bytes(n, c):
-            ws = _scratch(lib.texb_reduce_pair_workspace_bytes(n, c), dev)
-            data._workspaces[key] = ws
-        _native.check(
-            lib.texb_segment_reduce_pair(op, feats.data_ptr(), feats.element_size(), data.sid.data_ptr(),
-                                         data._perm_ptr, data.preSum.data_ptr(), int(data.has_empty or n == 0),
-                                         data.balance.data_ptr(), data.balance.numel(), n, c, m,
-                                         out_sum.data_ptr(), out_max.data_ptr(), arg.data_ptr(), int(arg_base),
-                                         ws.data_ptr(), ws.numel(), stream),
-            "texb_segment_reduce_pair")
-    return out_sum, out_max, arg
+    if data._pending is not None:
+        data._poll()
+    return _ext.reduce_pair(data._plan, op, feats, arg_base)
 
 
-def _grad(g: torch.Tensor) -> torch.Tensor:
-    # Autograd may hand over an expanded or strided gradient; the C ABI wants rows.
-    return g.contiguous() if g.dtype == torch.float32 else g.float().contiguous()
+_BACK_MODE = {"sum": _native.OP_SUM, "mean": _native.OP_MEAN, "max": _native.OP_MAX}
 
 
 def _broadcast_back(mode: str, data: "ScatterData", g: torch.Tensor, arg) -> torch.Tensor:
     """Gradient of the input rows: one fused pass in segment-sorted order (the
     plan's ``sid`` / ``perm``), so each row of ``g`` is fetched once per segment."""
-    g = _grad(g)
-    n, c, m = data.num_total, g.shape[1], data.num_unq
-    g_input = g.new_empty((n, c))
-    lib = _native.lib()
-    perm = None if data.perm is None else data.perm.data_ptr()
-    with _on_device(g.device):
-        if mode == "sum":
-            st = lib.texb_scatter_sum_backward(g.data_ptr(), data.sid.data_ptr(), perm, g_input.data_ptr(),
-                                               n, c, m, _stream())
-        elif mode == "mean":
-            st = lib.texb_scatter_mean_backward(g.data_ptr(), data.sid.data_ptr(), perm, data.preSum.data_ptr(),
-                                                g_input.data_ptr(), n, c, m, _stream())
-        else:
-            st = lib.texb_scatter_max_backward(g.data_ptr(), arg.data_ptr(), data.sid.data_ptr(), perm,
-                                               g_input.data_ptr(), n, c, m, _stream())
-        _native.check(st, f"texb_scatter_{mode}_backward")
-    return g_input
+    return _ext.broadcast_back(data._plan, _BACK_MODE[mode], g, arg)
 
 
 class ScatterSumFunction(Function):
@@ -521,17 +477,7 @@ class ScatterMeanMaxFunction(Function):
     @staticmethod
     def backward(ctx, g_mean, g_max, g_arg):
         (arg,) = ctx.saved_tensors
-        data = ctx.plan
-        g_mean, g_max = _grad(g_mean), _grad(g_max)
-        n, c, m = data.num_total, g_mean.shape[1], data.num_unq
-        g_input = g_mean.new_empty((n, c))
-        perm = None if data.perm is None else data.perm.data_ptr()
-        with _on_device(g_mean.device):
-            _native.check(
-                _native.lib().texb_scatter_mean_max_backward(
-                    g_mean.data_ptr(), g_max.data_ptr(), arg.data_ptr(), data.sid.data_ptr(), perm,
-                    data.preSum.data_ptr(), g_input.data_ptr(), n, c, m, _stream()),
-                "texb_scatter_mean_max_backward")
+        g_input = _ext.mean_max_backward(ctx.plan._plan, g_mean, g_max, arg)
         return g_input.to(ctx.in_dtype), None
 
 
@@ -547,10 +493,7 @@ class GetPreSumFunction(Function):
         unq_inv = unq_inv.contiguous()
         num_unq = int(unq_inv[-1]) + 1 if unq_inv.numel() else 0
         pre_sum = unq_inv.new_empty(num_unq + 1)
-        with _on_device(unq_inv.device):
-            _native.check(_native.lib().texb_get_pre_sum(unq_inv.data_ptr(), pre_sum.data_ptr(),
-                                                         unq_inv.numel(), num_unq, _stream()),
-                          "texb_get_pre_sum")
+        _ext.getPreSum(unq_inv, pre_sum)
         ctx.mark_non_differentiable(pre_sum)
         return pre_sum
 
