@@ -67,10 +67,11 @@ class ClockSampler(threading.Thread):
     """Polls SM clock and clock-event reasons through NVML while the timed
     region runs (read-only queries)."""
 
-    def __init__(self, index, period_s=0.004):
+    def __init__(self, index, period_s=0.001):
         super().__init__(daemon=True)
         self.period = period_s
         self.samples, self.reasons = [], set()
+        self.marks = {}
         self.sm_max = None
         self._halt = threading.Event()
         self.ok = False
@@ -103,13 +104,36 @@ class ClockSampler(threading.Thread):
                 pass
             time.sleep(self.period)
 
+    def mark(self, name):
+        """Remembers how many samples had been taken when `name` happened."""
+        self.marks[name] = len(self.samples)
+
     def stop(self):
         self._halt.set()
         if self.ok:
             self.join(timeout=1.0)
         med = statistics.median(self.samples) if self.samples else None
+        a, b = self.marks.get("timed_begin", 0), self.marks.get("timed_end", len(self.samples))
+        inside = self.samples[a:b]
         return {"sm_mhz": med, "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons),
-                "samples": len(self.samples)}
+                "samples": len(self.samples), "samples_in_timed_region": len(inside),
+                "sm_mhz_in_timed_region": statistics.median(inside) if inside else None,
+                "covers": "warm-up, the timed region and the per-operator loops that follow it"}
+
+
+def headline_workload():
+    return (f"skewed segments: N={N_POINTS:,} points, C={CHANNELS} fp32, M={N_SEGMENTS:,} segments "
+            f"(Zipf 1.2 sizes + one {N_POINTS // 10:,}-point segment), ids randomly permuted; "
+            "step = scatter_sum + scatter_mean + scatter_max forward with a prebuilt plan")
+
+
+def headline_config(world):
+    """`config` of the line, identical for both arms (the reference arm times the same
+    workload; what differs between the arms is said in their `note` fields)."""
+    return {"workload": headline_workload(), "points_per_gpu": N_POINTS, "channels": CHANNELS,
+            "segments": N_SEGMENTS, "frames": world, "sharding": "one frame per GPU, no collective",
+            "l2": f"inputs_exceed_l2 ({4 * N_POINTS * CHANNELS / 1e6:.0f} MB of features read by each of "
+                  "the three reductions of a step)", "seed": SEED}
 
 
 def physical_gpu_index(local_rank):
@@ -169,6 +193,8 @@ def run_ours(args):
                        else "ids randomly permuted; ") +
                     "step = scatter_sum + scatter_mean + scatter_max forward with a prebuilt plan"
                     + ("" if (n, c, m) == (N_POINTS, CHANNELS, N_SEGMENTS) else " [reduced size, for profiling only]"))
+    headline = (args.workload == "skewed" and not args.sorted_ids and args.features == "fp32"
+                and (n, c, m) == (N_POINTS, CHANNELS, N_SEGMENTS))
     bf16 = args.features == "bf16"
     if bf16:
         workload = workload.replace("fp32", "bf16 features, fp32 accumulation and output", 1) + " [secondary workload]"
@@ -187,9 +213,14 @@ def run_ours(args):
 
     entry = lib.texb_segment_reduce_bf16 if bf16 else lib.texb_segment_reduce
 
+    # The plan was built, and the device synchronised, long before the first reduction:
+    # the kernels may read it ahead of their stream wait (TEXB_PLAN_SETTLED).
+    torch.cuda.synchronize()
+    plan_flags = _native.PLAN_SETTLED
+
     def reduce(name):
         st = entry(ops[name], feat.data_ptr(), data.sid.data_ptr(), perm_ptr,
-                   data.preSum.data_ptr(), 0, data.balance.data_ptr(), data.balance.numel(),
+                   data.preSum.data_ptr(), plan_flags, data.balance.data_ptr(), data.balance.numel(),
                    n, c, m, outs[name].data_ptr(), arg.data_ptr(), 0, ws.data_ptr(), ws.numel(), stream)
         if st != 0:
             raise RuntimeError(_native.last_error())
@@ -198,6 +229,8 @@ def run_ours(args):
         if world > 1:
             dist.barrier()
 
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         for name in ops:
             reduce(name)
@@ -210,10 +243,9 @@ def run_ours(args):
     sampled = [i for i in range(k) if i % 8 == 0]
     ev_sum = {i: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for i in sampled}
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(physical_gpu_index(local_rank))
     barrier()
     torch.cuda.synchronize()
-    sampler.start()
+    sampler.mark("timed_begin")
     t0.record()
     for i in range(k):
         if i in ev_sum:
@@ -226,7 +258,7 @@ def run_ours(args):
         reduce("max")
     t1.record()
     torch.cuda.synchronize()
-    clocks = sampler.stop()
+    sampler.mark("timed_end")
     barrier()
     elapsed_ms = t0.elapsed_time(t1)
     if world > 1:
@@ -253,23 +285,32 @@ def run_ours(args):
         per_op[name] = {"us": round(us, 2), "GBps": round(gbs, 1), "Mpoints_per_s": round(n / us, 1),
                         "frac_of_8000": round(gbs / HBM_NOMINAL_GBS, 4)}
 
+    clocks = sampler.stop()
     peak, peak_kind = measured_peak_gbs()
-    # Duration of one launch pair of the sum reduction.  Two CUDA-event measurements:
-    # "in_stream": the mean over 50 back-to-back launch pairs (how the kernel runs in
-    # the timed region, where the next kernel is placed while the previous one drains);
-    # "bracketed": the mean of the pairs that were individually bracketed by events
-    # inside the timed region, which serialises them against their neighbours.
-    in_stream_us = per_op["sum"]["us"]
-    achieved = bytes_op["sum"] / in_stream_us / 1e3
+    # Roofline of the dominant kernel, segment_reduce_staged_kernel, from the TIMED REGION
+    # itself: the region is K x (sum, mean, max) launch pairs of that one kernel template
+    # and nothing else, so its average launch takes ms_per_step / 3 and moves
+    # bytes_step / 3 algorithmic bytes.  Beside it: the sum launch pairs that were
+    # individually bracketed by events inside the region (which serialises them against
+    # their neighbours), and the per-operator loops that ran right after the region.
+    per_launch_us = ms_per_step * 1e3 / 3
+    per_launch_bytes = bytes_step / 3
+    achieved = per_launch_bytes / per_launch_us / 1e3
     bracketed = bytes_op["sum"] / (sum_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": f"segment_reduce_staged_kernel<sum, {args.features}> + segment_fixup_kernel (one launch pair)",
+    roofline = {"bound": "hbm",
+                "kernel": f"segment_reduce_staged_kernel<{args.features}> + segment_fixup_kernel (one launch pair), "
+                          "average over the sum, mean and max launches of the timed region",
+                "timing": f"CUDA events around the timed region: {k} steps x 3 launch pairs",
                 "achieved": round(achieved, 1), "peak": peak, "peak_source": f"hbm_gbs of {peak_kind} copy",
                 "unit": "GB/s", "frac": round(achieved / peak, 4), "frac_of_nominal_8000": round(achieved / HBM_NOMINAL_GBS, 4),
-                "algorithmic_bytes_per_launch": bytes_op["sum"], "us_per_launch": in_stream_us,
-                "bracketed_in_timed_region": {"us_per_launch": round(sum_ms * 1e3, 2), "launches": len(ev_sum),
-                                              "achieved": round(bracketed, 1), "frac": round(bracketed / peak, 4)},
-                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (n, c, m) == (N_POINTS, CHANNELS, N_SEGMENTS)
-                and args.workload == "skewed" and not bf16 and not args.sorted_ids else None}
+                "algorithmic_bytes_per_launch": round(per_launch_bytes), "us_per_launch": round(per_launch_us, 2),
+                "sum_bracketed_in_timed_region": {"us_per_launch": round(sum_ms * 1e3, 2), "launches": len(ev_sum),
+                                                  "achieved": round(bracketed, 1), "frac": round(bracketed / peak, 4)},
+                "sum_in_loop_after_region": {"us_per_launch": per_op["sum"]["us"], "achieved": per_op["sum"]["GBps"],
+                                             "frac": round(per_op["sum"]["GBps"] / peak, 4)},
+                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if headline else None,
+                "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one sum launch pair in an ncu capture "
+                                  "of this workload (profiles/); not measured by this run" if headline else None}
 
     # ---- end to end through the public operators, host buffers in pinned memory
     e2e = None
@@ -339,13 +380,36 @@ def run_ours(args):
             t = torch.tensor([e_ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             e_ms = float(t.item())
+        # The ceiling of that leg: the same input bytes copied from the same pinned buffers by
+        # every rank at once and nothing else (one cudaMemcpyAsync per tensor), max over ranks.
+        barrier()
+        a2, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a2.record()
+        for _ in range(3):
+            d_feat[0].copy_(h_feat, non_blocking=True)
+            d_ids[0].copy_(h_ids, non_blocking=True)
+            d_cnt[0].copy_(h_cnt, non_blocking=True)
+        b2.record()
+        torch.cuda.synchronize()
+        h2d_ms = a2.elapsed_time(b2) / 3
+        if world > 1:
+            t = torch.tensor([h2d_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            h2d_ms = float(t.item())
+        h2d_bytes = h_feat.numel() * 4 + h_ids.numel() * 8 + h_cnt.numel() * 8
+        e2e_ceiling = {"h2d_only_ms_per_step": round(h2d_ms, 3),
+                       "h2d_GBps_per_gpu": round(h2d_bytes / (h2d_ms * 1e-3) / 1e9, 1),
+                       "e2e_over_h2d_only": round(e_ms / h2d_ms, 3),
+                       "note": "all ranks copy their step's inputs from pinned host memory at the same time; the "
+                               "end-to-end step cannot be shorter than this"}
         e2e = {"value": round(world * bytes_step / (e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
                "ms_per_step": round(e_ms, 3), "steps": steps_e2e,
                "h2d_bytes_per_step": h_feat.numel() * 4 + h_ids.numel() * 8 + h_cnt.numel() * 8,
                "d2h_bytes_per_step": 3 * m * c * 4 + m * c * 4 + 32,
                "includes": "H2D of feat, ids and counts from pinned memory, segment plan build, sum/mean/max "
                            "through torchex_b200.scatter_*, D2H of the three results and argmax; the upload of "
-                           "the next step overlaps the work of the current one (two streams, two device buffers)"}
+                           "the next step overlaps the work of the current one (two streams, two device buffers)",
+               "h2d_ceiling": e2e_ceiling}
         del h_feat
 
     # ---- multi-frame batch: 16 frames x 200 000 points, C = 128, frames sharded over the ranks
@@ -366,10 +430,11 @@ def run_ours(args):
             "steps": k, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": workload,
-                       "points_per_gpu": n, "channels": c, "segments": m, "frames": world,
-                       "sharding": "one frame per GPU, no collective", "l2": f"inputs_exceed_l2 ({4 * n * c / 1e6:.0f} MB of features read by each of the three reductions of a step)",
-                       "seed": SEED},
+            "config": headline_config(world) if headline else
+            {"workload": workload, "points_per_gpu": n, "channels": c, "segments": m, "frames": world,
+             "sharding": "one frame per GPU, no collective",
+             "l2": f"inputs_exceed_l2 ({4 * n * c / 1e6:.0f} MB of features read by each of the three reductions of a step)",
+             "seed": SEED},
             "Mpoints_per_s": round(world * 3 * n / (ms_per_step * 1e-3) / 1e6, 1),
             "pct_of_hbm_8000": round(100 * value / world / HBM_NOMINAL_GBS, 2),
             "per_op": per_op,
@@ -385,6 +450,8 @@ def run_ours(args):
         emit(line)
     if world > 1:
         dist.destroy_process_group()
+    if multi is not None and multi.get("parity") == "fail":
+        raise SystemExit("multi-frame results differ from the host check")
 
 
 def other_configs(dev):
@@ -437,9 +504,11 @@ def other_configs(dev):
         perm = None if data.perm is None else data.perm.data_ptr()
         b = algorithmic_bytes(n, c, m)
         res = {"points": n, "channels": c, "segments": m, "note": note}
+        torch.cuda.synchronize()  # the plan is complete and the host knows it
         for name, op in (("sum", _native.OP_SUM), ("mean", _native.OP_MEAN), ("max", _native.OP_MAX)):
             def call(on_stream):
-                st = lib.texb_segment_reduce(op, feat.data_ptr(), data.sid.data_ptr(), perm, data.preSum.data_ptr(), 0,
+                st = lib.texb_segment_reduce(op, feat.data_ptr(), data.sid.data_ptr(), perm, data.preSum.data_ptr(),
+                                             _native.PLAN_SETTLED,
                                              data.balance.data_ptr(), data.balance.numel(), n, c, m, out.data_ptr(),
                                              arg.data_ptr(), 0, ws.data_ptr(), ws.numel(), on_stream)
                 if st != 0:
@@ -449,6 +518,32 @@ def other_configs(dev):
             if graph:
                 res[name]["us_in_cuda_graph"] = round(graph_timed(call), 2)
         return res, data, arg
+
+    def through_module(ids, cnt, feat, note):
+        """Per call from Python through the compiled scatter_ext module: the reference's own
+        entry points (sum / max on sorted rows with caller-allocated outputs, as
+        torchex/operator_py/scatter_op.py:40-41, 97-99 calls them) and the operators of this
+        package on the unsorted ids.  Back-to-back calls, CUDA events around the loop."""
+        from torchex_b200 import scatter_ext, scatter_max, scatter_sum
+        n, c = feat.shape
+        m = cnt.numel()
+        order = torch.argsort(ids, stable=True)
+        feat_s = feat[order.to(dev)].contiguous()
+        ids_s = ids[order].int().to(dev)
+        pre = torch.empty(m + 1, dtype=torch.int32, device=dev)
+        scatter_ext.getPreSum(ids_s, pre)
+        out = torch.zeros((m, c), device=dev)
+        arg = torch.zeros((m, c), dtype=torch.int32, device=dev)
+        max_cnt = int(cnt.max())
+        data = ScatterData(ids.to(dev), cnt.to(dev))
+        assert data.max_cnt == max_cnt  # the plan statistics have reached the host
+        res = {"points": n, "channels": c, "segments": m, "max_cnt": max_cnt, "note": note}
+        res["scatter_ext.sum(feats, preSum, out, max_cnt)"] = round(timed(lambda: scatter_ext.sum(feat_s, pre, out, max_cnt), 200), 2)
+        res["scatter_ext.max(feats, preSum, out, arg, max_cnt)"] = round(timed(lambda: scatter_ext.max(feat_s, pre, out, arg, max_cnt), 200), 2)
+        res["scatter_sum(feats, data)"] = round(timed(lambda: scatter_sum(feat, data), 200), 2)
+        res["scatter_max(feats, data)"] = round(timed(lambda: scatter_max(feat, data), 200), 2)
+        res["unit"] = "us per call"
+        return res
 
     table = {}
     # the headline workload with bf16 features (fp32 accumulation and output)
@@ -485,8 +580,32 @@ def other_configs(dev):
         nbytes = algorithmic_bytes(n, c, m, f.element_size())["max"] + 4 * m * c
         pair[label] = {"us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1), "Mpoints_per_s": round(n / us, 1)}
     table["skewed_1m_c128_mean_max_pair"] = pair
-    del feat16, feat32, data, out, out2, arg
+    # cold path: plan build + one reduction of the headline workload through the operators
+    from torchex_b200 import scatter_sum
+    d_ids, d_cnt = ids.to(dev), cnt.to(dev)
+
+    def cold():
+        scatter_sum(feat32, ScatterData(d_ids, d_cnt))
+    table["skewed_1m_c128_cold"] = {"points": n, "channels": c, "segments": m, "us": round(timed(cold, 20), 1),
+                                    "note": "ScatterData(unq_inv, unq_cnts) on unsorted int64 ids (one host "
+                                            "synchronisation) followed by one scatter_sum, per call"}
+    del feat16, data, out, out2, arg
+    # the headline workload with the ids already sorted: the only layout TorchEx's callers have today
+    ids_s, cnt_s = W.skewed_ids(n, m, seed=SEED, shuffled=False)
+    table["skewed_1m_c128_sorted"], _, _ = forward(ids_s, cnt_s, feat32, "sorted",
+                                                   "config 3 with sorted ids (no permutation): 512 MB of features")
+    del feat32
+    # the workload of the reference's own test (test/test_scatter.py:10-24): 500 sorted groups of
+    # 100..4999 rows, C = 128, features a permutation of 0..cnt-1 repeated across the channels
+    ids_t, cnt_t, feat_t = W.reference_test_groups(seed=SEED, device=dev)
+    table["reference_test_shape"], _, _ = forward(ids_t, cnt_t, feat_t, "test_scatter",
+                                                  "shape of torchex test/test_scatter.py (sorted ids); "
+                                                  f"{feat_t.numel() * 4 / 1e6:.0f} MB of features")
+    del feat_t
     ids, cnt = W.uniform_ids(20_000, 2_000, SEED)
+    table["uniform_20k_c16_per_call"] = through_module(ids, cnt, W.features(20_000, 16, SEED, device=dev),
+                                                       "config 1 through the compiled module: one launch per call "
+                                                       "(small input, short segments)")
     table["uniform_20k_c16"], _, _ = forward(ids, cnt, W.features(20_000, 16, SEED, device=dev), "c1",
                                              "1.3 MB of features: L2-resident and launch-bound "
                                              "(us: launched from Python; us_in_cuda_graph: 20 calls replayed from a CUDA graph)",
@@ -516,7 +635,10 @@ def other_configs(dev):
 
 def multi_frame_bench(args, rank, world, dev, barrier):
     """Strong scaling of the 16-frame batch: frames sharded over the ranks;
-    Mpoints/s with the outputs left sharded and with an NCCL all-gather."""
+    Mpoints/s with the outputs left sharded and with every result replicated on every
+    GPU over NCCL.  Outside the timed regions each rank checks its own results against
+    torch.Tensor.scatter_reduce_ on the host, and the ranks check that their replicated
+    copies are identical."""
     import torch.distributed as dist
     from torchex_b200 import frames as F, workloads as W
     frames, per_frame, c = 16, 200_000, CHANNELS
@@ -531,18 +653,18 @@ def multi_frame_bench(args, rank, world, dev, barrier):
     layout = F.shard_layout(frame_segments, [per_frame] * frames, rank, world)
     shard = F.FrameShard([i for i, _ in mine], [cn for _, cn in mine], layout, dev)
     feats = W.features(layout.row_count, c, SEED + 200 + rank, device=dev)
-    res = {"frames": frames, "points": frames * per_frame, "channels": c, "segments": layout.seg_total}
-    for mode, replicated in (("sharded", False), ("replicated", True)):
-        def step():
-            shard.scatter("sum", feats, replicated)
-            shard.scatter("mean", feats, replicated)
-            shard.scatter("max", feats, replicated)
+    ops3 = ("sum", "mean", "max")
+    res = {"frames": frames, "points": frames * per_frame, "channels": c, "segments": layout.seg_total,
+           "gather": "none (one GPU)" if world == 1 else
+           f"{F._gather_method(layout, None)}: exact-size transfers straight into the rows of the result, "
+           "started after each reduction and waited for at the end of the step"}
+
+    def timed(step, reps=10):
         for _ in range(3):
             step()
         torch.cuda.synchronize()
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = 10
         a.record()
         for _ in range(reps):
             step()
@@ -553,11 +675,104 @@ def multi_frame_bench(args, rank, world, dev, barrier):
             t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
+        return ms
+
+    for mode, replicated in (("sharded", False), ("replicated", True)):
+        ms = timed(lambda: shard.scatter_many(ops3, feats, replicated))
         res[f"Mpoints_per_s_{mode}"] = round(3 * frames * per_frame / (ms * 1e-3) / 1e6, 1)
         res[f"ms_per_step_{mode}"] = round(ms, 4)
+    # bytes every GPU receives per replicated step: the other ranks' rows of sum, mean, max and arg
+    inbound = 4 * (layout.seg_total - layout.seg_count) * c * 4
+    if world > 1:
+        t = torch.tensor([float(inbound)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        inbound = int(t.item())
+        res["replicated_inbound_bytes_per_gpu"] = inbound
+        res["replicated_inbound_GBps_per_gpu"] = round(inbound / (res["ms_per_step_replicated"] * 1e-3) / 1e9, 1)
+    # mean and max (+ argmax) from one pass, three tensors replicated instead of four
+    ms = timed(lambda: shard.scatter("mean_max", feats, True))
+    res["ms_per_step_replicated_mean_max_pair"] = round(ms, 4)
+
+    # ---- the same batch on ONE GPU, in this same run (rank 0; the others wait)
+    if world > 1:
+        one_ms = None
+        if rank == 0:
+            every = [W.voxel_frame(per_frame, SEED + 100 + f) for f in range(frames)]
+            lay1 = F.shard_layout(frame_segments, [per_frame] * frames, 0, 1)
+            sh1 = F.FrameShard([i for i, _ in every], [cn for _, cn in every], lay1, dev)
+            f1 = W.features(lay1.row_count, c, SEED + 300, device=dev)
+            for _ in range(3):
+                sh1.scatter_many(ops3, f1)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(10):
+                sh1.scatter_many(ops3, f1)
+            b.record()
+            torch.cuda.synchronize()
+            one_ms = a.elapsed_time(b) / 10
+            del sh1, f1
+        barrier()
+        t = torch.tensor([one_ms or 0.0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        one_ms = float(t.item())
+        res["ms_per_step_one_gpu_same_run"] = round(one_ms, 4)
+        res["speedup_vs_1gpu"] = {"sharded": round(one_ms / res["ms_per_step_sharded"], 2),
+                                  "replicated": round(one_ms / res["ms_per_step_replicated"], 2)}
+
+    # ---- parity, outside every timed region
+    ok = True
+    try:
+        got = shard.scatter_many(ops3, feats, False)
+        seg0 = 0
+        for i, (ids_f, cnt_f) in enumerate(mine):  # frame by frame: keeps the host arrays small
+            rows = slice(i * per_frame, (i + 1) * per_frame)
+            segs = slice(seg0, seg0 + cnt_f.numel())
+            ok = ok and host_check(feats[rows].cpu(), ids_f, cnt_f.numel(), got["sum"][segs].cpu(), got["mean"][segs].cpu(),
+                                   got["max"][0][segs].cpu(), got["max"][1][segs].cpu(), layout.row_base + i * per_frame)
+            seg0 += cnt_f.numel()
+        if world > 1:
+            rep = shard.scatter_many(ops3, feats, True)
+            mine_rows = slice(layout.seg_base, layout.seg_base + layout.seg_count)
+            ok = ok and torch.equal(rep["sum"][mine_rows], got["sum"]) and torch.equal(rep["max"][1][mine_rows], got["max"][1])
+            # identical replicated copies on every rank: per-tensor checksums agree
+            sums = torch.stack([t.view(torch.int32).long().sum() for t in
+                                (rep["sum"], rep["mean"], rep["max"][0], rep["max"][1])])
+            hi_, lo_ = sums.clone(), sums.clone()
+            dist.all_reduce(hi_, op=dist.ReduceOp.MAX)
+            dist.all_reduce(lo_, op=dist.ReduceOp.MIN)
+            ok = ok and torch.equal(hi_, lo_)
+    except Exception as exc:  # a failed check must not hide the measurements
+        res["parity_error"] = f"{type(exc).__name__}: {exc}"
+        ok = False
+    if world > 1:
+        t = torch.tensor([1 if ok else 0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        ok = bool(t.item())
+    res["parity"] = "ok" if ok else "fail"
+    res["parity_how"] = ("each rank: its shard's sum / mean within 1e-6 + 1e-5 |x| of an fp64 scatter_reduce_ on the host, "
+                         "max bit-equal to scatter_reduce_ amax, arg = lowest global row attaining it; replicated copies "
+                         "checksum-identical on all ranks and equal to the local shard in its rows")
     res["note"] = ("step = sum + mean + max over all 16 frames through the operator API; sharded = outputs stay on the "
-                   "GPU that owns the frames, replicated = NCCL all-gather of every result to every GPU")
+                   "GPU that owns the frames, replicated = every result on every GPU")
     return res
+
+
+def host_check(feat, ids, m, s, mean, mx, arg, row_base):
+    """torch.Tensor.scatter_reduce_ on the host as the checker of one shard's results."""
+    n, c = feat.shape
+    index = ids[:, None].expand(-1, c)
+    s64 = torch.zeros((m, c), dtype=torch.float64).scatter_reduce_(0, index, feat.double(), "sum", include_self=False)
+    cnt = torch.bincount(ids, minlength=m).clamp(min=1)[:, None].double()
+    ok = bool(((s.double() - s64).abs() <= 1e-6 + 1e-5 * s64.abs()).all())
+    mean64 = s64 / cnt
+    ok = ok and bool(((mean.double() - mean64).abs() <= 1e-6 + 1e-5 * mean64.abs()).all())
+    amax = torch.zeros((m, c)).scatter_reduce_(0, index, feat, "amax", include_self=False)
+    ok = ok and torch.equal(mx, amax)
+    # lowest row attaining the maximum
+    rows = torch.arange(n)[:, None].expand(-1, c)
+    cand = torch.where(feat == amax[ids], rows, torch.full_like(rows, n))
+    low = torch.full((m, c), n, dtype=torch.int64).scatter_reduce_(0, index, cand, "amin", include_self=True)
+    return ok and torch.equal(arg.long(), low + row_base)
 
 
 # ---------------------------------------------------------------------------- CPU
@@ -618,11 +833,10 @@ def run_reference(args):
         "impl": "reference", "metric": "scatter_fwd_GBps", "value": round(value, 3), "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": round(dt * 1e3, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "skewed segments: N=1,000,000 points, C=128 fp32, M=50,000 segments "
-                               "(Zipf 1.2 sizes + one 100,000-point segment), ids randomly permuted; "
-                               "step = scatter_sum + scatter_mean + scatter_max forward",
-                   "note": "TorchEx has no CPU kernel for this path (its binding rejects non-CUDA tensors); "
-                           "this arm is the CPU statement of the operators, torch.Tensor.scatter_reduce_, on the host cores"},
+        "config": headline_config(args.gpus),
+        "note": "TorchEx has no CPU kernel for this path (its binding rejects non-CUDA tensors); this arm is the CPU "
+                "statement of the operators, torch.Tensor.scatter_reduce_ (no plan to prebuild), on the host cores of "
+                "rank 0 only, whatever --gpus says",
         "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -633,9 +847,10 @@ def run_reference(args):
 
 
 def reference_cuda_timing(n, c, m):
-    """TorchEx's own CUDA kernels (compiled unmodified into oracle/_ref) on the SORTED
-    variant of the workload -- the only layout they accept -- timed with CUDA events
-    on cuda:0.  Reported beside the CPU arm; it is not the arm's value."""
+    """TorchEx's own CUDA kernels (compiled unmodified into oracle/_ref) timed with CUDA
+    events on cuda:0, on sorted ids -- the only layout they accept: the headline workload,
+    the shape of the reference's own test, and config 1 per call.  Reported beside the CPU
+    arm; it is not the arm's value."""
     try:
         from oracle import scatter_oracle as O
         from torchex_b200 import workloads as W
@@ -644,31 +859,45 @@ def reference_cuda_timing(n, c, m):
         ref = O.reference_lib()
         dev = torch.device("cuda", 0)
         torch.cuda.set_device(dev)
+
+        def one(ids, cnt, feat, reps, unit):
+            n, c = feat.shape
+            m = cnt.numel()
+            max_cnt = int(cnt.max())
+            if ref.torchex_ref_limits(c, m, max_cnt, n) != 0:
+                return {"unavailable": "shape outside the reference's launch limits"}
+            d_ids = ids.int().to(dev)
+            pre = torch.zeros(m + 1, dtype=torch.int32, device=dev)
+            out = torch.zeros((m, c), device=dev)
+            arg = torch.zeros((m, c), dtype=torch.int32, device=dev)
+            assert ref.torchex_ref_get_pre_sum(d_ids.data_ptr(), pre.data_ptr(), n) == 0
+            b = algorithmic_bytes(n, c, m)
+            res = {"points": n, "channels": c, "segments": m, "layout": "ids sorted (required by the reference)",
+                   "max_cnt": max_cnt}
+            for name, call in (("sum", lambda: ref.torchex_ref_scatter_sum(feat.data_ptr(), pre.data_ptr(), out.data_ptr(), c, m, max_cnt, n)),
+                               ("max", lambda: ref.torchex_ref_scatter_max(feat.data_ptr(), pre.data_ptr(), out.data_ptr(), arg.data_ptr(), c, m, max_cnt, n))):
+                for _ in range(2):
+                    assert call() == 0
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps):
+                    assert call() == 0
+                e1.record()
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / reps
+                res[name] = ({"ms": round(ms, 3)} if unit == "ms" else {"us": round(ms * 1e3, 2)})
+                res[name]["GBps"] = round(b[name] / ms / 1e6, 1)
+            return res
+
         ids, cnt = W.skewed_ids(n, m, seed=SEED, shuffled=False)
-        max_cnt = int(cnt.max())
-        if ref.torchex_ref_limits(c, m, max_cnt, n) != 0:
-            return {"unavailable": "shape outside the reference's launch limits"}
-        feat = W.features(n, c, SEED, device=dev)
-        d_ids = ids.int().to(dev)
-        pre = torch.zeros(m + 1, dtype=torch.int32, device=dev)
-        out = torch.zeros((m, c), device=dev)
-        arg = torch.zeros((m, c), dtype=torch.int32, device=dev)
-        assert ref.torchex_ref_get_pre_sum(d_ids.data_ptr(), pre.data_ptr(), n) == 0
-        b = algorithmic_bytes(n, c, m)
-        res = {"layout": "ids sorted (required by the reference)", "max_cnt": max_cnt}
-        for name, call in (("sum", lambda: ref.torchex_ref_scatter_sum(feat.data_ptr(), pre.data_ptr(), out.data_ptr(), c, m, max_cnt, n)),
-                           ("max", lambda: ref.torchex_ref_scatter_max(feat.data_ptr(), pre.data_ptr(), out.data_ptr(), arg.data_ptr(), c, m, max_cnt, n))):
-            assert call() == 0
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            reps = 3
-            e0.record()
-            for _ in range(reps):
-                assert call() == 0
-            e1.record()
-            torch.cuda.synchronize()
-            ms = e0.elapsed_time(e1) / reps
-            res[name] = {"ms": round(ms, 3), "GBps": round(b[name] / ms / 1e6, 1)}
+        res = one(ids, cnt, W.features(n, c, SEED, device=dev), 3, "ms")  # keys of the headline kept at top level
+        ids_t, cnt_t, feat_t = W.reference_test_groups(seed=SEED, device=dev)
+        res["reference_test_shape"] = one(ids_t, cnt_t, feat_t, 5, "ms")
+        ids1, cnt1 = W.uniform_ids(20_000, 2_000, SEED)
+        order = torch.argsort(ids1, stable=True)
+        res["uniform_20k_c16_per_call"] = one(ids1[order], cnt1, W.features(20_000, 16, SEED, device=dev)[order.to(dev)].contiguous(),
+                                              200, "us")
         return res
     except Exception as exc:  # the CPU arm must still print its line
         return {"unavailable": f"{type(exc).__name__}: {exc}"}

@@ -24,7 +24,7 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "liboracle_scatter.so")
 REF_SO = os.path.join(HERE, "_ref", "libtorchex_scatter_ref.so")
-REF_OP_PYC = os.path.join(HERE, "_ref", "torchex_scatter_op.pyc")
+REF_OP_PYC = os.path.join(HERE, "_ref", "torchex_scatter_op.compiled")
 FLT_MAX = float(np.finfo(np.float32).max)
 
 _c = ctypes

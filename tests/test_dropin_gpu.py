@@ -23,7 +23,7 @@ pytestmark = pytest.mark.gpu
 def reference_ops():
     mod = O.reference_operator_module(scatter_ext.native)
     if mod is None:
-        pytest.skip("oracle/_ref/torchex_scatter_op.pyc was not built")
+        pytest.skip("oracle/_ref/torchex_scatter_op.compiled was not built")
     return mod
 
 

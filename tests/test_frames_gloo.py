@@ -1,6 +1,8 @@
 """Bookkeeping of the multi-frame driver on two CPU ranks (gloo): frame blocks,
-id rebasing, global argmax rows and the padded all-gather.  The CUDA reduce is
-replaced by the CPU oracle through FrameShard's `reduce` hook, so no GPU is used."""
+id rebasing, global argmax rows and the gather of the shards (padded equal-size
+all-gather, and exact-size point-to-point transfers into the rows of the result).
+The CUDA reduce is replaced by the CPU oracle through FrameShard's `reduce` hook,
+so no GPU is used."""
 import os
 import socket
 
@@ -53,9 +55,10 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, frames, per_frame, channels, out_dir):
+def _worker(rank, world, port, frames, per_frame, channels, out_dir, gather):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
+    os.environ["TEXB_GATHER"] = gather
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         all_frames = [W.voxel_frame(per_frame, 700 + f) for f in range(frames)]
@@ -73,15 +76,19 @@ def _worker(rank, world, port, frames, per_frame, channels, out_dir):
         mx, arg = shard.scatter("max", feats, replicated=True)
         res["max_all"], res["arg_all"] = mx, arg
         res["pair_mean"], res["pair_max"], res["pair_arg"] = shard.scatter("mean_max", feats, replicated=True)
+        many = shard.scatter_many(("sum", "mean", "max"), feats, replicated=True)  # gathers overlapped, waited at the end
+        res["many_sum"], res["many_mean"] = many["sum"], many["mean"]
+        res["many_max"], res["many_arg"] = many["max"]
         torch.save({k: v.clone() for k, v in res.items()}, os.path.join(out_dir, f"rank{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
 
-def test_two_rank_shards_reproduce_the_single_process_result(tmp_path):
+@pytest.mark.parametrize("gather", ["padded", "p2p"])
+def test_two_rank_shards_reproduce_the_single_process_result(tmp_path, gather):
     frames, per_frame, channels, world = 5, 3_000, 8, 2
     port = _free_port()
-    mp.spawn(_worker, args=(world, port, frames, per_frame, channels, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, frames, per_frame, channels, str(tmp_path), gather), nprocs=world, join=True)
     # single-process truth over the whole batch with global ids
     all_frames = [W.voxel_frame(per_frame, 700 + f) for f in range(frames)]
     segs = [int(c.numel()) for _, c in all_frames]
@@ -102,4 +109,6 @@ def test_two_rank_shards_reproduce_the_single_process_result(tmp_path):
         assert np.array_equal(out["pair_mean"].numpy(), want_mean)
         assert np.array_equal(out["pair_max"].numpy(), want_max)
         assert np.array_equal(out["pair_arg"].numpy(), want_arg)
+        assert np.array_equal(out["many_sum"].numpy(), want_sum) and np.array_equal(out["many_mean"].numpy(), want_mean)
+        assert np.array_equal(out["many_max"].numpy(), want_max) and np.array_equal(out["many_arg"].numpy(), want_arg)
         assert np.array_equal(out["sum_local"].numpy(), want_sum[seg_off[r]:seg_off[r + 1]])

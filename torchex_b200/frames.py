@@ -15,6 +15,7 @@ need to serve a batch of frames on an 8-GPU box.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Callable, List, Optional, Sequence, Tuple
 
@@ -82,26 +83,80 @@ def concat_local_ids(frame_ids: Sequence[torch.Tensor], frame_segments: Sequence
         torch.empty(0, dtype=torch.int64)
 
 
-def gather_shards(local: torch.Tensor, layout: ShardLayout, group=None) -> torch.Tensor:
-    """Replicated ``[seg_total, C]`` tensor from every rank's ``[seg_count, C]``
-    shard.  Shards are padded to the largest one so a single equal-size
-    all-gather (``all_gather_into_tensor``: NCCL over NVLink on GPUs, gloo on
-    CPU) moves them; the padding is dropped while the rows are put in place."""
+class PendingGather:
+    """A gather that may still be running on the collective library's own stream.
+    ``wait()`` makes the current stream wait for it and returns the replicated tensor."""
+
+    def __init__(self, out: torch.Tensor, works=(), keep=()):
+        self.out, self._works, self._keep = out, list(works), keep
+
+    def wait(self) -> torch.Tensor:
+        for w in self._works:
+            w.wait()
+        self._works, self._keep = [], ()
+        return self.out
+
+
+def _gather_method(layout: ShardLayout, group) -> str:
+    """How the shards travel.  NCCL moves exact sizes straight into the rows of the result
+    (grouped point-to-point transfers: every pair of GPUs has its own full-bandwidth path
+    through the NVSwitch); other backends (gloo on CPU ranks) get one equal-size all-gather
+    of padded shards.  TEXB_GATHER = p2p | broadcast | padded overrides the choice."""
+    forced = os.environ.get("TEXB_GATHER", "")
+    if forced in ("p2p", "broadcast", "padded"):
+        if forced == "broadcast" and min(layout.seg_counts_all) == 0:
+            return "p2p"  # a rank without segments has nothing to broadcast
+        return forced
+    return "p2p" if dist.get_backend(group) == "nccl" else "padded"
+
+
+def gather_shards_async(local: torch.Tensor, layout: ShardLayout, group=None) -> PendingGather:
+    """Starts the gather of every rank's ``[seg_count, C]`` shard into a replicated
+    ``[seg_total, C]`` tensor and returns at once.  With NCCL each shard lands directly in
+    its row range of the result, in this GPU's own memory -- no padding, no staging
+    buffer, no copy afterwards -- and the transfer runs on NCCL's stream, so kernels
+    launched next on the current stream (the next reduction) overlap it."""
     world = layout.world_size
     if world == 1:
-        return local
-    biggest = max(layout.seg_counts_all)
+        return PendingGather(local)
     c = local.shape[1]
-    padded = local.new_zeros((biggest, c))
-    padded[: local.shape[0]] = local
-    gathered = local.new_empty((world * biggest, c))
-    dist.all_gather_into_tensor(gathered, padded, group=group)
+    method = _gather_method(layout, group)
+    if method == "padded":
+        biggest = max(layout.seg_counts_all)
+        padded = local.new_zeros((biggest, c))
+        padded[: local.shape[0]] = local
+        gathered = local.new_empty((world * biggest, c))
+        dist.all_gather_into_tensor(gathered, padded, group=group)
+        out = local.new_empty((layout.seg_total, c))
+        start = 0
+        for r, cnt in enumerate(layout.seg_counts_all):
+            out[start:start + cnt] = gathered[r * biggest: r * biggest + cnt]
+            start += cnt
+        return PendingGather(out)
     out = local.new_empty((layout.seg_total, c))
-    start = 0
-    for r, cnt in enumerate(layout.seg_counts_all):
-        out[start:start + cnt] = gathered[r * biggest: r * biggest + cnt]
-        start += cnt
-    return out
+    views = list(out.split(layout.seg_counts_all))  # row ranges of the ranks: contiguous views of `out`
+    if method == "broadcast":
+        # unequal sizes: the process group issues one broadcast per rank inside one NCCL group
+        work = dist.all_gather(views, local, group=group, async_op=True)
+        return PendingGather(out, [work], (local,))
+    ops = []
+    for r in range(world):
+        if r == layout.rank:
+            continue
+        peer = r if group is None else dist.get_global_rank(group, r)
+        if local.shape[0] > 0:
+            ops.append(dist.P2POp(dist.isend, local, peer, group))
+        if layout.seg_counts_all[r] > 0:
+            ops.append(dist.P2POp(dist.irecv, views[r], peer, group))
+    works = dist.batch_isend_irecv(ops) if ops else []
+    views[layout.rank].copy_(local)
+    return PendingGather(out, works, (local,))
+
+
+def gather_shards(local: torch.Tensor, layout: ShardLayout, group=None) -> torch.Tensor:
+    """Replicated ``[seg_total, C]`` tensor from every rank's ``[seg_count, C]``
+    shard (see ``gather_shards_async``); usable on the current stream on return."""
+    return gather_shards_async(local, layout, group).wait()
 
 
 class FrameShard:
@@ -135,16 +190,30 @@ class FrameShard:
         ``mean_max`` the triple ``(mean, max, arg)``), or with
         ``replicated=True`` the full ``[seg_total, C]`` tensors on every rank."""
         res = self._reduce(op, feats, self.data, self.layout.row_base)
-        if op == "mean_max":  # (mean, max, arg) from one pass over feats
-            if replicated:
-                return tuple(gather_shards(t, self.layout, group) for t in res)
+        if not replicated:
             return res
-        if op == "max":
-            out, arg = res
-            if replicated:
-                return gather_shards(out, self.layout, group), gather_shards(arg, self.layout, group)
-            return out, arg
-        return gather_shards(res, self.layout, group) if replicated else res
+        if isinstance(res, tuple):
+            pending = [gather_shards_async(t, self.layout, group) for t in res]
+            return tuple(p.wait() for p in pending)
+        return gather_shards(res, self.layout, group)
+
+    def scatter_many(self, ops: Sequence[str], feats: torch.Tensor, replicated: bool = False, group=None):
+        """Several reductions of the same points, e.g. ``("sum", "mean", "max")``; returns
+        a dict op -> result as ``scatter`` gives it.  With ``replicated=True`` the gather
+        of each result is started as soon as its reduction has been launched and only
+        waited for at the end, so the transfer of reduction k runs under reduction k + 1."""
+        if not replicated:
+            return {op: self._reduce(op, feats, self.data, self.layout.row_base) for op in ops}
+        pending = {}
+        for op in ops:
+            res = self._reduce(op, feats, self.data, self.layout.row_base)
+            parts = res if isinstance(res, tuple) else (res,)
+            pending[op] = (isinstance(res, tuple), [gather_shards_async(t, self.layout, group) for t in parts])
+        out = {}
+        for op, (is_tuple, parts) in pending.items():
+            done = tuple(p.wait() for p in parts)
+            out[op] = done if is_tuple else done[0]
+        return out
 
 
 def _cuda_reduce(op: str, feats: torch.Tensor, data, row_base: int = 0):

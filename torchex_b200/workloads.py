@@ -144,3 +144,17 @@ def multi_frame(frames: int = 16, n_per_frame: int = 200_000, seed: int = 0):
     """``frames`` independent voxel frames; returns a list of (ids, cnt) with
     LOCAL ids per frame (a caller offsets them into one global id space)."""
     return [voxel_frame(n_per_frame, seed + f) for f in range(frames)]
+
+
+def reference_test_groups(groups: int = 500, cnt_min: int = 100, cnt_max: int = 5000, channel: int = 128,
+                          seed: int = 0, device="cpu"):
+    """The workload of the reference's own scatter test (test/test_scatter.py:10-24), seeded:
+    ``groups`` sorted groups of ``cnt_min`` .. ``cnt_max - 1`` rows; the features of a group
+    are a random permutation of 0 .. cnt - 1, the same in every channel.  Returns
+    (ids int64 [N] sorted, cnt int64 [groups], feat float32 [N, channel])."""
+    g = _gen(seed)
+    cnt = torch.randint(cnt_min, cnt_max, (groups,), generator=g, dtype=torch.int64)
+    ids = torch.repeat_interleave(torch.arange(groups), cnt)
+    col = torch.cat([torch.randperm(int(c), generator=g).float() for c in cnt])
+    feat = col.to(device)[:, None].expand(-1, channel).contiguous()
+    return ids, cnt, feat
