@@ -216,7 +216,7 @@ def run_ours(args):
     # The plan was built, and the device synchronised, long before the first reduction:
     # the kernels may read it ahead of their stream wait (TEXB_PLAN_SETTLED).
     torch.cuda.synchronize()
-    plan_flags = _native.PLAN_SETTLED
+    plan_flags = _native.PLAN_SETTLED | (_native.PLAN_NO_SPLIT if data.max_cnt <= _native.NO_SPLIT_MAX_CNT else 0)
 
     def reduce(name):
         st = entry(ops[name], feat.data_ptr(), data.sid.data_ptr(), perm_ptr,
@@ -505,10 +505,11 @@ def other_configs(dev):
         b = algorithmic_bytes(n, c, m)
         res = {"points": n, "channels": c, "segments": m, "note": note}
         torch.cuda.synchronize()  # the plan is complete and the host knows it
+        flags = _native.PLAN_SETTLED | (_native.PLAN_NO_SPLIT if data.max_cnt <= _native.NO_SPLIT_MAX_CNT else 0)
         for name, op in (("sum", _native.OP_SUM), ("mean", _native.OP_MEAN), ("max", _native.OP_MAX)):
             def call(on_stream):
                 st = lib.texb_segment_reduce(op, feat.data_ptr(), data.sid.data_ptr(), perm, data.preSum.data_ptr(),
-                                             _native.PLAN_SETTLED,
+                                             flags,
                                              data.balance.data_ptr(), data.balance.numel(), n, c, m, out.data_ptr(),
                                              arg.data_ptr(), 0, ws.data_ptr(), ws.numel(), on_stream)
                 if st != 0:
@@ -656,7 +657,7 @@ def multi_frame_bench(args, rank, world, dev, barrier):
     ops3 = ("sum", "mean", "max")
     res = {"frames": frames, "points": frames * per_frame, "channels": c, "segments": layout.seg_total,
            "gather": "none (one GPU)" if world == 1 else
-           f"{F._gather_method(layout, None)}: exact-size transfers straight into the rows of the result, "
+           f"{shard.gather_method(c)}: exact-size transfers straight into the rows of the result, "
            "started after each reduction and waited for at the end of the step"}
 
     def timed(step, reps=10):
@@ -689,6 +690,15 @@ def multi_frame_bench(args, rank, world, dev, barrier):
         inbound = int(t.item())
         res["replicated_inbound_bytes_per_gpu"] = inbound
         res["replicated_inbound_GBps_per_gpu"] = round(inbound / (res["ms_per_step_replicated"] * 1e-3) / 1e9, 1)
+    # the transfers alone: one [seg_total, C] result replicated with no reduction beside it
+    ring = shard._ring_for(c, None) if world > 1 else None
+    if ring is not None:
+        def move_only():
+            return ring.gather(ring.acquire(), torch.float32).wait()
+        ms = timed(move_only)
+        one = (layout.seg_total - layout.seg_count) * c * 4
+        res["transfer_only"] = {"ms_per_tensor": round(ms, 4), "inbound_GBps_per_gpu": round(one / (ms * 1e-3) / 1e9, 1),
+                                "note": "pulling the other ranks' rows of one result (slowest rank), nothing else running"}
     # mean and max (+ argmax) from one pass, three tensors replicated instead of four
     ms = timed(lambda: shard.scatter("mean_max", feats, True))
     res["ms_per_step_replicated_mean_max_pair"] = round(ms, 4)
@@ -754,6 +764,7 @@ def multi_frame_bench(args, rank, world, dev, barrier):
                          "checksum-identical on all ranks and equal to the local shard in its rows")
     res["note"] = ("step = sum + mean + max over all 16 frames through the operator API; sharded = outputs stay on the "
                    "GPU that owns the frames, replicated = every result on every GPU")
+    shard.close()
     return res
 
 

@@ -44,6 +44,10 @@ extern "C" {
 #define TEXB_PLAN_HAS_EMPTY 1 /* some segment may have no rows: fill their output rows */
 #define TEXB_PLAN_SETTLED 2   /* the plan arrays were complete, and the host had synchronised
                                  with their stream, before this call (see "Stream order") */
+#define TEXB_PLAN_NO_SPLIT 4  /* every cut of the balance table is a segment start (largest segment
+                                 <= 128 rows, table built with the plan statistics): the reduce is
+                                 then a single launch, nothing is left for a fix-up */
+#define TEXB_PLAN_NO_SPLIT_MAX_CNT 128
 
 /* Library version (major * 100 + minor). */
 int texb_version(void);
@@ -71,7 +75,10 @@ int texb_device_status(int* wait_timeouts, int* bad_indices);
  * "staged" (0 register kernel, 1 cp.async ring, 2 bulk-copy ring),
  * "compensated" (1 = error-free sums), "fixup_pdl", "balanced", "end_cost_x4"
  * (cost of closing a segment in quarter rows, used by texb_plan_balance),
- * "l2_stream_hint" (1 = feature rows are copied with an L2 evict-first policy).
+ * "l2_stream_hint" (1 = feature rows are copied with an L2 evict-first policy),
+ * "chain_inline" (1 = segments that span several CTAs are finished inside the reduce
+ * kernel by the CTA where they end, which looks back over its neighbours' records
+ * with bounded waits; 0 = by a second, dependent launch).
  * Process-wide; returns TEXB_ERR_INVALID_ARGUMENT for unknown keys or values
  * out of range.  texb_tune_get returns the current value or -1. */
 int texb_tune_set(const char* key, int value);
@@ -118,9 +125,17 @@ int texb_plan_build(const void* ids, int id_bytes, int64_t n,
  * run of consecutive pieces, so regions full of tiny segments do not finish
  * later than regions inside one huge segment.  K around 50 times the number
  * of groups in flight (131072 is plenty for a B200) keeps the cut fine enough.
+ * A cut that falls inside a segment is moved forward to the start of the next
+ * segment when that is near.  plan_stats_dev (optional, may be NULL) is the
+ * statistics array that texb_plan_build / texb_unique_fill wrote in the same
+ * stream: when it says that the largest segment has at most 128 rows, every cut
+ * is moved to a segment start, so that no segment is split between two groups;
+ * a caller who knows this on the host (largest segment <= 128 rows and the table
+ * built with the statistics) may then pass TEXB_PLAN_NO_SPLIT to the reduce
+ * entry points.  Without the statistics cuts move by at most 8 positions.
  * No counterpart in the reference, whose grid is one block per segment. */
 int texb_plan_balance(const int32_t* sid, int64_t n, int32_t* balance_out,
-                      int balance_len, void* stream);
+                      int balance_len, const int32_t* plan_stats_dev, void* stream);
 
 /* ---- plan straight from keys (the caller's torch.unique step) ----------------
  * TorchEx's callers obtain unq_inv / unq_cnts with
@@ -377,6 +392,29 @@ int texb_scatter_mean_max_backward(const float* g_mean, const float* g_max,
                                    const int32_t* perm, const int32_t* offsets,
                                    float* g_in, int64_t n, int channel,
                                    int64_t num_segments, void* stream);
+
+/* ---- peer buffers for the multi-GPU driver ---------------------------------------
+ * One process per GPU; a caller that wants every GPU to hold the whole result of a
+ * sharded reduction lets each GPU write its shard into a buffer the other processes
+ * can map, and each GPU then pulls the other shards with plain device-to-device
+ * copies (copy engines over NVLink; no kernel reads peer memory).  Ordering between
+ * the processes -- a shard is complete before it is pulled and pulled before it is
+ * overwritten -- is the caller's job (torchex_b200/frames.py uses small NCCL
+ * collectives).  No counterpart in the reference, which has no multi-GPU code.
+ *   texb_peer_buffer_create : cudaMalloc of `bytes` on the current device (THIS call
+ *     allocates; free with texb_peer_buffer_destroy) and its 64-byte CUDA IPC handle,
+ *     to be sent to the other processes by any host channel;
+ *   texb_peer_buffer_open   : maps a peer's buffer into this process with the current
+ *     device as the accessing device (peer access is enabled lazily); the pointer is
+ *     only ever used as the source of texb_peer_copy; close it before the owner
+ *     destroys the buffer;
+ *   texb_peer_copy          : cudaMemcpyAsync(dst, src, bytes) on `stream`. */
+#define TEXB_PEER_HANDLE_BYTES 64
+int texb_peer_buffer_create(size_t bytes, void** dev_ptr, unsigned char* handle_out);
+int texb_peer_buffer_destroy(void* dev_ptr);
+int texb_peer_buffer_open(const unsigned char* handle, void** peer_ptr);
+int texb_peer_buffer_close(void* peer_ptr);
+int texb_peer_copy(void* dst, const void* src, size_t bytes, void* stream);
 
 #ifdef __cplusplus
 }

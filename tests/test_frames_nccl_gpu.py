@@ -44,8 +44,9 @@ def _worker(rank, world, port, frames, per_frame, channels, out_dir):
         res["sum_local"] = shard.scatter("sum", feats)
         mx, arg = shard.scatter("max", feats)
         res["max_local"], res["arg_local"] = mx, arg
-        for method in ("p2p", "broadcast"):
+        for method in ("dma", "p2p", "broadcast"):
             os.environ["TEXB_GATHER"] = method
+            assert shard.gather_method(channels) == method
             many = shard.scatter_many(("sum", "mean", "max"), feats, replicated=True)
             res[f"{method}_sum"], res[f"{method}_mean"] = many["sum"], many["mean"]
             res[f"{method}_max"], res[f"{method}_arg"] = many["max"]
@@ -53,6 +54,7 @@ def _worker(rank, world, port, frames, per_frame, channels, out_dir):
             res[f"{method}_pair_mean"], res[f"{method}_pair_max"], res[f"{method}_pair_arg"] = pm, px, pa
         torch.cuda.synchronize()
         torch.save({k: v.cpu() for k, v in res.items()}, os.path.join(out_dir, f"rank{rank}.pt"))
+        shard.close()
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -76,7 +78,7 @@ def test_two_gpu_shards_against_the_oracle(tmp_path):
         assert O.within_tolerance(out["sum_local"].numpy(), s64[mine], REL, ABS).all()
         assert np.array_equal(out["max_local"].numpy(), want_max[mine])
         assert np.array_equal(out["arg_local"].numpy(), want_arg[mine])  # global rows through arg_base
-        for method in ("p2p", "broadcast"):
+        for method in ("dma", "p2p", "broadcast"):
             assert O.within_tolerance(out[f"{method}_sum"].numpy(), s64, REL, ABS).all(), method
             assert O.within_tolerance(out[f"{method}_mean"].numpy(), mean64, REL, ABS).all(), method
             assert np.array_equal(out[f"{method}_max"].numpy(), want_max), method

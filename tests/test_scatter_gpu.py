@@ -573,3 +573,75 @@ def test_more_than_2_to_the_31_feature_elements():
         first = (block == block.max(0).values).int().argmax(0)  # lowest row among equal maxima
         assert torch.equal(arg[seg].long(), rows[first])
     assert _native.device_wait_timeouts() == 0 and _native.device_bad_indices() == bad_before
+
+
+@pytest.mark.parametrize("c", [20, 64, 128, 260])
+def test_chains_finished_in_the_kernel_equal_the_fix_up_kernel(c):
+    """Segments that span several CTAs are finished either by the CTA where they end,
+    inside the reduce kernel (look-back over the neighbours' records, the default), or by
+    the separate fix-up launch ("chain_inline" = 0).  Both fold the same pieces in the same
+    order: the results are bit-identical.  Skewed segments with one very long run, so that
+    chains of many CTAs exist; every lane layout (register kernel, 8- and 16-byte lanes,
+    several channel slabs)."""
+    n, m = 400_000, 12_000
+    ids, cnt = W.skewed_ids(n, m, seed=95, giant=150_000)
+    feat = W.features(n, c, 95)
+    data = ScatterData(ids.to(DEV), cnt.to(DEV))
+    x = feat.to(DEV)
+    old = _native.tune_get("chain_inline")
+    got = {}
+    try:
+        for mode in (0, 1):
+            _native.tune_set("chain_inline", mode)
+            for rep in range(3):  # repeated calls reuse the plan's workspace: stale flags must not count
+                s, mean = scatter_sum(x, data), scatter_mean(x, data)
+                mx, arg = scatter_max(x, data)
+                pm, px, pa = scatter_mean_max(x, data)
+            torch.cuda.synchronize()
+            got[mode] = (s, mean, mx, arg, pm, px, pa)
+    finally:
+        _native.tune_set("chain_inline", old)
+    for a, b in zip(got[0], got[1]):
+        assert torch.equal(a, b)
+    s64, c64 = O.spec_scatter_sum_f64(feat, ids, m)
+    assert O.within_tolerance(got[1][0].cpu().numpy(), s64, REL, ABS).all()
+    want_mx, want_arg = O.spec_scatter_max(feat, ids, m)
+    assert np.array_equal(got[1][2].cpu().numpy(), want_mx) and np.array_equal(got[1][3].cpu().numpy(), want_arg)
+    assert _native.device_wait_timeouts() == 0
+
+
+def test_balance_cuts_land_on_segment_starts_when_segments_are_short():
+    """With a largest segment of at most 128 rows every cut of the balance table is moved to
+    a segment start: no segment is split between two groups, and a reduction that is told so
+    (TEXB_PLAN_NO_SPLIT) is a single launch whose result equals the ordinary launch pair."""
+    lib = _native.lib()
+    ids, cnt = W.voxel_frame(200_000, seed=96)
+    n, m, c = ids.numel(), cnt.numel(), 64
+    data = ScatterData(ids.to(DEV), cnt.to(DEV))
+    assert data.max_cnt <= _native.NO_SPLIT_MAX_CNT and data._plan.no_split
+    cuts = data.balance.long()
+    assert int(cuts[0]) == 0 and int(cuts[-1]) == n and bool((cuts[1:] >= cuts[:-1]).all())
+    inner = cuts[(cuts > 0) & (cuts < n)]
+    assert bool((data.sid[inner - 1] != data.sid[inner]).all())
+    feat = W.features(n, c, 96).to(DEV)
+    ws = torch.empty(lib.texb_reduce_workspace_bytes(n, c), dtype=torch.uint8, device=DEV)
+    res = {}
+    for flags in (0, _native.PLAN_NO_SPLIT, _native.PLAN_NO_SPLIT | _native.PLAN_SETTLED):
+        out = torch.full((3, m, c), float("nan"), device=DEV)
+        arg = torch.full((m, c), -7, dtype=torch.int32, device=DEV)
+        for i, op in enumerate((_native.OP_SUM, _native.OP_MEAN, _native.OP_MAX)):
+            st = lib.texb_segment_reduce(op, feat.data_ptr(), data.sid.data_ptr(), data._perm_ptr, data.preSum.data_ptr(),
+                                         flags, data.balance.data_ptr(), data.balance.numel(), n, c, m, out[i].data_ptr(),
+                                         arg.data_ptr(), 0, ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
+            assert st == 0, _native.last_error()
+        res[flags] = (out, arg)
+    for flags in list(res)[1:]:
+        assert torch.equal(res[flags][0], res[0][0]) and torch.equal(res[flags][1], res[0][1])
+    s64, c64 = O.spec_scatter_sum_f64(feat.cpu(), ids, m)
+    assert O.within_tolerance(res[0][0][0].cpu().numpy(), s64, REL, ABS).all()
+    # long segments: cuts move by at most a few positions and the table stays usable
+    ids, cnt = W.skewed_ids(300_000, 9_000, seed=97, giant=50_000)
+    data = ScatterData(ids.to(DEV), cnt.to(DEV))
+    assert data.max_cnt > _native.NO_SPLIT_MAX_CNT and not data._plan.no_split
+    cuts = data.balance.long()
+    assert int(cuts[0]) == 0 and int(cuts[-1]) == 300_000 and bool((cuts[1:] >= cuts[:-1]).all())

@@ -40,7 +40,7 @@ _SIGNATURES = {
                                              _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_int32, _c.c_void_p]),
     "texb_get_pre_sum": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p]),
     "texb_reduce_workspace_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int]),
-    "texb_plan_balance": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_int, _c.c_void_p]),
+    "texb_plan_balance": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_int, _c.c_void_p, _c.c_void_p]),
     "texb_segment_reduce": (_c.c_int, [_c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                        _c.c_int, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int, _c.c_int64,
                                        _c.c_void_p, _c.c_void_p, _c.c_int32, _c.c_void_p, _c.c_size_t,
@@ -70,13 +70,19 @@ _SIGNATURES = {
                                               _c.c_int64, _c.c_int, _c.c_int64, _c.c_void_p]),
     "texb_scatter_max_backward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                              _c.c_int64, _c.c_int, _c.c_int64, _c.c_void_p]),
+    "texb_peer_buffer_create": (_c.c_int, [_c.c_size_t, _c.POINTER(_c.c_void_p), _c.c_void_p]),
+    "texb_peer_buffer_destroy": (_c.c_int, [_c.c_void_p]),
+    "texb_peer_buffer_open": (_c.c_int, [_c.c_void_p, _c.POINTER(_c.c_void_p)]),
+    "texb_peer_buffer_close": (_c.c_int, [_c.c_void_p]),
+    "texb_peer_copy": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
     "texb_scatter_mean_max_backward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                                   _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int, _c.c_int64,
                                                   _c.c_void_p]),
 }
 
 OP_SUM, OP_MEAN, OP_MAX = 0, 1, 2
-PLAN_HAS_EMPTY, PLAN_SETTLED = 1, 2  # bits of the plan_flags argument of the reduce entry points
+PLAN_HAS_EMPTY, PLAN_SETTLED, PLAN_NO_SPLIT = 1, 2, 4  # bits of the plan_flags argument of the reduce entry points
+NO_SPLIT_MAX_CNT = 128  # largest segment for which texb_plan_balance puts every cut on a segment start
 BALANCE_PIECES = 131072  # pieces of the plan's balance table (see texb_plan_balance)
 
 
@@ -93,7 +99,7 @@ def lib() -> ctypes.CDLL:
             path = _build.LIB_PATH
             if not os.path.exists(path):
                 raise RuntimeError(
-                    f"{path} is missing: build it with `python -m torchex_b200.build` "
+                    f"{path} is missing: build it with `python torchex_b200/build.py` "
                     "(there is no CPU or PyTorch fallback for the scatter kernels)")
             handle = ctypes.CDLL(path)
             for name, (res, args) in _SIGNATURES.items():

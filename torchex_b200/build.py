@@ -1,6 +1,7 @@
 """Builds the native code in-tree for sm_100a.
 
-``python -m torchex_b200.build`` writes
+``python torchex_b200/build.py`` (run as a script: importing the package needs the
+libraries this builds) writes
 
 * ``torchex_b200/lib/libtexb_scatter.so`` -- the kernels behind the plain C ABI of
   ``include/texb_scatter.h`` (nvcc; no torch dependency), and
@@ -22,11 +23,14 @@ import sysconfig
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
-LIB_DIR = os.path.join(PKG_DIR, "lib")
+# TEXB_LIB_DIR: another directory to build into and load from (for trying out a build with
+# different -D options beside the regular one); TEXB_NVCC_EXTRA: extra nvcc options for it.
+LIB_DIR = os.environ.get("TEXB_LIB_DIR") or os.path.join(PKG_DIR, "lib")
 OBJ_DIR = os.path.join(LIB_DIR, "obj")
 LIB_PATH = os.path.join(LIB_DIR, "libtexb_scatter.so")
 HEADER = os.path.join(os.path.dirname(PKG_DIR), "include", "texb_scatter.h")
-SOURCES = ["abi.cu", "segment_reduce.cu", "segment_small.cu", "segment_plan.cu", "segment_backward.cu"]
+SOURCES = ["abi.cu", "segment_reduce.cu", "reduce_unit_sum.cu", "reduce_unit_sum_plain.cu", "reduce_unit_max.cu",
+           "reduce_unit_sum_max.cu", "segment_small.cu", "segment_plan.cu", "segment_backward.cu", "peer_copy.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
@@ -79,7 +83,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         path = os.path.join(CSRC, src)
         obj = os.path.join(OBJ_DIR, src[:-3] + ".o")
         if force or _newer(obj, [path] + headers):
-            cmd = [nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-c", "-o", obj, path]
+            cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("TEXB_NVCC_EXTRA", "").split(),
+                   *(["-Xptxas", "-v"] if verbose else []), "-c", "-o", obj, path]
             jobs.append((cmd, src))
     with concurrent.futures.ThreadPoolExecutor(max_workers=max(1, min(len(jobs), os.cpu_count() or 1))) as pool:
         for log in pool.map(lambda j: _run(j[0], "nvcc " + j[1]), jobs):
@@ -91,7 +96,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 def extension_is_stale() -> bool:
-    return _newer(EXT_PATH, [EXT_SOURCE, HEADER, LIB_PATH])
+    # the module links the library dynamically: only its own source and the ABI header matter
+    return _newer(EXT_PATH, [EXT_SOURCE, HEADER])
 
 
 def build_extension(force: bool = False) -> str:

@@ -22,7 +22,7 @@ size_t reduce_pair_workspace_bytes_impl(int64_t, int);
 int segment_reduce_impl(int, const void*, int, const int32_t*, const int32_t*, const int32_t*, int,
                         const int32_t*, int, int64_t, int, int64_t, float*, int32_t*, int32_t, void*,
                         size_t, cudaStream_t, float* out_sum = nullptr);
-int plan_balance_impl(const int32_t*, int64_t, int32_t*, int, cudaStream_t);
+int plan_balance_impl(const int32_t*, int64_t, int32_t*, int, const int32_t*, cudaStream_t);
 size_t unique_workspace_bytes_impl(int64_t);
 int unique_count_impl(const void*, int, int64_t, int64_t, int, int32_t*, int32_t*, int32_t*, void*, size_t,
                       cudaStream_t);
@@ -47,11 +47,17 @@ int max_backward_impl(const float*, const int32_t*, const int32_t*, const int32_
 int mean_max_backward_impl(const float*, const float*, const int32_t*, const int32_t*, const int32_t*,
                            const int32_t*, float*, int64_t, int, int64_t, cudaStream_t);
 
+int peer_buffer_create_impl(size_t, void**, unsigned char*);
+int peer_buffer_destroy_impl(void*);
+int peer_buffer_open_impl(const unsigned char*, void**);
+int peer_buffer_close_impl(void*);
+int peer_copy_impl(void*, const void*, size_t, cudaStream_t);
+
 namespace {
 thread_local char t_error[512] = "";
 
 std::mutex g_tuning_mutex;
-Tuning g_tuning = {0, 2, 1, 1, 1, 5, 0};
+Tuning g_tuning = {0, 2, 1, 1, 1, 5, 0, 0};
 bool g_tuning_env_read = false;
 
 int env_int(const char* name, int fallback) {
@@ -96,6 +102,11 @@ bool set_knob(Tuning& t, const char* key, int value) {
     t.end_cost_x4 = value;
     return true;
   }
+  if (!std::strcmp(key, "chain_inline")) {
+    if (value != 0 && value != 1) return false;
+    t.chain_inline = value;
+    return true;
+  }
   return false;
 }
 
@@ -109,6 +120,7 @@ void read_env_locked() {
   set_knob(g_tuning, "balanced", env_int("TEXB_BALANCED", g_tuning.balanced));
   set_knob(g_tuning, "end_cost_x4", env_int("TEXB_END_COST_X4", g_tuning.end_cost_x4));
   set_knob(g_tuning, "l2_stream_hint", env_int("TEXB_L2_STREAM_HINT", g_tuning.l2_stream_hint));
+  set_knob(g_tuning, "chain_inline", env_int("TEXB_CHAIN_INLINE", g_tuning.chain_inline));
 }
 }  // namespace
 
@@ -161,6 +173,7 @@ int texb_tune_get(const char* key) {
   if (!std::strcmp(key, "balanced")) return t.balanced;
   if (!std::strcmp(key, "end_cost_x4")) return t.end_cost_x4;
   if (!std::strcmp(key, "l2_stream_hint")) return t.l2_stream_hint;
+  if (!std::strcmp(key, "chain_inline")) return t.chain_inline;
   return -1;
 }
 
@@ -196,8 +209,8 @@ size_t texb_reduce_workspace_bytes(int64_t n, int channel) {
 }
 
 int texb_plan_balance(const int32_t* sid, int64_t n, int32_t* balance_out, int balance_len,
-                      void* stream) {
-  return plan_balance_impl(sid, n, balance_out, balance_len, static_cast<cudaStream_t>(stream));
+                      const int32_t* plan_stats_dev, void* stream) {
+  return plan_balance_impl(sid, n, balance_out, balance_len, plan_stats_dev, static_cast<cudaStream_t>(stream));
 }
 
 size_t texb_unique_workspace_bytes(int64_t n) { return unique_workspace_bytes_impl(n); }
@@ -353,6 +366,18 @@ int texb_scatter_mean_max_backward(const float* g_mean, const float* g_max, cons
                                    void* stream) {
   return mean_max_backward_impl(g_mean, g_max, arg, ids, perm, offsets, g_in, n, channel, num_segments,
                                 static_cast<cudaStream_t>(stream));
+}
+
+int texb_peer_buffer_create(size_t bytes, void** dev_ptr, unsigned char* handle_out) {
+  return peer_buffer_create_impl(bytes, dev_ptr, handle_out);
+}
+int texb_peer_buffer_destroy(void* dev_ptr) { return peer_buffer_destroy_impl(dev_ptr); }
+int texb_peer_buffer_open(const unsigned char* handle, void** peer_ptr) {
+  return peer_buffer_open_impl(handle, peer_ptr);
+}
+int texb_peer_buffer_close(void* peer_ptr) { return peer_buffer_close_impl(peer_ptr); }
+int texb_peer_copy(void* dst, const void* src, size_t bytes, void* stream) {
+  return peer_copy_impl(dst, src, bytes, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

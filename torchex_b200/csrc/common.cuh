@@ -25,6 +25,7 @@ struct Tuning {
   int balanced;      // 1: use the plan's balance table to cut the rows by estimated cost
   int end_cost_x4;   // cost of closing a segment, in quarter rows, for that table
   int l2_stream_hint;  // 1: bulk copies of feature rows carry an L2 evict-first policy
+  int chain_inline;    // 1: segments that span CTAs are finished inside the reduce kernel; 0: by the fix-up kernel
 };
 Tuning tuning();
 

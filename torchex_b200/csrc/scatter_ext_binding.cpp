@@ -126,6 +126,7 @@ struct Plan {
   int64_t max_cnt = -1;    // rows of the largest segment, -1 while the host does not know it
   bool has_empty = true;   // false only once the host knows that every segment has rows
   bool settled = false;    // the host has synchronised with the stream since the arrays were built
+  bool no_split = false;   // every cut of the balance table is a segment start (short segments only)
   struct Scratch {
     int64_t channels;
     bool pair;
@@ -134,7 +135,10 @@ struct Plan {
   };
   std::vector<Scratch> scratch_cache;  // one buffer per (channel count, operator kind, stream)
 
-  int flags() const { return (has_empty || num_total == 0 ? TEXB_PLAN_HAS_EMPTY : 0) | (settled ? TEXB_PLAN_SETTLED : 0); }
+  int flags() const {
+    return (has_empty || num_total == 0 ? TEXB_PLAN_HAS_EMPTY : 0) | (settled ? TEXB_PLAN_SETTLED : 0) |
+           (no_split ? TEXB_PLAN_NO_SPLIT : 0);
+  }
   const int32_t* perm_ptr() const { return perm.defined() ? perm.data_ptr<int>() : nullptr; }
 
   // Calls on one stream are ordered, so they can share a buffer; another stream gets its own.
@@ -177,6 +181,58 @@ Plan make_plan(at::Tensor sid, c10::optional<at::Tensor> perm, at::Tensor offset
   return p;
 }
 
+// Builds the segment plan of ScatterData in one call: inspection of the ids (the one
+// synchronisation with the device: sortedness, range, run count), then -- if the ids fit
+// the `m` segments -- the sort (skipped for sorted ids), offsets, statistics and balance
+// table, and an asynchronous copy of the statistics to pinned host memory.  Returns
+//   (is_sorted, id_min, id_max, runs, m, sid, perm | None, offsets, balance, stats_host)
+// with sid .. stats_host None when the ids lie outside [0, m) (the caller raises).
+// m < 0: take the largest id + 1.  Replaces the constructor of the reference class and
+// its getPreSum call (torchex/operator_py/scatter_op.py:8-21, 114-135).
+py::tuple build_plan(const at::Tensor& ids_in, int64_t m, int64_t balance_pieces) {
+  TORCH_CHECK(ids_in.device().is_cuda(), "unq_inv must be a CUDAtensor");
+  TORCH_CHECK(ids_in.scalar_type() == at::kInt || ids_in.scalar_type() == at::kLong, "ids must be int32 or int64");
+  TORCH_CHECK(balance_pieces >= 1, "balance_pieces must be positive");
+  const at::Tensor ids = ids_in.reshape({-1}).contiguous();
+  const int64_t n = ids.numel();
+  const int id_bytes = int(ids.element_size());
+  const c10::cuda::CUDAGuard guard(ids.device());
+  void* stream = stream_of(ids);
+  const auto i32 = ids.options().dtype(at::kInt);
+  at::Tensor stats = at::empty({4}, i32);
+  check_status(texb_ids_inspect(ids.data_ptr(), id_bytes, n, stats.data_ptr<int>(), stream), "texb_ids_inspect");
+  const at::Tensor h = stats.to(at::kCPU);  // the one synchronisation
+  const int32_t* hs = h.data_ptr<int>();
+  const bool is_sorted = hs[0] != 0;
+  const int64_t id_min = hs[1], id_max = hs[2], runs = hs[3];
+  if (m < 0) m = n > 0 ? id_max + 1 : 0;
+  if (n > 0 && (id_min < 0 || id_max >= m))
+    return py::make_tuple(is_sorted, id_min, id_max, runs, m, py::none(), py::none(), py::none(), py::none(), py::none());
+  at::Tensor offsets = at::empty({m + 1}, i32);
+  at::Tensor plan_stats = at::empty({4}, i32);
+  at::Tensor sid, perm;
+  if (is_sorted) {
+    sid = ids.scalar_type() == at::kInt ? ids : at::empty({n}, i32);
+  } else {
+    sid = at::empty({n}, i32);
+    perm = at::empty({n}, i32);
+  }
+  const size_t ws_bytes = texb_plan_workspace_bytes(n, m, is_sorted ? 1 : 0);
+  at::Tensor ws = scratch(ws_bytes, ids);
+  check_status(texb_plan_build(ids.data_ptr(), id_bytes, n, m, is_sorted ? 1 : 0, sid.data_ptr<int>(),
+                               perm.defined() ? perm.data_ptr<int>() : nullptr, offsets.data_ptr<int>(),
+                               plan_stats.data_ptr<int>(), ws.data_ptr(), size_t(ws.numel()), stream),
+               "texb_plan_build");
+  at::Tensor balance = at::empty({balance_pieces + 1}, i32);
+  check_status(texb_plan_balance(sid.data_ptr<int>(), n, balance.data_ptr<int>(), int(balance.numel()),
+                                 plan_stats.data_ptr<int>(), stream),
+               "texb_plan_balance");
+  at::Tensor stats_host = at::empty({4}, at::TensorOptions().dtype(at::kInt).pinned_memory(true));
+  stats_host.copy_(plan_stats, /*non_blocking=*/true);
+  return py::make_tuple(is_sorted, id_min, id_max, runs, m, sid, perm.defined() ? py::cast(perm) : py::object(py::none()),
+                        offsets, balance, stats_host);
+}
+
 // feats as the kernels take them: contiguous fp32, or bf16 where the bf16 kernel covers the shape.
 at::Tensor prepare_feats(const Plan& p, const at::Tensor& feats, bool pair) {
   TORCH_CHECK(feats.device().is_cuda(), "feats must be a CUDAtensor ");
@@ -197,18 +253,31 @@ at::Tensor prepare_feats(const Plan& p, const at::Tensor& feats, bool pair) {
   return f;
 }
 
+// An output the caller provides (e.g. a buffer that other processes map) instead of a fresh tensor.
+at::Tensor output_rows(const c10::optional<at::Tensor>& given, const at::Tensor& feats, int64_t m, int64_t c,
+                       at::ScalarType dtype, const char* name) {
+  if (!given.has_value() || !given->defined()) return at::empty({m, c}, feats.options().dtype(dtype));
+  const at::Tensor& t = *given;
+  TORCH_CHECK(t.device() == feats.device(), name, " must be on the device of feats");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous ");
+  TORCH_CHECK(t.scalar_type() == dtype, name, " must have dtype ", dtype, ", got ", t.scalar_type());
+  TORCH_CHECK(t.dim() == 2 && t.size(0) == m && t.size(1) == c, name, " must be [num_unq, channel]");
+  return t;
+}
+
 std::tuple<at::Tensor, c10::optional<at::Tensor>> reduce(Plan& p, int op, const at::Tensor& feats_in,
-                                                         int64_t arg_base) {
+                                                         int64_t arg_base, c10::optional<at::Tensor> out_given,
+                                                         c10::optional<at::Tensor> arg_given) {
   TORCH_CHECK(op == TEXB_OP_SUM || op == TEXB_OP_MEAN || op == TEXB_OP_MAX, "unknown reduce op ", op);
   const at::Tensor feats = prepare_feats(p, feats_in, false);
   const int64_t n = feats.size(0), c = feats.size(1), m = p.num_segments;
   const c10::cuda::CUDAGuard guard(feats.device());
   void* stream = stream_of(feats);
-  at::Tensor out = at::empty({m, c}, feats.options().dtype(at::kFloat));
+  at::Tensor out = output_rows(out_given, feats, m, c, at::kFloat, "out");
   c10::optional<at::Tensor> arg;
   int32_t* arg_ptr = nullptr;
   if (op == TEXB_OP_MAX) {
-    arg = at::empty({m, c}, feats.options().dtype(at::kInt));
+    arg = output_rows(arg_given, feats, m, c, at::kInt, "arg");
     arg_ptr = arg->data_ptr<int>();
   }
   const bool bf16 = feats.scalar_type() == at::kBFloat16;
@@ -236,15 +305,17 @@ std::tuple<at::Tensor, c10::optional<at::Tensor>> reduce(Plan& p, int op, const 
 }
 
 std::tuple<at::Tensor, at::Tensor, at::Tensor> reduce_pair(Plan& p, int op, const at::Tensor& feats_in,
-                                                           int64_t arg_base) {
+                                                           int64_t arg_base, c10::optional<at::Tensor> sum_given,
+                                                           c10::optional<at::Tensor> max_given,
+                                                           c10::optional<at::Tensor> arg_given) {
   TORCH_CHECK(op == TEXB_OP_SUM || op == TEXB_OP_MEAN, "the two-output reduction pairs the maximum with sum or mean");
   const at::Tensor feats = prepare_feats(p, feats_in, true);
   const int64_t n = feats.size(0), c = feats.size(1), m = p.num_segments;
   const c10::cuda::CUDAGuard guard(feats.device());
   void* stream = stream_of(feats);
-  at::Tensor out_sum = at::empty({m, c}, feats.options().dtype(at::kFloat));
-  at::Tensor out_max = at::empty({m, c}, feats.options().dtype(at::kFloat));
-  at::Tensor arg = at::empty({m, c}, feats.options().dtype(at::kInt));
+  at::Tensor out_sum = output_rows(sum_given, feats, m, c, at::kFloat, "out_sum");
+  at::Tensor out_max = output_rows(max_given, feats, m, c, at::kFloat, "out_max");
+  at::Tensor arg = output_rows(arg_given, feats, m, c, at::kInt, "arg");
   at::Tensor& ws = p.workspace(c, true, stream, texb_reduce_pair_workspace_bytes(n, int(c)));
   check_status(texb_segment_reduce_pair(op, feats.data_ptr(), int(feats.element_size()), p.sid.data_ptr<int>(),
                                         p.perm_ptr(), p.offsets.data_ptr<int>(), p.flags(),
@@ -333,12 +404,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readwrite("max_cnt", &Plan::max_cnt)
       .def_readwrite("has_empty", &Plan::has_empty)
       .def_readwrite("settled", &Plan::settled)
+      .def_readwrite("no_split", &Plan::no_split)
       .def("scratch_buffers", [](const Plan& p) { return p.scratch_cache.size(); },
            "number of reduce workspaces the plan holds (one per channel count, operator kind and stream)");
   m.def("make_plan", &make_plan, py::arg("sid"), py::arg("perm"), py::arg("offsets"), py::arg("balance"),
         py::arg("num_segments"), py::arg("has_empty"), py::arg("max_cnt"), py::arg("settled"));
-  m.def("reduce", &reduce, py::arg("plan"), py::arg("op"), py::arg("feats"), py::arg("arg_base") = 0);
-  m.def("reduce_pair", &reduce_pair, py::arg("plan"), py::arg("op"), py::arg("feats"), py::arg("arg_base") = 0);
+  m.def("build_plan", &build_plan, py::arg("ids"), py::arg("num_segments"), py::arg("balance_pieces"));
+  m.def("reduce", &reduce, py::arg("plan"), py::arg("op"), py::arg("feats"), py::arg("arg_base") = 0,
+        py::arg("out") = c10::nullopt, py::arg("arg") = c10::nullopt);
+  m.def("reduce_pair", &reduce_pair, py::arg("plan"), py::arg("op"), py::arg("feats"), py::arg("arg_base") = 0,
+        py::arg("out_sum") = c10::nullopt, py::arg("out_max") = c10::nullopt, py::arg("arg") = c10::nullopt);
   m.def("broadcast_back", &broadcast_back, py::arg("plan"), py::arg("mode"), py::arg("g"),
         py::arg("arg") = c10::nullopt);
   m.def("mean_max_backward", &mean_max_backward);

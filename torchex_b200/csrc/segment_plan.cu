@@ -154,8 +154,20 @@ __global__ void plan_stats_kernel(const int32_t* __restrict__ offsets, int m, in
 // as sid[p] - sid[0] (exact for dense ids, an over-estimate across gaps, always
 // non-decreasing).  table[k] is the first position whose cost reaches k / K of
 // the total, so consecutive entries cut the rows into K pieces of equal cost.
+//
+// Cuts that fall inside a segment are then moved forward to the start of the next
+// segment when that is near: at most kSnapFar positions away if the plan's largest
+// segment has at most kSnapFar rows (then EVERY cut lands on a segment start, no
+// segment is ever split between two groups of lanes, and the reduce needs neither
+// its stitching nor its fix-up launch: TEXB_PLAN_NO_SPLIT), else at most kSnapNear
+// positions (fewer split segments at no visible cost in balance).  Moving cuts
+// forward keeps the table non-decreasing.
+constexpr int kSnapFar = 128;
+constexpr int kSnapNear = 8;
+
 __global__ void balance_table_kernel(const int32_t* __restrict__ sid, int n, int end_cost_x4,
-                                     int32_t* __restrict__ table, int K) {
+                                     int32_t* __restrict__ table, int K,
+                                     const int32_t* __restrict__ plan_stats) {
   const int k = blockIdx.x * blockDim.x + threadIdx.x;
   if (k > K) return;
   if (k == 0) { table[0] = 0; return; }
@@ -170,6 +182,22 @@ __global__ void balance_table_kernel(const int32_t* __restrict__ sid, int n, int
     const int mid = lo + ((hi - lo) >> 1);
     const long long c = 4LL * mid + (long long)end_cost_x4 * (__ldg(sid + mid) - first);
     if (c < target) lo = mid; else hi = mid;
+  }
+  // hi in [1, n]: move it to the next segment start if it lies inside a segment
+  if (hi < n) {
+    const int s_here = __ldg(sid + hi);
+    if (__ldg(sid + hi - 1) == s_here) {
+      const int window = (plan_stats != nullptr && plan_stats[0] <= kSnapFar) ? kSnapFar : kSnapNear;
+      const int far = min(hi + window, n);  // the segment ends at or before `far`, or the cut stays
+      if (far == n || __ldg(sid + far) != s_here) {
+        int a = hi, b = far;  // sid[a] == s_here; b == n or sid[b] != s_here: first position past the segment
+        while (b - a > 1) {
+          const int mid = a + ((b - a) >> 1);
+          if (__ldg(sid + mid) == s_here) a = mid; else b = mid;
+        }
+        hi = b;
+      }
+    }
   }
   table[k] = hi;
 }
@@ -676,7 +704,8 @@ int unique_fill_impl(const int32_t* sorted_keys, const int32_t* perm, int64_t n,
   return check_launch("plan_stats_kernel");
 }
 
-int plan_balance_impl(const int32_t* sid, int64_t n, int32_t* table, int table_len, cudaStream_t stream) {
+int plan_balance_impl(const int32_t* sid, int64_t n, int32_t* table, int table_len, const int32_t* plan_stats,
+                      cudaStream_t stream) {
   if (n < 0 || !table || table_len < 2 || (n > 0 && !sid))
     return fail(TEXB_ERR_INVALID_ARGUMENT, "plan_balance: bad pointer or size");
   if (n > INT_MAX - 65536) return fail(TEXB_ERR_UNSUPPORTED, "plan_balance: n must be below 2^31 - 65536");
@@ -687,7 +716,7 @@ int plan_balance_impl(const int32_t* sid, int64_t n, int32_t* table, int table_l
     return TEXB_OK;
   }
   balance_table_kernel<<<unsigned(ceil_div(table_len, 256)), 256, 0, stream>>>(
-      sid, int(n), tuning().end_cost_x4, table, K);
+      sid, int(n), tuning().end_cost_x4, table, K, plan_stats);
   return check_launch("balance_table_kernel");
 }
 

@@ -101,7 +101,10 @@ def _gather_method(layout: ShardLayout, group) -> str:
     """How the shards travel.  NCCL moves exact sizes straight into the rows of the result
     (grouped point-to-point transfers: every pair of GPUs has its own full-bandwidth path
     through the NVSwitch); other backends (gloo on CPU ranks) get one equal-size all-gather
-    of padded shards.  TEXB_GATHER = p2p | broadcast | padded overrides the choice."""
+    of padded shards.  ``FrameShard`` with the CUDA operators prefers "dma": the reduce
+    writes each shard into a buffer the other ranks map, and every rank pulls the others'
+    shards with device-to-device copies (``peer_ring.PeerRing``).
+    TEXB_GATHER = dma | p2p | broadcast | padded overrides the choice."""
     forced = os.environ.get("TEXB_GATHER", "")
     if forced in ("p2p", "broadcast", "padded"):
         if forced == "broadcast" and min(layout.seg_counts_all) == 0:
@@ -183,47 +186,100 @@ class FrameShard:
             make_data = ScatterData
         self.data = make_data(ids, cnts)
         self._reduce = reduce or _cuda_reduce
+        self._rings = {}
+
+    # ---- replicated results through the peer ring (CUDA operators on NCCL ranks) -----------
+
+    def _ring_for(self, channels: int, group):
+        """The ring of peer-mapped buffers for results of ``channels`` columns, or None when
+        shards travel through the process group instead.  Created collectively on first use."""
+        if self._reduce is not _cuda_reduce or self.layout.world_size == 1:
+            return None
+        forced = os.environ.get("TEXB_GATHER", "")
+        if forced not in ("", "dma") or dist.get_backend(group) != "nccl":
+            return None  # (with "dma" forced on another backend _gather_method's fallback applies)
+        key = (channels, group)
+        if key not in self._rings:
+            from .peer_ring import PeerRing
+            try:
+                self._rings[key] = PeerRing(self.layout.seg_counts_all, self.layout.rank, channels, self.device, group)
+            except RuntimeError:
+                if forced == "dma":
+                    raise
+                self._rings[key] = None  # buffers cannot be shared on this box: NCCL transfers instead
+            # every rank must take the same path
+            ok = torch.tensor([0 if self._rings[key] is None else 1], device=self.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) == 0 and self._rings[key] is not None:
+                self._rings[key].close()
+                self._rings[key] = None
+        return self._rings[key]
+
+    def _replicated_start(self, op: str, feats: torch.Tensor, group):
+        """Launches the reduction and starts moving its result(s); returns the pending
+        gathers (objects with ``wait()``), one per result tensor."""
+        ring = self._ring_for(feats.shape[1], group)
+        if ring is None:
+            res = self._reduce(op, feats, self.data, self.layout.row_base)
+            parts = res if isinstance(res, tuple) else (res,)
+            return [gather_shards_async(t, self.layout, group) for t in parts]
+        kinds = {"sum": (torch.float32,), "mean": (torch.float32,), "max": (torch.float32, torch.int32),
+                 "mean_max": (torch.float32, torch.float32, torch.int32)}[op]
+        slots = [ring.acquire() for _ in kinds]
+        views = [ring.view(s, k) for s, k in zip(slots, kinds)]
+        _cuda_reduce(op, feats, self.data, self.layout.row_base, views)   # the kernels write into the ring
+        return [ring.gather(s, k) for s, k in zip(slots, kinds)]
+
+    def gather_method(self, channels: int, group=None) -> str:
+        """How a replicated result of ``channels`` columns travels: "dma", "p2p", "broadcast" or "padded"."""
+        if self.layout.world_size == 1:
+            return "none"
+        return "dma" if self._ring_for(channels, group) is not None else _gather_method(self.layout, group)
+
+    def close(self) -> None:
+        """Collective: releases the peer-mapped buffers (if any were created)."""
+        for ring in self._rings.values():
+            if ring is not None:
+                ring.close()
+        self._rings = {}
 
     def scatter(self, op: str, feats: torch.Tensor, replicated: bool = False, group=None):
         """Reduces this rank's points.  Returns the shard's ``[seg_count, C]``
         result (for ``max`` also ``arg`` holding GLOBAL row numbers; for
         ``mean_max`` the triple ``(mean, max, arg)``), or with
         ``replicated=True`` the full ``[seg_total, C]`` tensors on every rank."""
-        res = self._reduce(op, feats, self.data, self.layout.row_base)
-        if not replicated:
-            return res
-        if isinstance(res, tuple):
-            pending = [gather_shards_async(t, self.layout, group) for t in res]
-            return tuple(p.wait() for p in pending)
-        return gather_shards(res, self.layout, group)
+        if not replicated or self.layout.world_size == 1:
+            return self._reduce(op, feats, self.data, self.layout.row_base)
+        done = tuple(p.wait() for p in self._replicated_start(op, feats, group))
+        return done if len(done) > 1 else done[0]
 
     def scatter_many(self, ops: Sequence[str], feats: torch.Tensor, replicated: bool = False, group=None):
         """Several reductions of the same points, e.g. ``("sum", "mean", "max")``; returns
-        a dict op -> result as ``scatter`` gives it.  With ``replicated=True`` the gather
+        a dict op -> result as ``scatter`` gives it.  With ``replicated=True`` the transfer
         of each result is started as soon as its reduction has been launched and only
-        waited for at the end, so the transfer of reduction k runs under reduction k + 1."""
-        if not replicated:
+        waited for at the end, so the bytes of reduction k move under reduction k + 1."""
+        if not replicated or self.layout.world_size == 1:
             return {op: self._reduce(op, feats, self.data, self.layout.row_base) for op in ops}
-        pending = {}
-        for op in ops:
-            res = self._reduce(op, feats, self.data, self.layout.row_base)
-            parts = res if isinstance(res, tuple) else (res,)
-            pending[op] = (isinstance(res, tuple), [gather_shards_async(t, self.layout, group) for t in parts])
+        pending = {op: self._replicated_start(op, feats, group) for op in ops}
         out = {}
-        for op, (is_tuple, parts) in pending.items():
+        for op, parts in pending.items():
             done = tuple(p.wait() for p in parts)
-            out[op] = done if is_tuple else done[0]
+            out[op] = done if len(done) > 1 else done[0]
         return out
 
 
-def _cuda_reduce(op: str, feats: torch.Tensor, data, row_base: int = 0):
+def _cuda_reduce(op: str, feats: torch.Tensor, data, row_base: int = 0, outputs=None):
     """The CUDA operators; for ``max`` the kernel itself reports rows as
-    ``row_base + local row`` (global rows of the batch)."""
-    from .operator_py import scatter_mean, scatter_sum
+    ``row_base + local row`` (global rows of the batch).  ``outputs``: tensors the
+    kernels write into instead of fresh ones (one per result, in result order)."""
     from .operator_py.scatter_op import _reduce, _reduce_pair
     from . import _native
+    o = list(outputs) if outputs is not None else [None, None, None]
     if op == "mean_max":
-        return _reduce_pair(_native.OP_MEAN, feats, data, arg_base=row_base)
+        return _reduce_pair(_native.OP_MEAN, feats, data, arg_base=row_base, out_sum=o[0], out_max=o[1], arg=o[2])
     if op == "max":
-        return _reduce(_native.OP_MAX, feats, data, want_arg=True, arg_base=row_base)
-    return {"sum": scatter_sum, "mean": scatter_mean}[op](feats, data)
+        return _reduce(_native.OP_MAX, feats, data, want_arg=True, arg_base=row_base, out=o[0], arg=o[1])
+    if outputs is None:  # the public operators: autograd works through a sharded sum / mean
+        from .operator_py import scatter_mean, scatter_sum
+        return {"sum": scatter_sum, "mean": scatter_mean}[op](feats, data)
+    return _reduce({"sum": _native.OP_SUM, "mean": _native.OP_MEAN}[op], feats, data, want_arg=False, out=o[0])[0]

@@ -136,6 +136,9 @@ class ScatterData:
         plan.max_cnt = max_cnt
         plan.has_empty = bool(self._has_empty)
         plan.settled = True
+        # the balance table was built with these statistics: with short segments only, all of
+        # its cuts are segment starts and a reduction is a single launch
+        plan.no_split = max_cnt <= _native.NO_SPLIT_MAX_CNT
 
     def _watch_stats(self, plan_stats: torch.Tensor) -> None:
         host = torch.empty(4, dtype=torch.int32, pin_memory=True)
@@ -221,7 +224,8 @@ class ScatterData:
                           "texb_plan_build")
             self.balance = torch.empty(_native.BALANCE_PIECES + 1, dtype=torch.int32, device=dev)
             _native.check(lib.texb_plan_balance(self.sid.data_ptr(), n, self.balance.data_ptr(),
-                                                self.balance.numel(), _stream()), "texb_plan_balance")
+                                                self.balance.numel(), plan_stats.data_ptr(), _stream()),
+                          "texb_plan_balance")
             if ids.dtype == torch.int32:
                 self.unq_inv = ids
             elif self.is_sorted:
@@ -274,7 +278,8 @@ def _plan_from_keys(cls, keys: torch.Tensor):
         self.is_sorted = bool(is_sorted)
         self.balance = torch.empty(_native.BALANCE_PIECES + 1, dtype=torch.int32, device=dev)
         _native.check(lib.texb_plan_balance(self.sid.data_ptr(), n, self.balance.data_ptr(),
-                                            self.balance.numel(), _stream()), "texb_plan_balance")
+                                            self.balance.numel(), plan_stats.data_ptr(), _stream()),
+                      "texb_plan_balance")
         self._has_empty = False  # dense ids: every segment has rows
         self._watch_stats(plan_stats)  # max_cnt reaches the host asynchronously
     self.num_unq = m
@@ -385,19 +390,21 @@ def gather_back(values: torch.Tensor, data: ScatterData) -> torch.Tensor:
     return _broadcast_back("sum", data, values, None)
 
 
-def _reduce(op: int, feats: torch.Tensor, data: ScatterData, want_arg: bool, arg_base: int = 0):
-    """One trip into the compiled module: it checks ``feats``, allocates the outputs,
-    picks the kernel path and launches on the current stream of ``feats``' device."""
+def _reduce(op: int, feats: torch.Tensor, data: ScatterData, want_arg: bool, arg_base: int = 0, out=None, arg=None):
+    """One trip into the compiled module: it checks ``feats``, allocates the outputs
+    (unless ``out`` / ``arg`` are given), picks the kernel path and launches on the
+    current stream of ``feats``' device."""
     if data._pending is not None:
         data._poll()
-    return _ext.reduce(data._plan, op, feats, arg_base)
+    return _ext.reduce(data._plan, op, feats, arg_base, out, arg)
 
 
-def _reduce_pair(op: int, feats: torch.Tensor, data: ScatterData, arg_base: int = 0):
+def _reduce_pair(op: int, feats: torch.Tensor, data: ScatterData, arg_base: int = 0, out_sum=None, out_max=None,
+                 arg=None):
     """(sum or mean, max, arg) of the same rows from one pass over ``feats``."""
     if data._pending is not None:
         data._poll()
-    return _ext.reduce_pair(data._plan, op, feats, arg_base)
+    return _ext.reduce_pair(data._plan, op, feats, arg_base, out_sum, out_max, arg)
 
 
 _BACK_MODE = {"sum": _native.OP_SUM, "mean": _native.OP_MEAN, "max": _native.OP_MAX}

@@ -1,0 +1,162 @@
+"""Shards pulled from the other GPUs with DMA copies (one process per GPU).
+
+``frames.gather_shards`` can move the shards with NCCL point-to-point transfers; on an
+NVSwitch box a plain device-to-device copy between two GPUs is faster than that and
+uses no SM.  ``PeerRing`` gives every rank a ring of buffer slots that the other
+ranks map through CUDA IPC (``texb_peer_buffer_*`` of the C ABI).  A replicated
+gather of one result then is:
+
+1. the reduce kernels write this rank's shard straight into a slot of its ring;
+2. a one-element NCCL all-reduce on the copy stream: every rank's shard is complete;
+3. this rank pulls the other ranks' shards out of their rings into the row ranges of
+   its result with ``texb_peer_copy`` (``cudaMemcpyAsync``, copy engines); its own shard
+   is copied into place on a third stream at the same time;
+4. a second one-element all-reduce: every rank has finished pulling, the slot is free.
+
+Steps 2-4 run on a side stream, so the next reduction proceeds on the main stream
+while the bytes move.  No kernel reads another GPU's memory; nothing is multicast.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from . import _native
+
+
+class _RawCuda:
+    """Device memory owned by someone else, described the way ``torch.as_tensor`` accepts."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PendingPull:
+    """Result of ``PeerRing.gather``: ``wait()`` makes the current stream wait for the
+    copies and returns the replicated tensor."""
+
+    def __init__(self, out: torch.Tensor, done):
+        self.out, self._done = out, list(done)
+
+    def wait(self) -> torch.Tensor:
+        for ev in self._done:
+            torch.cuda.current_stream(self.out.device).wait_event(ev)
+        self._done = []
+        return self.out
+
+
+class PeerRing:
+    """``slots`` buffers of ``slot_rows x channels`` 4-byte words on this rank, mapped by
+    every other rank of ``group``.  All ranks must construct it collectively with the same
+    arguments, use the slots in the same order and ``close()`` it collectively."""
+
+    def __init__(self, seg_counts_all: Sequence[int], rank: int, channels: int, device, group=None, slots: int = 8):
+        self.rank, self.world = rank, len(seg_counts_all)
+        self.counts = [int(v) for v in seg_counts_all]
+        self.channels, self.device, self.group, self.slots = channels, torch.device(device), group, slots
+        self.slot_bytes = (max(self.counts + [1]) * channels * 4 + 255) // 256 * 256
+        self._lib = _native.lib()
+        self._ptr = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(self.device):
+            _native.check(self._lib.texb_peer_buffer_create(self.slot_bytes * slots, ctypes.byref(self._ptr), handle),
+                          "texb_peer_buffer_create")
+            handles: List[Optional[bytes]] = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            self._peers: List[Optional[int]] = [None] * self.world
+            for r, h in enumerate(handles):
+                if r == rank:
+                    continue
+                p = ctypes.c_void_p()
+                buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                _native.check(self._lib.texb_peer_buffer_open(buf, ctypes.byref(p)), "texb_peer_buffer_open")
+                self._peers[r] = p.value
+            self._local = torch.as_tensor(_RawCuda(self._ptr.value, self.slot_bytes * slots), device=self.device)
+            self._stream = torch.cuda.Stream(self.device)        # handshakes and pulls from the peers
+            self._own_stream = torch.cuda.Stream(self.device)    # this rank's own shard, copied beside them
+            self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self._free = [None] * slots   # event: every rank has pulled what the slot held
+        self._next = 0
+        self._closed = False
+
+    # ---- slots -------------------------------------------------------------------
+
+    def acquire(self) -> int:
+        """Next slot of the ring; the current stream waits until the previous shard held
+        there has been pulled by every rank."""
+        slot = self._next
+        self._next = (self._next + 1) % self.slots
+        if self._free[slot] is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._free[slot])
+        return slot
+
+    def view(self, slot: int, dtype: torch.dtype) -> torch.Tensor:
+        """This rank's ``[seg_count, channels]`` shard inside ``slot``, as a tensor the reduce writes into."""
+        rows = self.counts[self.rank]
+        raw = self._local[slot * self.slot_bytes: slot * self.slot_bytes + rows * self.channels * 4]
+        return raw.view(dtype).view(rows, self.channels)
+
+    # ---- the gather ----------------------------------------------------------------
+
+    def gather(self, slot: int, dtype: torch.dtype) -> PendingPull:
+        """Starts pulling every rank's shard of ``slot`` into a new ``[seg_total, channels]``
+        tensor.  Call it after the kernels that fill this rank's shard have been launched on
+        the current stream."""
+        main = torch.cuda.current_stream(self.device)
+        out = torch.empty((sum(self.counts), self.channels), dtype=dtype, device=self.device)
+        row, offsets = 0, []
+        for cnt in self.counts:
+            offsets.append(row)
+            row += cnt
+        row_bytes = self.channels * 4
+
+        def copy(r, stream):
+            nbytes = self.counts[r] * row_bytes
+            if nbytes:
+                src = (self._ptr.value if r == self.rank else self._peers[r]) + slot * self.slot_bytes
+                _native.check(self._lib.texb_peer_copy(out.data_ptr() + offsets[r] * row_bytes, src, nbytes,
+                                                       stream.cuda_stream), "texb_peer_copy")
+
+        # this rank's own shard: a local copy on a stream of its own, beside the pulls
+        own = self._own_stream
+        own.wait_stream(main)
+        copy(self.rank, own)
+        own_done = torch.cuda.Event()
+        own_done.record(own)
+        side = self._stream
+        side.wait_stream(main)                      # this rank's shard is complete ...
+        with torch.cuda.stream(side):
+            dist.all_reduce(self._token, group=self.group)   # ... and so is everyone else's
+            for step in range(1, self.world):       # start with the next rank, so that not everyone pulls from rank 0 first
+                copy((self.rank + step) % self.world, side)
+            done = torch.cuda.Event()
+            done.record(side)
+            side.wait_event(own_done)               # the slot is only free once the local copy has read it too
+            dist.all_reduce(self._token, group=self.group)   # every rank has pulled: the slot may be refilled
+            free = torch.cuda.Event()
+            free.record(side)
+            self._free[slot] = free
+        out.record_stream(side)
+        out.record_stream(own)
+        return PendingPull(out, (done, own_done))
+
+    # ---- teardown --------------------------------------------------------------------
+
+    def close(self) -> None:
+        """Collective: unmaps the peers' buffers, waits for everyone, frees this rank's buffer."""
+        if self._closed:
+            return
+        self._closed = True
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            for r, p in enumerate(self._peers):
+                if p is not None:
+                    self._lib.texb_peer_buffer_close(ctypes.c_void_p(p))
+                    self._peers[r] = None
+            dist.barrier(group=self.group)
+            self._local = None
+            self._lib.texb_peer_buffer_destroy(self._ptr)
+            self._ptr = ctypes.c_void_p()

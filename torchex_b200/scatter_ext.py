@@ -27,7 +27,7 @@ def _load():
     path = _build.EXT_PATH
     if not os.path.exists(path) or not os.path.exists(_build.LIB_PATH):
         raise ImportError(
-            f"{path} is missing: build it with `python -m torchex_b200.build` "
+            f"{path} is missing: build it with `python torchex_b200/build.py` "
             "(there is no CPU or PyTorch fallback for the scatter kernels)")
     spec = importlib.util.spec_from_file_location(_build.EXT_NAME, path)
     module = importlib.util.module_from_spec(spec)
