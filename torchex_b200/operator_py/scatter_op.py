@@ -180,59 +180,35 @@ class ScatterData:
         self._build(unq_inv, int(self.unq_cnts.shape[0]))
 
     def _build(self, unq_inv: torch.Tensor, m) -> None:
-        """Builds the plan for ``unq_inv`` with ``m`` segments (``None``: the largest id + 1)."""
+        """Builds the plan for ``unq_inv`` with ``m`` segments (``None``: the largest id + 1):
+        one call into the compiled module, which inspects the ids (the one synchronisation),
+        sorts them if they are not sorted, and derives offsets, statistics and balance table."""
         if not unq_inv.is_cuda:
             raise RuntimeError("unq_inv must be a CUDAtensor")
         ids = unq_inv.reshape(-1)
         if ids.dtype not in (torch.int32, torch.int64):
             ids = ids.long()
         ids = ids.contiguous()
-        n = ids.numel()
-        dev = ids.device
-        lib = _native.lib()
-        id_bytes = ids.element_size()
-
-        with _on_device(dev):
-            stats = torch.empty(4, dtype=torch.int32, device=dev)
-            _native.check(lib.texb_ids_inspect(ids.data_ptr(), id_bytes, n, stats.data_ptr(), _stream()),
-                          "texb_ids_inspect")
-            is_sorted, id_min, id_max, runs = stats.tolist()  # the one synchronisation
-            if m is None:
-                m = id_max + 1 if n > 0 else 0
-            if n > 0 and (id_min < 0 or id_max >= m):
-                raise ValueError(f"unq_inv holds ids in [{id_min}, {id_max}] but unq_cnts "
-                                 f"describes {m} segments")
-            self.is_sorted = bool(is_sorted)
-            # sorted ids: as many runs as segments means no segment is empty; unsorted ids:
-            # known once the plan statistics have reached the host
-            self._has_empty = (runs != m) if self.is_sorted else None
-            self.preSum = torch.empty(m + 1, dtype=torch.int32, device=dev)
-            plan_stats = torch.empty(4, dtype=torch.int32, device=dev)
-            if self.is_sorted:
-                self.perm = None
-                self.sid = ids if ids.dtype == torch.int32 else torch.empty(n, dtype=torch.int32, device=dev)
-                ws = _scratch(lib.texb_plan_workspace_bytes(n, m, 1), dev)
-                perm_ptr = None
-            else:
-                self.sid = torch.empty(n, dtype=torch.int32, device=dev)
-                self.perm = torch.empty(n, dtype=torch.int32, device=dev)
-                ws = _scratch(lib.texb_plan_workspace_bytes(n, m, 0), dev)
-                perm_ptr = self.perm.data_ptr()
-            _native.check(lib.texb_plan_build(ids.data_ptr(), id_bytes, n, m, int(self.is_sorted),
-                                              self.sid.data_ptr(), perm_ptr, self.preSum.data_ptr(),
-                                              plan_stats.data_ptr(), ws.data_ptr(), ws.numel(), _stream()),
-                          "texb_plan_build")
-            self.balance = torch.empty(_native.BALANCE_PIECES + 1, dtype=torch.int32, device=dev)
-            _native.check(lib.texb_plan_balance(self.sid.data_ptr(), n, self.balance.data_ptr(),
-                                                self.balance.numel(), plan_stats.data_ptr(), _stream()),
-                          "texb_plan_balance")
-            if ids.dtype == torch.int32:
-                self.unq_inv = ids
-            elif self.is_sorted:
-                self.unq_inv = self.sid
-            else:
-                self._ids64 = ids  # narrowed to int32 when ``unq_inv`` is first read
-            self._watch_stats(plan_stats)
+        (is_sorted, id_min, id_max, runs, m, sid, perm, offsets, balance, stats_host) = _ext.build_plan(
+            ids, -1 if m is None else int(m), _native.BALANCE_PIECES)
+        if sid is None:
+            raise ValueError(f"unq_inv holds ids in [{id_min}, {id_max}] but unq_cnts "
+                             f"describes {m} segments")
+        self.is_sorted = bool(is_sorted)
+        # sorted ids: as many runs as segments means no segment is empty; unsorted ids:
+        # known once the plan statistics have reached the host
+        self._has_empty = (runs != m) if self.is_sorted else None
+        self.sid, self.perm, self.preSum, self.balance = sid, perm, offsets, balance
+        if ids.dtype == torch.int32:
+            self.unq_inv = ids
+        elif self.is_sorted:
+            self.unq_inv = self.sid
+        else:
+            self._ids64 = ids  # narrowed to int32 when ``unq_inv`` is first read
+        with _on_device(ids.device):
+            done = torch.cuda.Event()
+            done.record()
+        self._pending = (stats_host, done)
         self.num_unq = m
         self._perm_ptr = None if self.perm is None else self.perm.data_ptr()
         self._plan = _ext.make_plan(self.sid, self.perm, self.preSum, self.balance, m,

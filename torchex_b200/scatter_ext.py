@@ -42,6 +42,7 @@ max = native.max  # noqa: A001
 getPreSum = native.getPreSum
 Plan = native.Plan
 make_plan = native.make_plan
+build_plan = native.build_plan
 reduce = native.reduce
 reduce_pair = native.reduce_pair
 broadcast_back = native.broadcast_back
