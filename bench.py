@@ -124,7 +124,7 @@ class ClockSampler(threading.Thread):
 def headline_workload():
     return (f"skewed segments: N={N_POINTS:,} points, C={CHANNELS} fp32, M={N_SEGMENTS:,} segments "
             f"(Zipf 1.2 sizes + one {N_POINTS // 10:,}-point segment), ids randomly permuted; "
-            "step = scatter_sum + scatter_mean + scatter_max forward with a prebuilt plan")
+            "step = scatter_sum + scatter_mean + scatter_max forward of the same features with a prebuilt plan")
 
 
 def headline_config(world):
@@ -207,6 +207,9 @@ def run_ours(args):
     outs = {k: torch.empty((m, c), device=dev) for k in ("sum", "mean", "max")}
     arg = torch.empty((m, c), dtype=torch.int32, device=dev)
     ws = torch.empty(lib.texb_reduce_workspace_bytes(n, c), dtype=torch.uint8, device=dev)
+    # one workspace per reduction of a step: the reductions of a sequence overlap on the GPU
+    ws_seq = {k: torch.empty(lib.texb_reduce_workspace_bytes(n, c), dtype=torch.uint8, device=dev)
+              for k in ("sum", "mean", "max")}
     stream = torch.cuda.current_stream().cuda_stream
     perm_ptr = None if data.perm is None else data.perm.data_ptr()
     ops = {"sum": _native.OP_SUM, "mean": _native.OP_MEAN, "max": _native.OP_MAX}
@@ -218,12 +221,26 @@ def run_ours(args):
     torch.cuda.synchronize()
     plan_flags = _native.PLAN_SETTLED | (_native.PLAN_NO_SPLIT if data.max_cnt <= _native.NO_SPLIT_MAX_CNT else 0)
 
-    def reduce(name):
+    def reduce(name, sequence=0):
+        """One reduction through the C ABI.  sequence: 0 = a call on its own; 1 / 2 = first /
+        following reduction of a step issued as one sequence (TEXB_SEQUENCE_FIRST / _NEXT:
+        the following ones do not wait for the stream at their start)."""
+        w = ws if sequence == 0 else ws_seq[name]
+        flags = plan_flags | (0, _native.SEQUENCE_FIRST, _native.SEQUENCE_NEXT)[sequence]
         st = entry(ops[name], feat.data_ptr(), data.sid.data_ptr(), perm_ptr,
-                   data.preSum.data_ptr(), plan_flags, data.balance.data_ptr(), data.balance.numel(),
-                   n, c, m, outs[name].data_ptr(), arg.data_ptr(), 0, ws.data_ptr(), ws.numel(), stream)
+                   data.preSum.data_ptr(), flags, data.balance.data_ptr(), data.balance.numel(),
+                   n, c, m, outs[name].data_ptr(), arg.data_ptr(), 0, w.data_ptr(), w.numel(), stream)
         if st != 0:
             raise RuntimeError(_native.last_error())
+
+    def step(sequence):
+        if sequence:
+            reduce("sum", 1)
+            reduce("mean", 2)
+            reduce("max", 2)
+        else:
+            for name in ops:
+                reduce(name)
 
     def barrier():
         if world > 1:
@@ -231,31 +248,20 @@ def run_ours(args):
 
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
+    as_sequence = not args.no_sequence
     for _ in range(max(args.warmup, 3)):
-        for name in ops:
-            reduce(name)
+        step(as_sequence)
     torch.cuda.synchronize()
 
     # ---- timed region: K steps, device timed, per-step events around the sum launch pair
     k = args.steps
-    # Events around the sum launch pair on every 8th step only: an event record between two
-    # kernels keeps the next kernel from being placed while the previous one drains.
-    sampled = [i for i in range(k) if i % 8 == 0]
-    ev_sum = {i: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for i in sampled}
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     torch.cuda.synchronize()
     sampler.mark("timed_begin")
     t0.record()
     for i in range(k):
-        if i in ev_sum:
-            ev_sum[i][0].record()
-            reduce("sum")
-            ev_sum[i][1].record()
-        else:
-            reduce("sum")
-        reduce("mean")
-        reduce("max")
+        step(as_sequence)
     t1.record()
     torch.cuda.synchronize()
     sampler.mark("timed_end")
@@ -267,8 +273,25 @@ def run_ours(args):
         elapsed_ms = float(t.item())
     ms_per_step = elapsed_ms / k
     value = world * bytes_step / (ms_per_step * 1e-3) / 1e9
-    sum_ms = statistics.mean(a.elapsed_time(b) for a, b in ev_sum.values())
     timeouts = _native.device_wait_timeouts()
+
+    # ---- the same K steps issued the other way (three calls on their own / one sequence)
+    other_ms = None
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        step(not as_sequence)
+    a.record()
+    for i in range(k):
+        step(not as_sequence)
+    b.record()
+    torch.cuda.synchronize()
+    other_ms = a.elapsed_time(b) / k
+    step_variants = {"one_sequence" if as_sequence else "three_calls": round(ms_per_step, 4),
+                     "three_calls" if as_sequence else "one_sequence": round(other_ms, 4),
+                     "timed_region": "one_sequence" if as_sequence else "three_calls", "unit": "ms per step (this rank)",
+                     "note": "one_sequence: the three reductions of a step marked TEXB_SEQUENCE_FIRST / _NEXT, each a "
+                             "single launch with its own workspace, the second and third not waiting for the stream at "
+                             "their start; three_calls: three independent calls (reduce + fix-up launch pairs)"}
 
     # ---- per-op device time (same buffers, right after the timed region)
     per_op = {}
@@ -288,26 +311,24 @@ def run_ours(args):
     clocks = sampler.stop()
     peak, peak_kind = measured_peak_gbs()
     # Roofline of the dominant kernel, segment_reduce_staged_kernel, from the TIMED REGION
-    # itself: the region is K x (sum, mean, max) launch pairs of that one kernel template
+    # itself: the region is K x (sum, mean, max) launches of that one kernel template
     # and nothing else, so its average launch takes ms_per_step / 3 and moves
-    # bytes_step / 3 algorithmic bytes.  Beside it: the sum launch pairs that were
-    # individually bracketed by events inside the region (which serialises them against
-    # their neighbours), and the per-operator loops that ran right after the region.
+    # bytes_step / 3 algorithmic bytes.  In a sequence consecutive launches overlap at their
+    # edges, so this is the time a launch adds to the region, not the life of one grid;
+    # the per-operator loops that ran right after the region give a launch on its own.
     per_launch_us = ms_per_step * 1e3 / 3
     per_launch_bytes = bytes_step / 3
     achieved = per_launch_bytes / per_launch_us / 1e3
-    bracketed = bytes_op["sum"] / (sum_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm",
-                "kernel": f"segment_reduce_staged_kernel<{args.features}> + segment_fixup_kernel (one launch pair), "
-                          "average over the sum, mean and max launches of the timed region",
-                "timing": f"CUDA events around the timed region: {k} steps x 3 launch pairs",
+                "kernel": f"segment_reduce_staged_kernel<{args.features}>, average over the sum, mean and max launches "
+                          "of the timed region" + ("" if as_sequence else " (each followed by its segment_fixup_kernel)"),
+                "timing": f"CUDA events around the timed region: {k} steps x 3 reductions",
                 "achieved": round(achieved, 1), "peak": peak, "peak_source": f"hbm_gbs of {peak_kind} copy",
                 "unit": "GB/s", "frac": round(achieved / peak, 4), "frac_of_nominal_8000": round(achieved / HBM_NOMINAL_GBS, 4),
                 "algorithmic_bytes_per_launch": round(per_launch_bytes), "us_per_launch": round(per_launch_us, 2),
-                "sum_bracketed_in_timed_region": {"us_per_launch": round(sum_ms * 1e3, 2), "launches": len(ev_sum),
-                                                  "achieved": round(bracketed, 1), "frac": round(bracketed / peak, 4)},
-                "sum_in_loop_after_region": {"us_per_launch": per_op["sum"]["us"], "achieved": per_op["sum"]["GBps"],
-                                             "frac": round(per_op["sum"]["GBps"] / peak, 4)},
+                "sum_alone_in_loop_after_region": {"us_per_launch": per_op["sum"]["us"], "achieved": per_op["sum"]["GBps"],
+                                                   "frac": round(per_op["sum"]["GBps"] / peak, 4),
+                                                   "note": "50 independent scatter_sum calls (reduce + fix-up) back to back"},
                 "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if headline else None,
                 "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one sum launch pair in an ncu capture "
                                   "of this workload (profiles/); not measured by this run" if headline else None}
@@ -441,7 +462,8 @@ def run_ours(args):
             "roofline": roofline,
             "cpu_baseline": cpu,
             "e2e": e2e,
-            "gpu_launches": 6 * k * world,
+            "gpu_launches": (3 if as_sequence else 6) * k * world,
+            "step_variants": step_variants,
             "clocks": clocks,
             "multi_frame": multi,
             "other_configs": configs,
@@ -945,6 +967,8 @@ def main():
     ap.add_argument("--points", type=int, default=N_POINTS, help="reduced sizes are for profiling only")
     ap.add_argument("--segments", type=int, default=N_SEGMENTS)
     ap.add_argument("--channels", type=int, default=CHANNELS)
+    ap.add_argument("--no-sequence", action="store_true",
+                    help="time the step as three independent calls instead of one sequence of three reductions")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-multi-frame", action="store_true")

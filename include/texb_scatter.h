@@ -48,6 +48,19 @@ extern "C" {
                                  <= 128 rows, table built with the plan statistics): the reduce is
                                  then a single launch, nothing is left for a fix-up */
 #define TEXB_PLAN_NO_SPLIT_MAX_CNT 128
+/* Sequences: several reductions of the SAME feats with the SAME plan issued back to back
+ * on one stream (a pooling layer that wants sum, mean and max of its point features).
+ * Mark the first call TEXB_SEQUENCE_FIRST and the following ones TEXB_SEQUENCE_NEXT, and
+ * give every call of the sequence outputs and a workspace of its own.  The first call
+ * waits for the earlier work of the stream like any call; a following call does not wait
+ * at its start -- its CTAs take over the SMs one by one as the CTAs of the call before it
+ * retire, so the ramp-down of one reduction, the finishing of its long segments and the
+ * ramp-up of the next overlap -- and waits at its end instead, so that the calls still
+ * complete in order.  Every call of a sequence is a single launch (long segments are
+ * finished inside the reduce kernel).  TEXB_SEQUENCE_NEXT requires TEXB_PLAN_SETTLED, and
+ * nothing else may be put on the stream between the calls of a sequence. */
+#define TEXB_SEQUENCE_FIRST 8
+#define TEXB_SEQUENCE_NEXT 16
 
 /* Library version (major * 100 + minor). */
 int texb_version(void);

@@ -645,3 +645,52 @@ def test_balance_cuts_land_on_segment_starts_when_segments_are_short():
     assert data.max_cnt > _native.NO_SPLIT_MAX_CNT and not data._plan.no_split
     cuts = data.balance.long()
     assert int(cuts[0]) == 0 and int(cuts[-1]) == 300_000 and bool((cuts[1:] >= cuts[:-1]).all())
+
+
+@pytest.mark.parametrize("kind", ["skewed_c128", "skewed_c260", "skewed_c20", "skewed_bf16", "voxel_c64", "gaps_c128"])
+def test_sequence_of_reductions_equals_the_single_operators(kind):
+    """scatter_multi issues sum, mean and max as one sequence in which the second and third
+    reduction do not wait for the stream before they start.  Every result must equal the
+    single operator's bit for bit, call after call (the calls of a sequence overlap on the
+    GPU: each has its own workspace and its own outputs), also when the stream is kept busy
+    right before the sequence and when sequences over two different plans alternate."""
+    from torchex_b200 import scatter_multi
+    if kind.startswith("skewed"):
+        n, m = 400_000, 12_000
+        ids, cnt = W.skewed_ids(n, m, seed=98, giant=150_000)
+        c = {"skewed_c128": 128, "skewed_c260": 260, "skewed_c20": 20, "skewed_bf16": 128}[kind]
+    elif kind == "voxel_c64":
+        ids, cnt = W.voxel_frame(200_000, seed=98)
+        n, m, c = ids.numel(), cnt.numel(), 64
+    else:  # ids that skip values: empty segments, which take the plain calls
+        ids, cnt = W.skewed_ids(100_000, 3_000, seed=98, giant=20_000)
+        ids, n, m, c = ids * 2, 100_000, 6_000, 128
+        cnt = torch.bincount(ids, minlength=m)
+    x = W.features(n, c, 98).to(DEV)
+    if kind == "skewed_bf16":
+        x = x.to(torch.bfloat16)
+    data = ScatterData(ids.to(DEV), cnt.to(DEV))
+    assert data.max_cnt == int(cnt.max())  # the plan statistics have arrived: the plan is settled
+    other_ids, other_cnt = W.uniform_ids(150_000, 40_000, seed=99)
+    other = ScatterData(other_ids.to(DEV), other_cnt.to(DEV))
+    y = W.features(150_000, 128, 99).to(DEV)
+    assert other.max_cnt > 0
+    want = (scatter_sum(x, data), scatter_mean(x, data)) + tuple(scatter_max(x, data))
+    want_other = scatter_max(y, other)
+    busy = torch.empty(32 << 20, dtype=torch.uint8, device=DEV)
+    kept = []
+    for rep in range(12):
+        if rep % 3 == 0:
+            busy.zero_()                      # earlier work of the stream that the first reduction must wait for
+        got = scatter_multi(x, data)
+        if rep % 2:
+            kept.append(scatter_multi(y, other, ops=("max", "sum")))
+        kept.append(got)
+    torch.cuda.synchronize()
+    for got in kept:
+        if "mean" in got:
+            assert torch.equal(got["sum"], want[0]) and torch.equal(got["mean"], want[1])
+            assert torch.equal(got["max"][0], want[2]) and torch.equal(got["max"][1], want[3])
+        else:
+            assert torch.equal(got["max"][0], want_other[0]) and torch.equal(got["max"][1], want_other[1])
+    assert _native.device_wait_timeouts() == 0

@@ -5,7 +5,7 @@ Drop-in for the scatter part of ``torchex``: ``ScatterData``, ``scatter_sum``,
 sm_100a kernels behind a C ABI (``include/texb_scatter.h``).
 """
 from .operator_py import (ScatterData, TorchTimer, gather_back, getPreSum, ingroup_inds, ingroup_rank,
-                          scatter_max, scatter_mean, scatter_mean_max, scatter_sum)
+                          scatter_max, scatter_mean, scatter_mean_max, scatter_multi, scatter_sum)
 
 __all__ = ["ScatterData", "TorchTimer", "getPreSum", "scatter_max", "scatter_mean", "scatter_sum",
-           "ingroup_inds", "ingroup_rank", "gather_back", "scatter_mean_max"]
+           "ingroup_inds", "ingroup_rank", "gather_back", "scatter_mean_max", "scatter_multi"]

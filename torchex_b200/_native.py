@@ -82,6 +82,7 @@ _SIGNATURES = {
 
 OP_SUM, OP_MEAN, OP_MAX = 0, 1, 2
 PLAN_HAS_EMPTY, PLAN_SETTLED, PLAN_NO_SPLIT = 1, 2, 4  # bits of the plan_flags argument of the reduce entry points
+SEQUENCE_FIRST, SEQUENCE_NEXT = 8, 16  # reductions of the same features issued back to back as one sequence
 NO_SPLIT_MAX_CNT = 128  # largest segment for which texb_plan_balance puts every cut on a segment start
 BALANCE_PIECES = 131072  # pieces of the plan's balance table (see texb_plan_balance)
 

@@ -129,7 +129,7 @@ struct Plan {
   bool no_split = false;   // every cut of the balance table is a segment start (short segments only)
   struct Scratch {
     int64_t channels;
-    bool pair;
+    int slot;  // 0: single calls; k: the k-th reduction of a sequence; -1: the two-output operator
     void* stream;
     at::Tensor buffer;
   };
@@ -142,13 +142,13 @@ struct Plan {
   const int32_t* perm_ptr() const { return perm.defined() ? perm.data_ptr<int>() : nullptr; }
 
   // Calls on one stream are ordered, so they can share a buffer; another stream gets its own.
-  at::Tensor& workspace(int64_t channels, bool pair, void* stream, size_t bytes) {
+  at::Tensor& workspace(int64_t channels, int slot, void* stream, size_t bytes) {
     for (auto& s : scratch_cache)
-      if (s.channels == channels && s.pair == pair && s.stream == stream) {
+      if (s.channels == channels && s.slot == slot && s.stream == stream) {
         if (size_t(s.buffer.numel()) < bytes) s.buffer = scratch(bytes, sid);
         return s.buffer;
       }
-    scratch_cache.push_back({channels, pair, stream, scratch(bytes, sid)});
+    scratch_cache.push_back({channels, slot, stream, scratch(bytes, sid)});
     return scratch_cache.back().buffer;
   }
 };
@@ -287,7 +287,7 @@ std::tuple<at::Tensor, c10::optional<at::Tensor>> reduce(Plan& p, int op, const 
                  "texb_segment_reduce_small");
     return {out, arg};
   }
-  at::Tensor& ws = p.workspace(c, false, stream, texb_reduce_workspace_bytes(n, int(c)));
+  at::Tensor& ws = p.workspace(c, 0, stream, texb_reduce_workspace_bytes(n, int(c)));
   if (bf16) {
     check_status(texb_segment_reduce_bf16(op, feats.data_ptr(), p.sid.data_ptr<int>(), p.perm_ptr(),
                                           p.offsets.data_ptr<int>(), p.flags(), p.balance.data_ptr<int>(),
@@ -316,7 +316,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> reduce_pair(Plan& p, int op, cons
   at::Tensor out_sum = output_rows(sum_given, feats, m, c, at::kFloat, "out_sum");
   at::Tensor out_max = output_rows(max_given, feats, m, c, at::kFloat, "out_max");
   at::Tensor arg = output_rows(arg_given, feats, m, c, at::kInt, "arg");
-  at::Tensor& ws = p.workspace(c, true, stream, texb_reduce_pair_workspace_bytes(n, int(c)));
+  at::Tensor& ws = p.workspace(c, -1, stream, texb_reduce_pair_workspace_bytes(n, int(c)));
   check_status(texb_segment_reduce_pair(op, feats.data_ptr(), int(feats.element_size()), p.sid.data_ptr<int>(),
                                         p.perm_ptr(), p.offsets.data_ptr<int>(), p.flags(),
                                         p.balance.data_ptr<int>(), int(p.balance.numel()), n, int(c), m,
@@ -324,6 +324,54 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> reduce_pair(Plan& p, int op, cons
                                         int32_t(arg_base), ws.data_ptr(), size_t(ws.numel()), stream),
                "texb_segment_reduce_pair");
   return {out_sum, out_max, arg};
+}
+
+// Several reductions of the same rows, issued back to back as one sequence
+// (TEXB_SEQUENCE_FIRST / TEXB_SEQUENCE_NEXT): the second and later ones do not wait for the
+// stream at their start, so each takes over the SMs as the one before it drains.  Every
+// reduction has its own outputs and its own workspace.  Returns one (out, arg | None) per op.
+std::vector<std::tuple<at::Tensor, c10::optional<at::Tensor>>> reduce_sequence(Plan& p, const std::vector<int>& ops,
+                                                                               const at::Tensor& feats_in,
+                                                                               int64_t arg_base) {
+  const at::Tensor feats = prepare_feats(p, feats_in, false);
+  const int64_t n = feats.size(0), c = feats.size(1), m = p.num_segments;
+  const bool bf16 = feats.scalar_type() == at::kBFloat16;
+  std::vector<std::tuple<at::Tensor, c10::optional<at::Tensor>>> results;
+  // The one-launch kernel for small inputs, a plan the host does not yet know to be complete,
+  // or a plan that may have empty segments (their fill is a launch of its own between the
+  // reductions): plain calls, one after the other.
+  if ((!bf16 && texb_segment_reduce_small_ok(n, int(c), p.max_cnt)) || !p.settled || p.has_empty || n == 0) {
+    for (int op : ops) results.push_back(reduce(p, op, feats, arg_base, c10::nullopt, c10::nullopt));
+    return results;
+  }
+  const c10::cuda::CUDAGuard guard(feats.device());
+  void* stream = stream_of(feats);
+  int k = 0;
+  for (int op : ops) {
+    TORCH_CHECK(op == TEXB_OP_SUM || op == TEXB_OP_MEAN || op == TEXB_OP_MAX, "unknown reduce op ", op);
+    at::Tensor out = at::empty({m, c}, feats.options().dtype(at::kFloat));
+    c10::optional<at::Tensor> arg;
+    int32_t* arg_ptr = nullptr;
+    if (op == TEXB_OP_MAX) {
+      arg = at::empty({m, c}, feats.options().dtype(at::kInt));
+      arg_ptr = arg->data_ptr<int>();
+    }
+    at::Tensor& ws = p.workspace(c, k + 1, stream, texb_reduce_workspace_bytes(n, int(c)));
+    const int flags = p.flags() | (k == 0 ? TEXB_SEQUENCE_FIRST : TEXB_SEQUENCE_NEXT);
+    const int st = bf16
+        ? texb_segment_reduce_bf16(op, feats.data_ptr(), p.sid.data_ptr<int>(), p.perm_ptr(), p.offsets.data_ptr<int>(),
+                                   flags, p.balance.data_ptr<int>(), int(p.balance.numel()), n, int(c), m,
+                                   out.data_ptr<float>(), arg_ptr, int32_t(arg_base), ws.data_ptr(), size_t(ws.numel()),
+                                   stream)
+        : texb_segment_reduce(op, feats.data_ptr<float>(), p.sid.data_ptr<int>(), p.perm_ptr(),
+                              p.offsets.data_ptr<int>(), flags, p.balance.data_ptr<int>(), int(p.balance.numel()), n,
+                              int(c), m, out.data_ptr<float>(), arg_ptr, int32_t(arg_base), ws.data_ptr(),
+                              size_t(ws.numel()), stream);
+    check_status(st, "texb_segment_reduce (sequence)");
+    results.emplace_back(out, arg);
+    ++k;
+  }
+  return results;
 }
 
 // Autograd may hand over an expanded or strided gradient; the C ABI wants fp32 rows.
@@ -412,6 +460,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("build_plan", &build_plan, py::arg("ids"), py::arg("num_segments"), py::arg("balance_pieces"));
   m.def("reduce", &reduce, py::arg("plan"), py::arg("op"), py::arg("feats"), py::arg("arg_base") = 0,
         py::arg("out") = c10::nullopt, py::arg("arg") = c10::nullopt);
+  m.def("reduce_sequence", &reduce_sequence, py::arg("plan"), py::arg("ops"), py::arg("feats"),
+        py::arg("arg_base") = 0);
   m.def("reduce_pair", &reduce_pair, py::arg("plan"), py::arg("op"), py::arg("feats"), py::arg("arg_base") = 0,
         py::arg("out_sum") = c10::nullopt, py::arg("out_max") = c10::nullopt, py::arg("arg") = c10::nullopt);
   m.def("broadcast_back", &broadcast_back, py::arg("plan"), py::arg("mode"), py::arg("g"),

@@ -54,6 +54,11 @@ int segment_reduce_impl(int op, const void* feats, int in_bytes, const int32_t* 
   const bool has_empty = (plan_flags & TEXB_PLAN_HAS_EMPTY) != 0;
   const bool plan_settled = (plan_flags & TEXB_PLAN_SETTLED) != 0;
   const bool no_split = (plan_flags & TEXB_PLAN_NO_SPLIT) != 0;
+  const bool no_wait = (plan_flags & TEXB_SEQUENCE_NEXT) != 0;
+  const bool single_launch = no_wait || (plan_flags & TEXB_SEQUENCE_FIRST) != 0;
+  if (no_wait && !plan_settled)
+    return fail(TEXB_ERR_INVALID_ARGUMENT, "TEXB_SEQUENCE_NEXT needs TEXB_PLAN_SETTLED: a reduction that does not "
+                "wait for the stream may only read a plan the host knows to be complete");
   if (in_bytes != 4 && in_bytes != 2)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "features must be fp32 (4 bytes) or bf16 (2 bytes)");
   if (op != TEXB_OP_SUM && op != TEXB_OP_MEAN && op != TEXB_OP_MAX)
@@ -92,7 +97,8 @@ int segment_reduce_impl(int op, const void* feats, int in_bytes, const int32_t* 
   if (balance && balance_len < 2)
     return fail(TEXB_ERR_INVALID_ARGUMENT, "balance table needs at least 2 entries");
   Call c = {feats, sid, perm, out, out_sum, arg, workspace, workspace_bytes, int(n), C, op == TEXB_OP_MEAN, stream,
-            balance, balance ? balance_len - 1 : 0, int(arg_base), int(m), plan_settled, no_split};
+            balance, balance ? balance_len - 1 : 0, int(arg_base), int(m), plan_settled, no_split, single_launch,
+            no_wait};
   if (pair) return reduce_dispatch_sum_max(g, c);
   if (op == TEXB_OP_MAX) return reduce_dispatch_max(g, c);
   if (tuning().compensated) return reduce_dispatch_sum(g, c);

@@ -259,6 +259,17 @@ __device__ __forceinline__ unsigned global_timer_lo() {
   return t;
 }
 
+// A reduction that did not wait for the stream at its start waits here, when its own work
+// is done: its grid then cannot complete before the grid launched just before it has, so the
+// reductions of a sequence complete in order and whatever follows them in the stream sees
+// all of their results.  The earlier grid started first, so this wait is normally over
+// before it begins.
+__device__ __forceinline__ void stream_tail_wait(bool no_wait) {
+#if __CUDA_ARCH__ >= 900
+  if (no_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
+#endif
+}
+
 // Stitches the edge runs a CTA left in shared memory.  The valid slots, taken in
 // slot order, form chains: a slot that is open to the right is continued by the
 // next valid slot.  A chain is folded in position order by the group that owns
@@ -536,6 +547,7 @@ struct Split {
   int balance_k;
   int stream_hint;         // 1: feature rows are copied with an L2 evict-first policy
   int plan_settled;        // 1: the plan arrays may be read before the stream's earlier work is visible
+  int no_wait;             // 1: a later reduction of a back-to-back sequence: nothing is waited for at the start
   int rows_per_cta, rows_per_group, num_ctas;
 };
 
@@ -584,7 +596,10 @@ segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict
   // the stream (typically the fix-up of the previous reduction): its CTAs are then
   // placed while that kernel drains, and the wait below holds them until all of
   // its memory operations are visible, before anything is read.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // A later reduction of a back-to-back sequence (sp.no_wait) does not wait: everything it
+  // reads was complete before the first reduction of the sequence let its dependents start,
+  // and it writes only buffers of its own.  It waits at its END instead (see stream_tail_wait).
+  if (!sp.no_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #endif
   const int lane_g = threadIdx.x & (LPR - 1);
@@ -680,6 +695,7 @@ segment_reduce_kernel(const float* __restrict__ feats, const int32_t* __restrict
   if (ws.ready)
     finish_chain_in_kernel<Op, VEC, LPR>(ws, ends_here, s_vec, s_cnt, out, arg, C, ch, lane_on, lane_g, group, mean,
                                          ospec);
+  stream_tail_wait(sp.no_wait != 0);
 }
 
 // ---- staged kernel --------------------------------------------------------------
@@ -873,17 +889,19 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
   // the tail of the previous kernel; the features are read and global memory is
   // written after it either way.  A no-op for a plain launch.
   bool waited = false;
-  auto wait_for_stream = [&waited] {
+  const bool no_wait = sp.no_wait != 0;
+  auto wait_for_stream = [&waited, no_wait] {
     if (waited) return;
     waited = true;
 #if __CUDA_ARCH__ >= 900
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    // Let the dependent fix-up grid be scheduled now (it parks at its own wait until
-    // this grid has finished).
+    // A later reduction of a back-to-back sequence does not wait here (see stream_tail_wait).
+    if (!no_wait) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Let the dependent grid be scheduled now (a fix-up parks at its own wait until this
+    // grid has finished; the next reduction of a sequence starts as this grid's CTAs retire).
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #endif
   };
-  if (!sp.plan_settled) wait_for_stream();
+  if (!sp.plan_settled || no_wait) wait_for_stream();
   const unsigned t_start = global_timer_lo();
   const int lane_g = threadIdx.x & (LPR - 1);
   const int group = threadIdx.x / LPR;
@@ -1154,6 +1172,7 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
   if (ws.ready)
     finish_chain_in_kernel<Op, VEC, LPR>(ws, ends_here, s_vec, s_cnt, out, arg, C, ch, lane_on, lane_g, group, mean,
                                          ospec);
+  stream_tail_wait(sp.no_wait != 0);
 }
 
 // ---- fix-up kernel --------------------------------------------------------------
@@ -1277,6 +1296,7 @@ inline Split make_split(int64_t n, const Layout& g, int ctas_per_sm) {
   s.balance_k = 0;
   s.stream_hint = tuning().l2_stream_hint;
   s.plan_settled = 0;
+  s.no_wait = 0;
   int64_t rows = tuning().rows_per_cta;
   if (rows <= 0) {
     const int64_t resident = int64_t(sm_count()) * ctas_per_sm;
@@ -1348,6 +1368,8 @@ struct Call {
   int m;
   bool plan_settled;
   bool no_split;  // every cut of the balance table is a segment start: no records, nothing to fix up
+  bool single_launch;  // finish chains inside the reduce kernel whatever the knob says (sequences of reductions)
+  bool no_wait;        // a later reduction of such a sequence
 };
 
 // Resident CTAs per SM of one kernel instantiation (asked once per process).
@@ -1370,6 +1392,7 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
     s.balance_k = c.balance_k;
   }
   s.plan_settled = c.plan_settled ? 1 : 0;
+  s.no_wait = c.no_wait ? 1 : 0;
   const size_t vec_bytes = records_vec_bytes(g, s.num_ctas, Op::kPlanes);
   const size_t meta_bytes = records_meta_bytes(g, s.num_ctas);
   const size_t need = vec_bytes + meta_bytes + records_ready_bytes(g, s.num_ctas);
@@ -1383,7 +1406,7 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
   ws.meta = reinterpret_cast<int4*>(base + vec_bytes);
   // Chains are finished by the reduce kernel itself ("chain_inline" knob, the default) or by
   // the fix-up kernel that follows it.
-  const bool inline_chains = tuning().chain_inline != 0 && s.num_ctas > 1;
+  const bool inline_chains = (tuning().chain_inline != 0 || c.single_launch || c.no_wait) && s.num_ctas > 1;
   ws.ready = inline_chains ? reinterpret_cast<unsigned long long*>(base + vec_bytes + meta_bytes) : nullptr;
   ws.epoch = inline_chains ? next_launch_epoch() : 0ull;
 

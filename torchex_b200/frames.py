@@ -259,6 +259,8 @@ class FrameShard:
         of each result is started as soon as its reduction has been launched and only
         waited for at the end, so the bytes of reduction k move under reduction k + 1."""
         if not replicated or self.layout.world_size == 1:
+            if self._reduce is _cuda_reduce and all(op in ("sum", "mean", "max") for op in ops):
+                return _cuda_reduce_sequence(ops, feats, self.data, self.layout.row_base)
             return {op: self._reduce(op, feats, self.data, self.layout.row_base) for op in ops}
         pending = {op: self._replicated_start(op, feats, group) for op in ops}
         out = {}
@@ -283,3 +285,14 @@ def _cuda_reduce(op: str, feats: torch.Tensor, data, row_base: int = 0, outputs=
         from .operator_py import scatter_mean, scatter_sum
         return {"sum": scatter_sum, "mean": scatter_mean}[op](feats, data)
     return _reduce({"sum": _native.OP_SUM, "mean": _native.OP_MEAN}[op], feats, data, want_arg=False, out=o[0])[0]
+
+
+def _cuda_reduce_sequence(ops: Sequence[str], feats: torch.Tensor, data, row_base: int = 0):
+    """The reductions ``ops`` of the same rows issued as one sequence (see
+    ``operator_py.scatter_multi``), with rows reported from ``row_base``."""
+    from .operator_py.scatter_op import _OPS
+    from . import scatter_ext
+    if data._pending is not None:
+        data._poll()
+    res = scatter_ext.reduce_sequence(data._plan, [_OPS[o] for o in ops], feats, row_base)
+    return {o: (r if o == "max" else r[0]) for o, r in zip(ops, res)}

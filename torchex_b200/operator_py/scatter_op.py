@@ -519,4 +519,23 @@ def scatter_mean_max(feats: torch.Tensor, data: ScatterData):
     return _reduce_pair(_native.OP_MEAN, feats, data)
 
 
+_OPS = {"sum": _native.OP_SUM, "mean": _native.OP_MEAN, "max": _native.OP_MAX}
+
+
+def scatter_multi(feats: torch.Tensor, data: ScatterData, ops=("sum", "mean", "max")):
+    """Several reductions of the same ``feats`` issued as one sequence: returns a dict
+    ``{"sum": out, "mean": out, "max": (out, arg)}`` for the ops asked for, each equal bit for
+    bit to what ``scatter_sum`` / ``scatter_mean`` / ``scatter_max`` return.  The second and
+    later reductions do not wait for the stream before they start (they read nothing the first
+    one did not already wait for, and write buffers of their own), so each takes over the SMs
+    as the previous one drains instead of starting after its last CTA and its fix-up have
+    finished.  Forward only: use the single operators where a gradient is needed.  No
+    counterpart in the reference, whose callers run the operators one after the other
+    (scatter_op.py:138-141)."""
+    if data._pending is not None:
+        data._poll()
+    res = _ext.reduce_sequence(data._plan, [_OPS[o] for o in ops], feats, 0)
+    return {o: (r if o == "max" else r[0]) for o, r in zip(ops, res)}
+
+
 getPreSum = GetPreSumFunction.apply

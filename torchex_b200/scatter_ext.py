@@ -45,6 +45,7 @@ make_plan = native.make_plan
 build_plan = native.build_plan
 reduce = native.reduce
 reduce_pair = native.reduce_pair
+reduce_sequence = getattr(native, "reduce_sequence", None)
 broadcast_back = native.broadcast_back
 mean_max_backward = native.mean_max_backward
 segment_rank = native.segment_rank
