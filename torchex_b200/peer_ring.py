@@ -9,8 +9,9 @@ gather of one result then is:
 1. the reduce kernels write this rank's shard straight into a slot of its ring;
 2. a one-element NCCL all-reduce on the copy stream: every rank's shard is complete;
 3. this rank pulls the other ranks' shards out of their rings into the row ranges of
-   its result with ``texb_peer_copy`` (``cudaMemcpyAsync``, copy engines); its own shard
-   is copied into place on a third stream at the same time;
+   its result with ``texb_peer_copy`` (``cudaMemcpyAsync``, copy engines), in pieces spread
+   over a few streams so that several copies are in flight; its own shard is copied into
+   place on another stream at the same time;
 4. a second one-element all-reduce: every rank has finished pulling, the slot is free.
 
 Steps 2-4 run on a side stream, so the next reduction proceeds on the main stream
@@ -25,6 +26,10 @@ import torch
 import torch.distributed as dist
 
 from . import _native
+
+
+PULL_STREAMS = 4            # concurrent device-to-device copies per rank
+PULL_CHUNK_BYTES = 64 << 20  # a shard larger than this is pulled in pieces spread over the streams
 
 
 class _RawCuda:
@@ -75,8 +80,11 @@ class PeerRing:
                 _native.check(self._lib.texb_peer_buffer_open(buf, ctypes.byref(p)), "texb_peer_buffer_open")
                 self._peers[r] = p.value
             self._local = torch.as_tensor(_RawCuda(self._ptr.value, self.slot_bytes * slots), device=self.device)
-            self._stream = torch.cuda.Stream(self.device)        # handshakes and pulls from the peers
-            self._own_stream = torch.cuda.Stream(self.device)    # this rank's own shard, copied beside them
+            self._stream = torch.cuda.Stream(self.device)        # the handshakes
+            self._own_stream = torch.cuda.Stream(self.device)    # this rank's own shard, copied beside the pulls
+            # the pulls: several copies in flight at once keep more than one copy engine (and,
+            # with several peers, more than one NVLink path) busy
+            self._pull_streams = [torch.cuda.Stream(self.device) for _ in range(PULL_STREAMS)]
             self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
             self._free = [None] * slots   # event: every rank has pulled what the slot held
         self._next = 0
@@ -113,11 +121,12 @@ class PeerRing:
             row += cnt
         row_bytes = self.channels * 4
 
-        def copy(r, stream):
-            nbytes = self.counts[r] * row_bytes
+        def copy(r, stream, first=0, nbytes=None):
+            total = self.counts[r] * row_bytes
+            nbytes = total - first if nbytes is None else nbytes
             if nbytes:
-                src = (self._ptr.value if r == self.rank else self._peers[r]) + slot * self.slot_bytes
-                _native.check(self._lib.texb_peer_copy(out.data_ptr() + offsets[r] * row_bytes, src, nbytes,
+                src = (self._ptr.value if r == self.rank else self._peers[r]) + slot * self.slot_bytes + first
+                _native.check(self._lib.texb_peer_copy(out.data_ptr() + offsets[r] * row_bytes + first, src, nbytes,
                                                        stream.cuda_stream), "texb_peer_copy")
 
         # this rank's own shard: a local copy on a stream of its own, beside the pulls
@@ -128,20 +137,37 @@ class PeerRing:
         own_done.record(own)
         side = self._stream
         side.wait_stream(main)                      # this rank's shard is complete ...
+        done = [own_done]
         with torch.cuda.stream(side):
             dist.all_reduce(self._token, group=self.group)   # ... and so is everyone else's
-            for step in range(1, self.world):       # start with the next rank, so that not everyone pulls from rank 0 first
-                copy((self.rank + step) % self.world, side)
-            done = torch.cuda.Event()
-            done.record(side)
-            side.wait_event(own_done)               # the slot is only free once the local copy has read it too
+            ready = torch.cuda.Event()
+            ready.record(side)
+            # pieces to pull, starting with the next rank so that not everyone pulls from rank 0 first
+            pieces = []
+            for step in range(1, self.world):
+                r = (self.rank + step) % self.world
+                total = self.counts[r] * row_bytes
+                for first in range(0, total, PULL_CHUNK_BYTES):
+                    pieces.append((r, first, min(PULL_CHUNK_BYTES, total - first)))
+            for i, st in enumerate(self._pull_streams):
+                mine = pieces[i::len(self._pull_streams)]
+                if not mine:
+                    continue
+                st.wait_event(ready)
+                for r, first, nbytes in mine:
+                    copy(r, st, first, nbytes)
+                ev = torch.cuda.Event()
+                ev.record(st)
+                done.append(ev)
+                out.record_stream(st)
+            for ev in done:                         # the slot is free once every copy has read it
+                side.wait_event(ev)
             dist.all_reduce(self._token, group=self.group)   # every rank has pulled: the slot may be refilled
             free = torch.cuda.Event()
             free.record(side)
             self._free[slot] = free
-        out.record_stream(side)
         out.record_stream(own)
-        return PendingPull(out, (done, own_done))
+        return PendingPull(out, done)
 
     # ---- teardown --------------------------------------------------------------------
 
