@@ -694,3 +694,49 @@ def test_sequence_of_reductions_equals_the_single_operators(kind):
         else:
             assert torch.equal(got["max"][0], want_other[0]) and torch.equal(got["max"][1], want_other[1])
     assert _native.device_wait_timeouts() == 0
+
+
+@pytest.mark.parametrize("channel", [128, 256])
+def test_bf16_maximum_on_packed_pairs_with_special_values(channel):
+    """The maximum of bf16 rows is taken on packed bf16 pairs.  NaN, both infinities, signed
+    zeros and the many exact ties of bf16 data must give the fp32 path's answer: values equal
+    to the oracle's on the widened features, rows the lowest ones."""
+    n, m = 120_000, 5_000
+    ids, cnt = W.skewed_ids(n, m, seed=73, giant=30_000)
+    g = torch.Generator().manual_seed(73)
+    feat = W.features(n, channel, 73)
+    for value in (float("nan"), float("-inf"), float("inf"), 0.0, -0.0):
+        rows = torch.randint(0, n, (2_000,), generator=g)
+        cols = torch.randint(0, channel, (2_000,), generator=g)
+        feat[rows, cols] = value
+    feat[ids == 11] = float("nan")       # a segment that is NaN everywhere
+    feat[ids == 12] = float("-inf")      # and one that is -inf everywhere
+    feat16 = feat.to(torch.bfloat16)
+    wide = feat16.float()
+    data = ScatterData(ids.to(DEV), cnt.to(DEV))
+    mx, arg = scatter_max(feat16.to(DEV), data)
+    want_mx, want_arg = O.spec_scatter_max(wide, ids, m)
+    assert np.array_equal(mx.cpu().numpy(), want_mx)
+    assert np.array_equal(arg.cpu().numpy(), want_arg)
+    assert (arg[11] == -1).all() and (arg[12] == -1).all()
+    pm, px, pa = scatter_mean_max(feat16.to(DEV), data)   # the one-pass pair keeps the fp32 form
+    if channel == 128:
+        assert torch.equal(px, mx) and torch.equal(pa, arg)
+
+
+def test_mean_of_an_empty_segment_against_the_reference_expression():
+    """The reference computes the mean as `scatter_sum(feats, data) / data.unq_cnts`
+    (scatter_op.py:68-69).  Where a segment has rows the fused mean equals that expression
+    bit for bit; for a segment without rows (which the reference's dense ids cannot express)
+    the expression would be 0 / 0 = NaN, and this library writes 0."""
+    n, m = 30_000, 2_000
+    ids, cnt = W.uniform_ids(n, m // 2, seed=74)
+    ids, cnt = ids * 2, torch.bincount(ids * 2, minlength=m)   # every odd segment is empty
+    feat = W.features(n, 32, 74).to(DEV)
+    data = ScatterData(ids.to(DEV), cnt.to(DEV))
+    assert data.has_empty
+    mean = scatter_mean(feat, data)
+    reference_expression = scatter_sum(feat, data) / cnt.to(DEV).unsqueeze(-1)
+    filled = cnt > 0
+    assert torch.equal(mean[filled], reference_expression[filled])
+    assert bool(torch.isnan(reference_expression[~filled]).all()) and bool((mean[~filled] == 0).all())

@@ -20,6 +20,7 @@ namespace texb {
 // VEC 32-bit words (shared memory or the workspace).
 
 struct OpSumComp {  // fp32 sum + error-free two-sum: (s, c) with s + c the exact running sum
+  static constexpr bool kRawBf16 = false;
   static constexpr bool kIsMax = false;
   static constexpr bool kHasSum = true;
   static constexpr int kPlanes = 2;
@@ -101,6 +102,7 @@ struct OpSumComp {  // fp32 sum + error-free two-sum: (s, c) with s + c the exac
 };
 
 struct OpSumPlain {  // plain fp32 running sum (the "compensated" knob set to 0)
+  static constexpr bool kRawBf16 = false;
   static constexpr bool kIsMax = false;
   static constexpr bool kHasSum = true;
   static constexpr int kPlanes = 2;
@@ -145,6 +147,7 @@ struct OpSumPlain {  // plain fp32 running sum (the "compensated" knob set to 0)
 // its -FLT_MAX start (scatter_kernel.cu:139-151); a channel no row claimed
 // reports -FLT_MAX / -1, the reference's untouched state.  NaN and -inf never win.
 struct OpMax {
+  static constexpr bool kRawBf16 = false;
   static constexpr bool kIsMax = true;
   static constexpr bool kHasSum = false;
   static constexpr int kPlanes = 2;
@@ -184,9 +187,88 @@ struct OpMax {
   static __device__ __forceinline__ int index(const State<VEC>& x, int k) { return x.i[k]; }
 };
 
+// Maximum + row for bf16 rows, kept on packed bf16 pairs: one packed maximum, one packed
+// compare (two predicates) and two selects per PAIR of channels instead of unpacking each
+// value to fp32 and spending a compare and two selects on it -- the fp32 form keeps the
+// integer / logic pipe two thirds busy on 256-byte rows.  Comparisons of bf16 values are
+// exact, so the result is the same: strict ">" keeps the lowest row on ties, NaN never
+// wins (the packed maximum returns the other operand), -inf never claims a row.  States
+// travel through shared memory and the workspace in the same two planes as OpMax
+// (fp32 value, row), so stitching and the fix-up are unchanged.
+struct OpMaxBf16 {
+  static constexpr bool kIsMax = true;
+  static constexpr bool kHasSum = false;
+  static constexpr int kPlanes = 2;
+  static constexpr bool kRawBf16 = true;  // add_raw takes the bf16 pairs as they come from memory
+  template <int VEC> struct State { uint32_t b[VEC / 2]; int i[VEC]; };
+  template <int VEC>
+  static __device__ __forceinline__ void init(State<VEC>& x) {
+    static_assert(VEC % 2 == 0, "bf16 channels come in pairs");
+#pragma unroll
+    for (int j = 0; j < VEC / 2; ++j) x.b[j] = 0xFF80FF80u;  // (-inf, -inf)
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) x.i[k] = -1;
+  }
+  // One pair: the low half is the even channel.
+  static __device__ __forceinline__ void pair_step(uint32_t& best, int& i_lo, int& i_hi, uint32_t w, int r_lo, int r_hi) {
+    asm("{\n"
+        ".reg .pred p, q;\n"
+        "setp.gt.bf16x2 p|q, %3, %0;\n"
+        "max.bf16x2 %0, %0, %3;\n"
+        "selp.s32 %1, %4, %1, p;\n"
+        "selp.s32 %2, %5, %2, q;\n"
+        "}\n"
+        : "+r"(best), "+r"(i_lo), "+r"(i_hi) : "r"(w), "r"(r_lo), "r"(r_hi));
+  }
+  template <int VEC>
+  static __device__ __forceinline__ void add_raw(State<VEC>& x, const uint32_t (&w)[VEC / 2], int row) {
+#pragma unroll
+    for (int j = 0; j < VEC / 2; ++j) pair_step(x.b[j], x.i[2 * j], x.i[2 * j + 1], w[j], row, row);
+  }
+  // fp32 values that came from bf16 (their low 16 bits are zero): repacked exactly.
+  template <int VEC>
+  static __device__ __forceinline__ void add(State<VEC>& x, const float (&v)[VEC], int row) {
+    uint32_t w[VEC / 2];
+#pragma unroll
+    for (int j = 0; j < VEC / 2; ++j)
+      w[j] = (__float_as_uint(v[2 * j]) >> 16) | (__float_as_uint(v[2 * j + 1]) & 0xffff0000u);
+    add_raw<VEC>(x, w, row);
+  }
+  template <int VEC>
+  static __device__ __forceinline__ void merge(State<VEC>& x, const State<VEC>& y) {
+#pragma unroll
+    for (int j = 0; j < VEC / 2; ++j) pair_step(x.b[j], x.i[2 * j], x.i[2 * j + 1], y.b[j], y.i[2 * j], y.i[2 * j + 1]);
+  }
+  template <int VEC>
+  static __device__ __forceinline__ void pack(const State<VEC>& x, uint32_t (&w)[kPlanes][VEC]) {
+#pragma unroll
+    for (int j = 0; j < VEC / 2; ++j) {
+      w[0][2 * j] = x.b[j] << 16;
+      w[0][2 * j + 1] = x.b[j] & 0xffff0000u;
+    }
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) w[1][k] = uint32_t(x.i[k]);
+  }
+  template <int VEC>
+  static __device__ __forceinline__ void unpack(State<VEC>& x, const uint32_t (&w)[kPlanes][VEC]) {
+#pragma unroll
+    for (int j = 0; j < VEC / 2; ++j) x.b[j] = (w[0][2 * j] >> 16) | (w[0][2 * j + 1] & 0xffff0000u);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) x.i[k] = int(w[1][k]);
+  }
+  template <int VEC>
+  static __device__ __forceinline__ float value(const State<VEC>& x, int k) {
+    const uint32_t bits = (k & 1) ? (x.b[k / 2] & 0xffff0000u) : (x.b[k / 2] << 16);
+    return x.i[k] < 0 ? -FLT_MAX : __uint_as_float(bits);
+  }
+  template <int VEC>
+  static __device__ __forceinline__ int index(const State<VEC>& x, int k) { return x.i[k]; }
+};
+
 // Sum (compensated) and maximum + row of the same rows in one pass: the state is
 // the two states side by side, and every step is the two operators' step.
 struct OpSumMax {
+  static constexpr bool kRawBf16 = false;
   static constexpr bool kIsMax = true;
   static constexpr bool kHasSum = true;
   static constexpr int kPlanes = 4;

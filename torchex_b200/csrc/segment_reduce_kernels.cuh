@@ -66,6 +66,13 @@
 #define TEXB_PACKED_F32X2 1
 #endif
 
+// TEXB_BF16_PACKED_MAX: 1 = the maximum of bf16 rows works on packed bf16 pairs (OpMaxBf16).
+#ifndef TEXB_BF16_PACKED_MAX
+#define TEXB_BF16_PACKED_MAX 1
+#endif
+
+#include <type_traits>
+
 #include "reduce_ops.cuh"
 
 namespace texb {
@@ -846,6 +853,33 @@ __device__ __forceinline__ void unpack_lane(const float2& t2, float (&v)[VEC]) {
   }
 }
 
+// Adds one row (the bytes this lane owns of it) to the running state.  An operator that
+// works on packed bf16 pairs takes them as they are; the others get fp32 channels.
+template <class Op, class In, int VEC, class State>
+__device__ __forceinline__ void accumulate_lane(State& acc, const float4& t4, int row) {
+  if constexpr (Op::kRawBf16 && sizeof(In) == 2) {
+    static_assert(VEC == 8, "16-byte lanes hold eight bf16 channels");
+    const uint32_t w[4] = {__float_as_uint(t4.x), __float_as_uint(t4.y), __float_as_uint(t4.z), __float_as_uint(t4.w)};
+    Op::template add_raw<VEC>(acc, w, row);
+  } else {
+    float v[VEC];
+    unpack_lane<In, VEC>(t4, v);
+    Op::template add<VEC>(acc, v, row);
+  }
+}
+template <class Op, class In, int VEC, class State>
+__device__ __forceinline__ void accumulate_lane(State& acc, const float2& t2, int row) {
+  if constexpr (Op::kRawBf16 && sizeof(In) == 2) {
+    static_assert(VEC == 4, "8-byte lanes hold four bf16 channels");
+    const uint32_t w[2] = {__float_as_uint(t2.x), __float_as_uint(t2.y)};
+    Op::template add_raw<VEC>(acc, w, row);
+  } else {
+    float v[VEC];
+    unpack_lane<In, VEC>(t2, v);
+    Op::template add<VEC>(acc, v, row);
+  }
+}
+
 // Resident CTAs per SM the staged kernel is compiled for: three where the ring and
 // the edge-run slots leave room (bf16 rows on 8-byte lanes, single-output operators),
 // otherwise two.  (8-byte lanes: bf16 rows of up to 128 channels, fp32 rows of up to 64.)
@@ -1054,15 +1088,15 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
     };
     // One row of a batch that holds run ends.  `single`: the row is a whole segment.
     auto row_step = [&](int q, const Word& t4, int row, bool end_k, bool single, int sids_reg, int lane_k) {
-      float v[VEC];
-      unpack_lane<In, VEC>(t4, v);
       if (single) {
+        float v[VEC];
+        unpack_lane<In, VEC>(t4, v);
         const int sid_now = __shfl_sync(gmask, sids_reg, lane_k, LPR);
         store_single<Op, VEC>(out, arg, sid_now, C, ch, lane_on, v, row, ospec);
         is_first = false;
         run_start = q + 1;
       } else {
-        Op::template add<VEC>(acc, v, row);
+        accumulate_lane<Op, In, VEC>(acc, t4, row);
         if (end_k) {
           const int sid_now = __shfl_sync(gmask, sids_reg, lane_k, LPR);
           close_run(sid_now, q - run_start + 1, false);
@@ -1114,11 +1148,9 @@ segment_reduce_staged_kernel(const In* __restrict__ feats, const int32_t* __rest
 #pragma unroll FU
           for (int k = 0; k < B; ++k) {
             const Word t4 = src[k * kSlotFloat4];
-            float v[VEC];
-            unpack_lane<In, VEC>(t4, v);
             int row = g0 + q0 + k;
             if constexpr (Op::kIsMax && HAS_PERM) row = __shfl_sync(gmask, rows_reg, (j0 & (LPR - 1)) + k, LPR);
-            Op::template add<VEC>(acc, v, row);
+            accumulate_lane<Op, In, VEC>(acc, t4, row);
           }
           carry = 0u;
         } else {
@@ -1406,7 +1438,11 @@ int launch_pair(Kernel kernel, size_t dyn_smem, int ctas_per_sm, const Layout& g
   ws.meta = reinterpret_cast<int4*>(base + vec_bytes);
   // Chains are finished by the reduce kernel itself ("chain_inline" knob, the default) or by
   // the fix-up kernel that follows it.
-  const bool inline_chains = (tuning().chain_inline != 0 || c.single_launch || c.no_wait) && s.num_ctas > 1;
+  // (The packed bf16 maximum always finishes its chains in the kernel: with a fix-up launch behind it a
+  // reduction of the skewed 1 M x 128 workload takes 81.6 us, without 63.4 us -- measured, not understood;
+  // its kernels alone take 64.9 + 7.4 us under ncu.)
+  const bool inline_chains =
+      (tuning().chain_inline != 0 || c.single_launch || c.no_wait || Op::kRawBf16) && s.num_ctas > 1;
   ws.ready = inline_chains ? reinterpret_cast<unsigned long long*>(base + vec_bytes + meta_bytes) : nullptr;
   ws.epoch = inline_chains ? next_launch_epoch() : 0ull;
 
@@ -1497,11 +1533,13 @@ template <class Op>
 int dispatch_layout(const Layout& g, const Call& c) {
   if (g.in_bytes == 2) {
     using H = __nv_bfloat16;
+    // the maximum of bf16 rows is taken on packed pairs
+    using BOp = std::conditional_t<std::is_same_v<Op, OpMax> && TEXB_BF16_PACKED_MAX != 0, OpMaxBf16, Op>;
     if (g.lane_bytes == 8 && g.lpr == 32)
-      return c.perm ? launch_staged<Op, H, 8, 32, true>(g, c) : launch_staged<Op, H, 8, 32, false>(g, c);
+      return c.perm ? launch_staged<BOp, H, 8, 32, true>(g, c) : launch_staged<BOp, H, 8, 32, false>(g, c);
     if constexpr (Op::kPlanes == 2) {  // the two-output operator's edge-run slots would not fit beside 16-byte bf16 lanes
       if (g.lane_bytes == 16 && g.lpr == 32)
-        return c.perm ? launch_staged<Op, H, 16, 32, true>(g, c) : launch_staged<Op, H, 16, 32, false>(g, c);
+        return c.perm ? launch_staged<BOp, H, 16, 32, true>(g, c) : launch_staged<BOp, H, 16, 32, false>(g, c);
     } else if (g.lane_bytes == 16) {
       return fail(TEXB_ERR_UNSUPPORTED, "the two-output reduction takes bf16 rows of up to 128 channels (got %d); "
                   "convert wider rows to fp32", c.C);
