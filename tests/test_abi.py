@@ -26,7 +26,7 @@ def test_header_declares_the_expected_surface():
 
 
 def test_library_exports_every_declared_symbol():
-    assert os.path.exists(build.LIB_PATH), "build the library first: python -m torchex_b200.build"
+    assert os.path.exists(build.LIB_PATH), "build the library first: python torchex_b200/build.py"
     lib = ctypes.CDLL(build.LIB_PATH)
     for name in declared_symbols():
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
@@ -83,3 +83,49 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(build, "LIB_PATH", "/nonexistent/libtexb_scatter.so")
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _native.lib()
+
+
+def test_sequence_flag_needs_a_settled_plan():
+    lib = _native.lib()
+    # a following reduction of a sequence reads the plan without waiting for the stream:
+    # refused unless the caller states that the plan is settled
+    st = lib.texb_segment_reduce(0, 1, 1, None, None, _native.SEQUENCE_NEXT, None, 0, 10, 4, 5, 1, None, 0, None, 0, None)
+    assert st == 1 and "TEXB_PLAN_SETTLED" in _native.last_error()
+
+
+def test_compiled_module_has_the_reference_interface():
+    """The torch extension module loads without a GPU, carries the three functions of TorchEx's
+    scatter_ext with their checks, and registers under that name."""
+    import sys
+    import torch
+    from torchex_b200 import scatter_ext
+    assert scatter_ext.native.__name__ == "scatter_ext"
+    for name in ("sum", "max", "getPreSum", "Plan", "make_plan", "build_plan", "reduce", "reduce_pair",
+                 "reduce_sequence", "broadcast_back", "mean_max_backward", "segment_rank"):
+        assert hasattr(scatter_ext.native, name), name
+    assert scatter_ext.abi_version() == _native.lib().texb_version()
+    with pytest.raises(RuntimeError, match="CUDAtensor"):
+        scatter_ext.sum(torch.zeros(4, 2), torch.zeros(3, dtype=torch.int32), torch.zeros(2, 2), 1)
+    with pytest.raises(RuntimeError, match="CUDAtensor"):
+        scatter_ext.getPreSum(torch.zeros(4, dtype=torch.int32), torch.zeros(3, dtype=torch.int32))
+    saved = sys.modules.pop("scatter_ext", None)
+    try:
+        scatter_ext.install()
+        import scatter_ext as top_level  # what torchex/operator_py/scatter_op.py:4 does
+        assert top_level is scatter_ext.native
+    finally:
+        sys.modules.pop("scatter_ext", None)
+        if saved is not None:
+            sys.modules["scatter_ext"] = saved
+
+
+def test_reference_operator_module_loads_on_the_compiled_module():
+    """TorchEx's own scatter_op.py (byte-compiled from the reference tree by oracle/Makefile)
+    imports with the compiled module in place of its native module and exposes its API."""
+    from oracle import scatter_oracle as O
+    from torchex_b200 import scatter_ext
+    mod = O.reference_operator_module(scatter_ext.native)
+    if mod is None:
+        pytest.skip("oracle/_ref/torchex_scatter_op.compiled was not built")
+    for name in ("ScatterData", "scatter_sum", "scatter_mean", "scatter_max", "getPreSum"):
+        assert hasattr(mod, name)

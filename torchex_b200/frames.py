@@ -201,18 +201,12 @@ class FrameShard:
         key = (channels, group)
         if key not in self._rings:
             from .peer_ring import PeerRing
-            try:
+            try:  # the constructor is collective: it succeeds on every rank or raises on every rank
                 self._rings[key] = PeerRing(self.layout.seg_counts_all, self.layout.rank, channels, self.device, group)
             except RuntimeError:
                 if forced == "dma":
                     raise
                 self._rings[key] = None  # buffers cannot be shared on this box: NCCL transfers instead
-            # every rank must take the same path
-            ok = torch.tensor([0 if self._rings[key] is None else 1], device=self.device)
-            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
-            if int(ok.item()) == 0 and self._rings[key] is not None:
-                self._rings[key].close()
-                self._rings[key] = None
         return self._rings[key]
 
     def _replicated_start(self, op: str, feats: torch.Tensor, group):

@@ -65,20 +65,34 @@ class PeerRing:
         self.slot_bytes = (max(self.counts + [1]) * channels * 4 + 255) // 256 * 256
         self._lib = _native.lib()
         self._ptr = ctypes.c_void_p()
+        self._peers: List[Optional[int]] = [None] * self.world
         handle = (ctypes.c_ubyte * 64)()
         with torch.cuda.device(self.device):
-            _native.check(self._lib.texb_peer_buffer_create(self.slot_bytes * slots, ctypes.byref(self._ptr), handle),
-                          "texb_peer_buffer_create")
+            # Every step below is collective: a rank on which something fails keeps taking part,
+            # and all ranks learn of the failure together (and raise together).
+            problem = None
+            if self._lib.texb_peer_buffer_create(self.slot_bytes * slots, ctypes.byref(self._ptr), handle) != 0:
+                problem = "texb_peer_buffer_create: " + _native.last_error()
             handles: List[Optional[bytes]] = [None] * self.world
-            dist.all_gather_object(handles, bytes(handle), group=group)
-            self._peers: List[Optional[int]] = [None] * self.world
-            for r, h in enumerate(handles):
-                if r == rank:
-                    continue
-                p = ctypes.c_void_p()
-                buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
-                _native.check(self._lib.texb_peer_buffer_open(buf, ctypes.byref(p)), "texb_peer_buffer_open")
-                self._peers[r] = p.value
+            dist.all_gather_object(handles, None if problem else bytes(handle), group=group)
+            if problem is None and any(h is None for h in handles):
+                problem = "another rank could not create its buffer"
+            if problem is None:
+                for r, h in enumerate(handles):
+                    if r == rank:
+                        continue
+                    p = ctypes.c_void_p()
+                    buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                    if self._lib.texb_peer_buffer_open(buf, ctypes.byref(p)) != 0:
+                        problem = "texb_peer_buffer_open: " + _native.last_error()
+                        break
+                    self._peers[r] = p.value
+            ok = torch.tensor([0 if problem else 1], dtype=torch.int32, device=self.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) == 0:
+                self._release()
+                raise RuntimeError("peer buffers cannot be shared between the ranks: " +
+                                   (problem or "a problem on another rank"))
             self._local = torch.as_tensor(_RawCuda(self._ptr.value, self.slot_bytes * slots), device=self.device)
             self._stream = torch.cuda.Stream(self.device)        # the handshakes
             self._own_stream = torch.cuda.Stream(self.device)    # this rank's own shard, copied beside the pulls
@@ -171,6 +185,16 @@ class PeerRing:
 
     # ---- teardown --------------------------------------------------------------------
 
+    def _release(self) -> None:
+        for r, p in enumerate(self._peers):
+            if p is not None:
+                self._lib.texb_peer_buffer_close(ctypes.c_void_p(p))
+                self._peers[r] = None
+        self._local = None
+        if self._ptr.value:
+            self._lib.texb_peer_buffer_destroy(self._ptr)
+            self._ptr = ctypes.c_void_p()
+
     def close(self) -> None:
         """Collective: unmaps the peers' buffers, waits for everyone, frees this rank's buffer."""
         if self._closed:
@@ -182,7 +206,5 @@ class PeerRing:
                 if p is not None:
                     self._lib.texb_peer_buffer_close(ctypes.c_void_p(p))
                     self._peers[r] = None
-            dist.barrier(group=self.group)
-            self._local = None
-            self._lib.texb_peer_buffer_destroy(self._ptr)
-            self._ptr = ctypes.c_void_p()
+            dist.barrier(group=self.group)   # nobody still maps this rank's buffer
+            self._release()
