@@ -7,19 +7,27 @@ ranks map through CUDA IPC (``texb_peer_buffer_*`` of the C ABI).  A replicated
 gather of one result then is:
 
 1. the reduce kernels write this rank's shard straight into a slot of its ring;
-2. a one-element NCCL all-reduce on the copy stream: every rank's shard is complete;
+2. a one-element NCCL all-reduce on the same stream, right behind those kernels: once it
+   has completed, every rank's shard is complete;
 3. this rank pulls the other ranks' shards out of their rings into the row ranges of
    its result with ``texb_peer_copy`` (``cudaMemcpyAsync``, copy engines), in pieces spread
-   over a few streams so that several copies are in flight; its own shard is copied into
-   place on another stream at the same time;
-4. a second one-element all-reduce: every rank has finished pulling, the slot is free.
+   over a few side streams so that several copies are in flight; its own shard is copied
+   into place on another stream at the same time.
 
-Steps 2-4 run on a side stream, so the next reduction proceeds on the main stream
-while the bytes move.  No kernel reads another GPU's memory; nothing is multicast.
+The pulls run on side streams, so the next reduction proceeds on the main stream while the
+bytes move.  A slot is refilled ``slots`` gathers later.  That is safe without a second
+handshake: before a rank enters the all-reduce of gather k it makes its stream wait for its
+own copies of gather k - slots / 2, so the completion of that all-reduce tells every rank
+that all copies of gather k - slots / 2 are done everywhere.  The kernels that refill that
+slot (for gather k + slots / 2) are launched on the same stream behind that all-reduce,
+because at most slots / 2 slots are filled ahead of their gathers.  All of this assumes one
+stream per ring for the reductions and gathers.  No kernel reads another GPU's memory; nothing
+is multicast.
 """
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional, Sequence
 
 import torch
@@ -28,8 +36,10 @@ import torch.distributed as dist
 from . import _native
 
 
-PULL_STREAMS = 4            # concurrent device-to-device copies per rank
-PULL_CHUNK_BYTES = 64 << 20  # a shard larger than this is pulled in pieces spread over the streams
+# concurrent device-to-device copies per rank, and the size above which a shard is pulled in
+# pieces spread over the streams (TEXB_PULL_STREAMS / TEXB_PULL_CHUNK_MB override them)
+PULL_STREAMS = max(1, int(os.environ.get("TEXB_PULL_STREAMS", "4")))
+PULL_CHUNK_BYTES = max(1, int(os.environ.get("TEXB_PULL_CHUNK_MB", "64"))) << 20
 
 
 class _RawCuda:
@@ -59,6 +69,8 @@ class PeerRing:
     arguments, use the slots in the same order and ``close()`` it collectively."""
 
     def __init__(self, seg_counts_all: Sequence[int], rank: int, channels: int, device, group=None, slots: int = 8):
+        if slots < 2 or slots % 2:
+            raise ValueError("slots must be even and at least 2")
         self.rank, self.world = rank, len(seg_counts_all)
         self.counts = [int(v) for v in seg_counts_all]
         self.channels, self.device, self.group, self.slots = channels, torch.device(device), group, slots
@@ -94,25 +106,26 @@ class PeerRing:
                 raise RuntimeError("peer buffers cannot be shared between the ranks: " +
                                    (problem or "a problem on another rank"))
             self._local = torch.as_tensor(_RawCuda(self._ptr.value, self.slot_bytes * slots), device=self.device)
-            self._stream = torch.cuda.Stream(self.device)        # the handshakes
             self._own_stream = torch.cuda.Stream(self.device)    # this rank's own shard, copied beside the pulls
             # the pulls: several copies in flight at once keep more than one copy engine (and,
             # with several peers, more than one NVLink path) busy
             self._pull_streams = [torch.cuda.Stream(self.device) for _ in range(PULL_STREAMS)]
             self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
-            self._free = [None] * slots   # event: every rank has pulled what the slot held
+            self._history = [[] for _ in range(slots)]   # events of this rank's copies of the last gathers
+            self._count = 0
         self._next = 0
         self._closed = False
 
     # ---- slots -------------------------------------------------------------------
 
     def acquire(self) -> int:
-        """Next slot of the ring; the current stream waits until the previous shard held
-        there has been pulled by every rank."""
-        slot = self._next
-        self._next = (self._next + 1) % self.slots
-        if self._free[slot] is not None:
-            torch.cuda.current_stream(self.device).wait_event(self._free[slot])
+        """Next slot of the ring (see ``gather`` for why it is free).  At most ``slots / 2``
+        slots may be acquired and filled before their gathers are started, and the gathers
+        are started in the order the slots were acquired."""
+        if self._next - self._count >= self.slots // 2:
+            raise RuntimeError("too many slots acquired before their gathers were started")
+        slot = self._next % self.slots
+        self._next += 1
         return slot
 
     def view(self, slot: int, dtype: torch.dtype) -> torch.Tensor:
@@ -127,6 +140,8 @@ class PeerRing:
         """Starts pulling every rank's shard of ``slot`` into a new ``[seg_total, channels]``
         tensor.  Call it after the kernels that fill this rank's shard have been launched on
         the current stream."""
+        if self._count >= self._next or slot != self._count % self.slots:
+            raise RuntimeError("gathers must be started in the order their slots were acquired")
         main = torch.cuda.current_stream(self.device)
         out = torch.empty((sum(self.counts), self.channels), dtype=dtype, device=self.device)
         row, offsets = 0, []
@@ -149,38 +164,38 @@ class PeerRing:
         copy(self.rank, own)
         own_done = torch.cuda.Event()
         own_done.record(own)
-        side = self._stream
-        side.wait_stream(main)                      # this rank's shard is complete ...
         done = [own_done]
-        with torch.cuda.stream(side):
-            dist.all_reduce(self._token, group=self.group)   # ... and so is everyone else's
-            ready = torch.cuda.Event()
-            ready.record(side)
-            # pieces to pull, starting with the next rank so that not everyone pulls from rank 0 first
-            pieces = []
-            for step in range(1, self.world):
-                r = (self.rank + step) % self.world
-                total = self.counts[r] * row_bytes
-                for first in range(0, total, PULL_CHUNK_BYTES):
-                    pieces.append((r, first, min(PULL_CHUNK_BYTES, total - first)))
-            for i, st in enumerate(self._pull_streams):
-                mine = pieces[i::len(self._pull_streams)]
-                if not mine:
-                    continue
-                st.wait_event(ready)
-                for r, first, nbytes in mine:
-                    copy(r, st, first, nbytes)
-                ev = torch.cuda.Event()
-                ev.record(st)
-                done.append(ev)
-                out.record_stream(st)
-            for ev in done:                         # the slot is free once every copy has read it
-                side.wait_event(ev)
-            dist.all_reduce(self._token, group=self.group)   # every rank has pulled: the slot may be refilled
-            free = torch.cuda.Event()
-            free.record(side)
-            self._free[slot] = free
+        # Handshake, on the main stream right behind the reduce kernels: first wait for this
+        # rank's copies of the gather half a ring ago (long finished), then the all-reduce.
+        # Its completion means: every shard of this gather is complete, and every rank has
+        # finished copying the gather half a ring ago -- whose slot is refilled half a ring from now.
+        k = self._count
+        self._count += 1
+        for ev in self._history[(k - self.slots // 2) % self.slots]:
+            main.wait_event(ev)
+        dist.all_reduce(self._token, group=self.group)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        # pieces to pull, starting with the next rank so that not everyone pulls from rank 0 first
+        pieces = []
+        for step in range(1, self.world):
+            r = (self.rank + step) % self.world
+            total = self.counts[r] * row_bytes
+            for first in range(0, total, PULL_CHUNK_BYTES):
+                pieces.append((r, first, min(PULL_CHUNK_BYTES, total - first)))
+        for i, st in enumerate(self._pull_streams):
+            mine = pieces[i::len(self._pull_streams)]
+            if not mine:
+                continue
+            st.wait_event(ready)
+            for r, first, nbytes in mine:
+                copy(r, st, first, nbytes)
+            ev = torch.cuda.Event()
+            ev.record(st)
+            done.append(ev)
+            out.record_stream(st)
         out.record_stream(own)
+        self._history[k % self.slots] = list(done)
         return PendingPull(out, done)
 
     # ---- teardown --------------------------------------------------------------------
