@@ -680,7 +680,9 @@ def multi_frame_bench(args, rank, world, dev, barrier):
     res = {"frames": frames, "points": frames * per_frame, "channels": c, "segments": layout.seg_total,
            "gather": "none (one GPU)" if world == 1 else
            f"{shard.gather_method(c)}: exact-size transfers straight into the rows of the result, "
-           "started after each reduction and waited for at the end of the step"}
+           "started after each reduction and waited for at the end of the step; with the peer ring "
+           "(dma) the mean is derived on every GPU from the replicated sum and the segment sizes, "
+           "so sum, max and argmax cross the links"}
 
     def timed(step, reps=10):
         for _ in range(3):
@@ -704,8 +706,14 @@ def multi_frame_bench(args, rank, world, dev, barrier):
         ms = timed(lambda: shard.scatter_many(ops3, feats, replicated))
         res[f"Mpoints_per_s_{mode}"] = round(3 * frames * per_frame / (ms * 1e-3) / 1e6, 1)
         res[f"ms_per_step_{mode}"] = round(ms, 4)
-    # bytes every GPU receives per replicated step: the other ranks' rows of sum, mean, max and arg
-    inbound = 4 * (layout.seg_total - layout.seg_count) * c * 4
+    # bytes every GPU receives per replicated step: the other ranks' rows of sum, max and arg, and of
+    # the mean as well unless it is derived locally (peer ring)
+    moved = 4
+    if world > 1 and shard.gather_method(c) == "dma":
+        moved = 3
+        ms = timed(lambda: shard.scatter_many(ops3, feats, True, derive_mean=False))
+        res["ms_per_step_replicated_all_four_moved"] = round(ms, 4)
+    inbound = moved * (layout.seg_total - layout.seg_count) * c * 4
     if world > 1:
         t = torch.tensor([float(inbound)], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -716,7 +724,7 @@ def multi_frame_bench(args, rank, world, dev, barrier):
     ring = shard._ring_for(c, None) if world > 1 else None
     if ring is not None:
         def move_only():
-            return ring.gather(ring.acquire(), torch.float32).wait()
+            return ring.gather(ring.acquire(), torch.float32, layout.seg_counts_all).wait()
         ms = timed(move_only)
         one = (layout.seg_total - layout.seg_count) * c * 4
         res["transfer_only"] = {"ms_per_tensor": round(ms, 4), "inbound_GBps_per_gpu": round(one / (ms * 1e-3) / 1e9, 1),
@@ -766,6 +774,7 @@ def multi_frame_bench(args, rank, world, dev, barrier):
             rep = shard.scatter_many(ops3, feats, True)
             mine_rows = slice(layout.seg_base, layout.seg_base + layout.seg_count)
             ok = ok and torch.equal(rep["sum"][mine_rows], got["sum"]) and torch.equal(rep["max"][1][mine_rows], got["max"][1])
+            ok = ok and torch.equal(rep["mean"][mine_rows], got["mean"])   # also when derived from the replicated sum
             # identical replicated copies on every rank: per-tensor checksums agree
             sums = torch.stack([t.view(torch.int32).long().sum() for t in
                                 (rep["sum"], rep["mean"], rep["max"][0], rep["max"][1])])

@@ -409,25 +409,49 @@ int texb_scatter_mean_max_backward(const float* g_mean, const float* g_max,
 /* ---- peer buffers for the multi-GPU driver ---------------------------------------
  * One process per GPU; a caller that wants every GPU to hold the whole result of a
  * sharded reduction lets each GPU write its shard into a buffer the other processes
- * can map, and each GPU then pulls the other shards with plain device-to-device
- * copies (copy engines over NVLink; no kernel reads peer memory).  Ordering between
+ * can map, and each GPU then pulls the other shards into its own memory: with one
+ * kernel that loads from all peers at once (texb_peer_pull), or with plain
+ * device-to-device copies on the copy engines (texb_peer_copy).  Ordering between
  * the processes -- a shard is complete before it is pulled and pulled before it is
- * overwritten -- is the caller's job (torchex_b200/frames.py uses small NCCL
- * collectives).  No counterpart in the reference, which has no multi-GPU code.
+ * overwritten -- is the caller's job (torchex_b200/peer_ring.py uses one small NCCL
+ * collective per gather).  No counterpart in the reference, which has no multi-GPU code.
  *   texb_peer_buffer_create : cudaMalloc of `bytes` on the current device (THIS call
  *     allocates; free with texb_peer_buffer_destroy) and its 64-byte CUDA IPC handle,
  *     to be sent to the other processes by any host channel;
  *   texb_peer_buffer_open   : maps a peer's buffer into this process with the current
  *     device as the accessing device (peer access is enabled lazily); the pointer is
- *     only ever used as the source of texb_peer_copy; close it before the owner
- *     destroys the buffer;
- *   texb_peer_copy          : cudaMemcpyAsync(dst, src, bytes) on `stream`. */
+ *     only ever used as a source of texb_peer_copy / texb_peer_pull; close it before
+ *     the owner destroys the buffer;
+ *   texb_peer_copy          : cudaMemcpyAsync(dst, src, bytes) on `stream`;
+ *   texb_peer_pull          : copies `n` regions, srcs[k] -> dsts[k] of bytes[k] bytes
+ *     (host arrays; multiples of 4 bytes at 4-byte aligned addresses, 16-byte alignment
+ *     is faster), with one kernel launch per TEXB_PEER_PULL_MAX regions on `stream`.
+ *     Sources may be peer mappings or local memory, destinations are local memory.
+ *     The kernel only loads from the sources: plain ld.global, no TMA, no multicast,
+ *     no waiting on anything.
+ *   texb_peer_pull_mean     : texb_peer_pull for regions that hold whole rows of SUMS
+ *     (`channel` floats per row, channel divisible by 4, everything 16-byte aligned):
+ *     next to every copied row it writes the row of means into mean_dsts[k], dividing by
+ *     counts[first_rows[k] + row of the region] exactly as the mean reduction divides
+ *     (`counts`: int32 segment sizes on this GPU; sizes <= 1 leave the row as it is).
+ *     The copy is bound by the links, so the means cost no time and no second pass.
+ *   texb_mean_from_sum      : out[s, :] = sums[s, :] / counts[s] for the num_segments
+ *     rows of `channel` floats, with the same correctly rounded division the mean
+ *     reduction applies to its sums (rows with counts[s] <= 1 are copied).  A caller
+ *     that holds the replicated sums and the segment sizes gets the replicated means
+ *     from local memory instead of moving a second tensor between the GPUs. */
 #define TEXB_PEER_HANDLE_BYTES 64
+#define TEXB_PEER_PULL_MAX 16
 int texb_peer_buffer_create(size_t bytes, void** dev_ptr, unsigned char* handle_out);
 int texb_peer_buffer_destroy(void* dev_ptr);
 int texb_peer_buffer_open(const unsigned char* handle, void** peer_ptr);
 int texb_peer_buffer_close(void* peer_ptr);
 int texb_peer_copy(void* dst, const void* src, size_t bytes, void* stream);
+int texb_peer_pull(const void* const* srcs, void* const* dsts, const size_t* bytes, int n, void* stream);
+int texb_peer_pull_mean(const void* const* srcs, void* const* dsts, void* const* mean_dsts, const size_t* bytes,
+                        const int64_t* first_rows, int n, const int32_t* counts, int channel, void* stream);
+int texb_mean_from_sum(const float* sums, const int32_t* counts, int64_t num_segments, int channel,
+                       float* out, void* stream);
 
 #ifdef __cplusplus
 }

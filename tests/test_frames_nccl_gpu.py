@@ -26,7 +26,8 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, frames, per_frame, channels, out_dir):
+def _worker(rank, world, port, frames, per_frame, channels, out_dir, pull):
+    os.environ["TEXB_PULL"] = pull   # read when the peer ring module is first imported
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dev = torch.device("cuda", rank)
@@ -52,6 +53,29 @@ def _worker(rank, world, port, frames, per_frame, channels, out_dir):
             res[f"{method}_max"], res[f"{method}_arg"] = many["max"]
             pm, px, pa = shard.scatter("mean_max", feats, replicated=True)
             res[f"{method}_pair_mean"], res[f"{method}_pair_max"], res[f"{method}_pair_arg"] = pm, px, pa
+        os.environ["TEXB_GATHER"] = "dma"
+        res["dma_mean_moved"] = shard.scatter_many(("sum", "mean"), feats, replicated=True, derive_mean=False)["mean"]
+        half = feats.to(torch.bfloat16)
+        res["dma_bf16_mean"] = shard.scatter_many(("mean", "sum"), half, replicated=True)["mean"]
+        res["dma_bf16_mean_moved"] = shard.scatter("mean", half, replicated=True)
+        # a second, larger batch on the same process group: the ring is replaced by a larger one
+        from torchex_b200 import peer_ring
+        before = peer_ring.ring_for(1, channels, rank, world, dev)
+        big = [W.voxel_frame(4 * per_frame, 900 + f) for f in range(2 * world)]
+        bsegs = [int(c.numel()) for _, c in big]
+        blay = F.shard_layout(bsegs, [4 * per_frame] * len(big), rank, world)
+        blo, bhi = blay.frames
+        bshard = F.FrameShard([i for i, _ in big[blo:bhi]], [c for _, c in big[blo:bhi]], blay, dev)
+        bfeats = W.features(blay.row_count, channels, 902 + rank, device=dev)
+        rep = bshard.scatter("sum", bfeats, replicated=True)
+        own = bshard.scatter("sum", bfeats)
+        assert peer_ring.ring_for(1, channels, rank, world, dev) is not before
+        assert torch.equal(rep[blay.seg_base: blay.seg_base + blay.seg_count], own)
+        sums = rep.view(torch.int32).long().sum().view(1)
+        lo_, hi_ = sums.clone(), sums.clone()
+        dist.all_reduce(lo_, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi_, op=dist.ReduceOp.MAX)
+        assert torch.equal(lo_, hi_)
         torch.cuda.synchronize()
         torch.save({k: v.cpu() for k, v in res.items()}, os.path.join(out_dir, f"rank{rank}.pt"))
         shard.close()
@@ -60,9 +84,10 @@ def _worker(rank, world, port, frames, per_frame, channels, out_dir):
         dist.destroy_process_group()
 
 
-def test_two_gpu_shards_against_the_oracle(tmp_path):
+@pytest.mark.parametrize("pull", ["sm", "dma"])
+def test_two_gpu_shards_against_the_oracle(tmp_path, pull):
     frames, per_frame, channels, world = 5, 40_000, 128, 2
-    mp.spawn(_worker, args=(world, _free_port(), frames, per_frame, channels, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), frames, per_frame, channels, str(tmp_path), pull), nprocs=world, join=True)
     all_frames = [W.voxel_frame(per_frame, 800 + f) for f in range(frames)]
     segs = [int(c.numel()) for _, c in all_frames]
     ids = F.concat_local_ids([i for i, _ in all_frames], segs)
@@ -86,5 +111,9 @@ def test_two_gpu_shards_against_the_oracle(tmp_path):
             assert O.within_tolerance(out[f"{method}_pair_mean"].numpy(), mean64, REL, ABS).all(), method
             assert np.array_equal(out[f"{method}_pair_max"].numpy(), want_max), method
             assert np.array_equal(out[f"{method}_pair_arg"].numpy(), want_arg), method
+            # the mean derived from the replicated sum has the bits of the mean that was moved
+            assert torch.equal(out["dma_mean"], out[f"{method}_mean"]), method
             # every rank holds the same replicated tensors, bit for bit
             assert torch.equal(out[f"{method}_sum"], outs[0][f"{method}_sum"])
+        assert torch.equal(out["dma_mean"], out["dma_mean_moved"])
+        assert torch.equal(out["dma_bf16_mean"], out["dma_bf16_mean_moved"])

@@ -75,6 +75,10 @@ _SIGNATURES = {
     "texb_peer_buffer_open": (_c.c_int, [_c.c_void_p, _c.POINTER(_c.c_void_p)]),
     "texb_peer_buffer_close": (_c.c_int, [_c.c_void_p]),
     "texb_peer_copy": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_size_t, _c.c_void_p]),
+    "texb_peer_pull": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p]),
+    "texb_peer_pull_mean": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int,
+                                       _c.c_void_p, _c.c_int, _c.c_void_p]),
+    "texb_mean_from_sum": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int, _c.c_void_p, _c.c_void_p]),
     "texb_scatter_mean_max_backward": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                                   _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int, _c.c_int64,
                                                   _c.c_void_p]),

@@ -52,6 +52,9 @@ int peer_buffer_destroy_impl(void*);
 int peer_buffer_open_impl(const unsigned char*, void**);
 int peer_buffer_close_impl(void*);
 int peer_copy_impl(void*, const void*, size_t, cudaStream_t);
+int peer_pull_impl(const void* const*, void* const*, const size_t*, int, void* const*, const int64_t*, const int32_t*, int,
+                   cudaStream_t);
+int mean_from_sum_impl(const float*, const int32_t*, int64_t, int, float*, cudaStream_t);
 
 namespace {
 thread_local char t_error[512] = "";
@@ -150,7 +153,7 @@ using namespace texb;
 
 extern "C" {
 
-int texb_version(void) { return 200; }
+int texb_version(void) { return 202; }
 
 const char* texb_last_error(void) { return t_error; }
 
@@ -378,6 +381,18 @@ int texb_peer_buffer_open(const unsigned char* handle, void** peer_ptr) {
 int texb_peer_buffer_close(void* peer_ptr) { return peer_buffer_close_impl(peer_ptr); }
 int texb_peer_copy(void* dst, const void* src, size_t bytes, void* stream) {
   return peer_copy_impl(dst, src, bytes, static_cast<cudaStream_t>(stream));
+}
+int texb_peer_pull(const void* const* srcs, void* const* dsts, const size_t* bytes, int n, void* stream) {
+  return peer_pull_impl(srcs, dsts, bytes, n, nullptr, nullptr, nullptr, 0, static_cast<cudaStream_t>(stream));
+}
+int texb_peer_pull_mean(const void* const* srcs, void* const* dsts, void* const* mean_dsts, const size_t* bytes,
+                        const int64_t* first_rows, int n, const int32_t* counts, int channel, void* stream) {
+  if (!mean_dsts) return fail(TEXB_ERR_INVALID_ARGUMENT, "peer_pull_mean: mean_dsts is NULL");
+  return peer_pull_impl(srcs, dsts, bytes, n, mean_dsts, first_rows, counts, channel, static_cast<cudaStream_t>(stream));
+}
+int texb_mean_from_sum(const float* sums, const int32_t* counts, int64_t num_segments, int channel, float* out,
+                       void* stream) {
+  return mean_from_sum_impl(sums, counts, num_segments, channel, out, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

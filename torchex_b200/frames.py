@@ -103,7 +103,7 @@ def _gather_method(layout: ShardLayout, group) -> str:
     through the NVSwitch); other backends (gloo on CPU ranks) get one equal-size all-gather
     of padded shards.  ``FrameShard`` with the CUDA operators prefers "dma": the reduce
     writes each shard into a buffer the other ranks map, and every rank pulls the others'
-    shards with device-to-device copies (``peer_ring.PeerRing``).
+    shards out of those buffers (``peer_ring.PeerRing``).
     TEXB_GATHER = dma | p2p | broadcast | padded overrides the choice."""
     forced = os.environ.get("TEXB_GATHER", "")
     if forced in ("p2p", "broadcast", "padded"):
@@ -186,32 +186,32 @@ class FrameShard:
             make_data = ScatterData
         self.data = make_data(ids, cnts)
         self._reduce = reduce or _cuda_reduce
-        self._rings = {}
+        self._cnts = cnts
+        self._counts_all = None
+        self._side = None
 
     # ---- replicated results through the peer ring (CUDA operators on NCCL ranks) -----------
 
     def _ring_for(self, channels: int, group):
         """The ring of peer-mapped buffers for results of ``channels`` columns, or None when
-        shards travel through the process group instead.  Created collectively on first use."""
+        shards travel through the process group instead.  Created collectively on first use
+        and kept for the following batches (``peer_ring.ring_for``)."""
         if self._reduce is not _cuda_reduce or self.layout.world_size == 1:
             return None
         forced = os.environ.get("TEXB_GATHER", "")
         if forced not in ("", "dma") or dist.get_backend(group) != "nccl":
             return None  # (with "dma" forced on another backend _gather_method's fallback applies)
-        key = (channels, group)
-        if key not in self._rings:
-            from .peer_ring import PeerRing
-            try:  # the constructor is collective: it succeeds on every rank or raises on every rank
-                self._rings[key] = PeerRing(self.layout.seg_counts_all, self.layout.rank, channels, self.device, group)
-            except RuntimeError:
-                if forced == "dma":
-                    raise
-                self._rings[key] = None  # buffers cannot be shared on this box: NCCL transfers instead
-        return self._rings[key]
+        from .peer_ring import ring_for
+        ring = ring_for(max(self.layout.seg_counts_all), channels, self.layout.rank, self.layout.world_size,
+                        self.device, group)
+        if ring is None and forced == "dma":
+            raise RuntimeError("TEXB_GATHER=dma, but peer buffers cannot be shared between the ranks")
+        return ring  # None: buffers cannot be shared on this box, NCCL transfers instead
 
-    def _replicated_start(self, op: str, feats: torch.Tensor, group):
+    def _replicated_start(self, op: str, feats: torch.Tensor, group, mean_counts=None):
         """Launches the reduction and starts moving its result(s); returns the pending
-        gathers (objects with ``wait()``), one per result tensor."""
+        gathers (objects with ``wait()``), one per result tensor.  ``mean_counts`` (only for
+        "sum" through a ring that can): the gather also writes the means, see ``PeerRing.gather``."""
         ring = self._ring_for(feats.shape[1], group)
         if ring is None:
             res = self._reduce(op, feats, self.data, self.layout.row_base)
@@ -220,22 +220,29 @@ class FrameShard:
         kinds = {"sum": (torch.float32,), "mean": (torch.float32,), "max": (torch.float32, torch.int32),
                  "mean_max": (torch.float32, torch.float32, torch.int32)}[op]
         slots = [ring.acquire() for _ in kinds]
-        views = [ring.view(s, k) for s, k in zip(slots, kinds)]
+        views = [ring.view(s, k, self.layout.seg_count) for s, k in zip(slots, kinds)]
         _cuda_reduce(op, feats, self.data, self.layout.row_base, views)   # the kernels write into the ring
-        return [ring.gather(s, k) for s, k in zip(slots, kinds)]
+        return [ring.gather(s, k, self.layout.seg_counts_all, mean_counts) for s, k in zip(slots, kinds)]
+
+    def _counts_everywhere(self, group) -> torch.Tensor:
+        """Sizes of ALL segments of the batch as int32 on this GPU (collective, once per batch)."""
+        if self._counts_all is None:
+            mine = self._cnts.to(torch.int32).view(-1, 1)
+            self._counts_all = gather_shards(mine, self.layout, group).view(-1)
+        return self._counts_all
 
     def gather_method(self, channels: int, group=None) -> str:
-        """How a replicated result of ``channels`` columns travels: "dma", "p2p", "broadcast" or "padded"."""
+        """How a replicated result of ``channels`` columns travels: "dma" (pulled out of the peers'
+        buffers, by a kernel or by the copy engines), "p2p", "broadcast" or "padded"."""
         if self.layout.world_size == 1:
             return "none"
         return "dma" if self._ring_for(channels, group) is not None else _gather_method(self.layout, group)
 
     def close(self) -> None:
-        """Collective: releases the peer-mapped buffers (if any were created)."""
-        for ring in self._rings.values():
-            if ring is not None:
-                ring.close()
-        self._rings = {}
+        """Collective: releases the peer-mapped buffers of this process (if any were created);
+        they are shared by all batches, so call it when the last batch is done."""
+        from .peer_ring import close_rings
+        close_rings()
 
     def scatter(self, op: str, feats: torch.Tensor, replicated: bool = False, group=None):
         """Reduces this rank's points.  Returns the shard's ``[seg_count, C]``
@@ -247,21 +254,56 @@ class FrameShard:
         done = tuple(p.wait() for p in self._replicated_start(op, feats, group))
         return done if len(done) > 1 else done[0]
 
-    def scatter_many(self, ops: Sequence[str], feats: torch.Tensor, replicated: bool = False, group=None):
+    def scatter_many(self, ops: Sequence[str], feats: torch.Tensor, replicated: bool = False, group=None,
+                     derive_mean: bool = True):
         """Several reductions of the same points, e.g. ``("sum", "mean", "max")``; returns
         a dict op -> result as ``scatter`` gives it.  With ``replicated=True`` the transfer
         of each result is started as soon as its reduction has been launched and only
-        waited for at the end, so the bytes of reduction k move under reduction k + 1."""
+        waited for at the end, so the bytes of reduction k move under reduction k + 1.
+        When both the sum and the mean are asked for, only the sum crosses the links and
+        every GPU divides it by the segment sizes itself (``derive_mean=False`` moves both)."""
         if not replicated or self.layout.world_size == 1:
             if self._reduce is _cuda_reduce and all(op in ("sum", "mean", "max") for op in ops):
                 return _cuda_reduce_sequence(ops, feats, self.data, self.layout.row_base)
             return {op: self._reduce(op, feats, self.data, self.layout.row_base) for op in ops}
-        pending = {op: self._replicated_start(op, feats, group) for op in ops}
-        out = {}
+        # A replicated mean next to a replicated sum is derived on every GPU from the sum it has
+        # received and the segment sizes (same division, same bits) instead of crossing the links.
+        derive_mean = (derive_mean and "sum" in ops and "mean" in ops
+                       and self._ring_for(feats.shape[1], group) is not None)
+        counts = self._counts_everywhere(group) if derive_mean else None
+        moved = [op for op in ops if not (derive_mean and op == "mean")]
+        if derive_mean:
+            moved.sort(key=lambda op: op != "sum")   # the sum first: the means are computed under the other transfers
+        pending, out, mean_ready = {}, {}, None
+        ring = self._ring_for(feats.shape[1], group) if derive_mean else None
+        fused = derive_mean and ring.can_fuse_mean()   # the kernel that pulls the sums writes the means beside them
+        for op in moved:
+            pending[op] = self._replicated_start(op, feats, group, counts if fused and op == "sum" else None)
+            if derive_mean and op == "sum" and not fused:
+                # on a side stream, as soon as the sums have arrived: the division runs on local
+                # memory under the transfers of the results that follow
+                from . import _native
+                if self._side is None:
+                    self._side = torch.cuda.Stream(self.device)
+                main = torch.cuda.current_stream(self.device)
+                with torch.cuda.stream(self._side):
+                    total = pending["sum"][0].wait()
+                    mean = torch.empty_like(total)
+                    _native.check(_native.lib().texb_mean_from_sum(total.data_ptr(), counts.data_ptr(), total.shape[0],
+                                                                   total.shape[1], mean.data_ptr(), self._side.cuda_stream),
+                                  "texb_mean_from_sum")
+                    mean_ready = torch.cuda.Event()
+                    mean_ready.record(self._side)
+                mean.record_stream(main)
+                out["mean"] = mean
         for op, parts in pending.items():
             done = tuple(p.wait() for p in parts)
             out[op] = done if len(done) > 1 else done[0]
-        return out
+        if fused:
+            out["mean"] = pending["sum"][0].mean   # complete with the sums (waited for above)
+        if mean_ready is not None:
+            torch.cuda.current_stream(self.device).wait_event(mean_ready)
+        return {op: out[op] for op in ops}
 
 
 def _cuda_reduce(op: str, feats: torch.Tensor, data, row_base: int = 0, outputs=None):
