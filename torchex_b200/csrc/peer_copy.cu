@@ -95,6 +95,9 @@ struct PullRegions {
   long long first_row[TEXB_PEER_PULL_MAX];
   const int32_t* counts;
   unsigned words_per_row;
+  // CTAs [cta_begin[k], cta_begin[k + 1]) of the 1-D grid copy region k
+  int cta_begin[TEXB_PEER_PULL_MAX + 1];
+  int n;
 };
 
 // One small CTA per SM (256 threads, at most 64 registers: 16 K of the SM's 64 K) so that it fits beside
@@ -103,6 +106,7 @@ struct PullRegions {
 constexpr int kPullThreads = 256;
 constexpr int kPullUnroll = 8;    // 16-byte loads in flight per thread
 constexpr int kPullCtas = 148;    // CTAs over all regions
+constexpr double kPullLocalWeight = 0.25;  // share of CTAs per byte of a region in this GPU's own memory (its own shard)
 
 // The mean row of the sums in 16-byte word `i` of a region: the division of the reduce kernels.
 __device__ __forceinline__ void store_mean_word(const PullRegions& r, int reg, unsigned long long i, const uint4& v) {
@@ -112,7 +116,7 @@ __device__ __forceinline__ void store_mean_word(const PullRegions& r, int reg, u
   __stcs(reinterpret_cast<float4*>(r.mean_dst[reg]) + i, make_float4(m[0], m[1], m[2], m[3]));
 }
 
-// grid (ctas per region, regions).  Region y is copied by the CTAs of row y with a grid-stride loop of
+// Region k is copied by its range of CTAs (more for regions behind a link than for local ones) with a grid-stride loop of
 // 16-byte words, kPullUnroll loads issued before the first store; a region whose addresses or size are
 // not multiples of 16 bytes goes word by word (results are 4-byte types, so 4 bytes always divide it).
 // MEAN: the regions hold rows of sums, and next to each copied word the kernel writes the word of means
@@ -120,11 +124,12 @@ __device__ __forceinline__ void store_mean_word(const PullRegions& r, int reg, u
 // links, so the division and the second store ride along for nothing.
 template <bool MEAN>
 __global__ void __launch_bounds__(kPullThreads, 4) peer_pull_kernel(PullRegions r) {
-  constexpr int U = MEAN ? kPullUnroll / 2 : kPullUnroll;
-  const int reg = blockIdx.y;
+  constexpr int U = kPullUnroll;
+  int reg = 0;
+  while (reg + 1 < r.n && int(blockIdx.x) >= r.cta_begin[reg + 1]) ++reg;
   const unsigned long long bytes = r.bytes[reg];
-  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
-  unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const unsigned long long stride = (unsigned long long)(r.cta_begin[reg + 1] - r.cta_begin[reg]) * blockDim.x;
+  unsigned long long i = (unsigned long long)(int(blockIdx.x) - r.cta_begin[reg]) * blockDim.x + threadIdx.x;
   const bool wide = ((reinterpret_cast<uintptr_t>(r.src[reg]) | reinterpret_cast<uintptr_t>(r.dst[reg]) | bytes) & 15) == 0;
   if (MEAN || wide) {   // (the host only launches MEAN on 16-byte aligned regions)
     const uint4* __restrict__ s = static_cast<const uint4*>(r.src[reg]);
@@ -165,8 +170,10 @@ int peer_pull_impl(const void* const* srcs, void* const* dsts, const size_t* byt
     PullRegions r;
     r.counts = counts;
     r.words_per_row = mean ? unsigned(channel / 4) : 1u;
-    int m = 0;
-    size_t largest = 0;
+    int m = 0, locals = 0;
+    bool local[TEXB_PEER_PULL_MAX];
+    int device = 0;
+    (void)cudaGetDevice(&device);
     for (int k = first; k < n && k < first + TEXB_PEER_PULL_MAX; ++k) {
       if (bytes[k] == 0) continue;
       if (!srcs[k] || !dsts[k] || (mean && !mean_dsts[k]))
@@ -182,17 +189,34 @@ int peer_pull_impl(const void* const* srcs, void* const* dsts, const size_t* byt
       r.bytes[m] = bytes[k];
       r.mean_dst[m] = mean ? static_cast<float*>(mean_dsts[k]) : nullptr;
       r.first_row[m] = mean ? first_rows[k] : 0;
-      largest = bytes[k] > largest ? bytes[k] : largest;
+      cudaPointerAttributes attr;   // a source in this GPU's own memory needs far fewer loads in flight than one behind a link
+      local[m] = cudaPointerGetAttributes(&attr, srcs[k]) == cudaSuccess && attr.type == cudaMemoryTypeDevice &&
+                 attr.device == device;
+      (void)cudaGetLastError();
+      locals += local[m] ? 1 : 0;
       ++m;
     }
     if (m == 0) continue;
-    // no more CTAs per region than the largest region has work for
+    r.n = m;
+    // CTAs in proportion to the time a region needs: its bytes, counted at a quarter when they are local
+    // (a CTA moves local bytes about ten times faster than bytes from behind a link); nobody gets more
+    // CTAs than it has work for
+    (void)locals;
+    double weight[TEXB_PEER_PULL_MAX], sum = 0;
+    for (int k = 0; k < m; ++k) sum += weight[k] = double(r.bytes[k]) * (local[k] ? kPullLocalWeight : 1.0);
     const size_t per_cta = size_t(kPullThreads) * kPullUnroll * 16;
-    int ctas = kPullCtas / m > 0 ? kPullCtas / m : 1;
-    const size_t useful = (largest + per_cta - 1) / per_cta;
-    if (size_t(ctas) > useful) ctas = int(useful);
-    if (mean) peer_pull_kernel<true><<<dim3(ctas, m), kPullThreads, 0, stream>>>(r);
-    else peer_pull_kernel<false><<<dim3(ctas, m), kPullThreads, 0, stream>>>(r);
+    int total = 0;
+    for (int k = 0; k < m; ++k) {
+      int ctas = int(kPullCtas * weight[k] / sum);
+      if (ctas < 1) ctas = 1;
+      const size_t useful = (size_t(r.bytes[k]) + per_cta - 1) / per_cta;
+      if (size_t(ctas) > useful) ctas = int(useful);
+      r.cta_begin[k] = total;
+      total += ctas;
+    }
+    r.cta_begin[m] = total;
+    if (mean) peer_pull_kernel<true><<<total, kPullThreads, 0, stream>>>(r);
+    else peer_pull_kernel<false><<<total, kPullThreads, 0, stream>>>(r);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(TEXB_ERR_CUDA, "peer_pull launch: %s", cudaGetErrorString(e));
   }

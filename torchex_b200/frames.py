@@ -286,15 +286,14 @@ class FrameShard:
                 if self._side is None:
                     self._side = torch.cuda.Stream(self.device)
                 main = torch.cuda.current_stream(self.device)
-                with torch.cuda.stream(self._side):
-                    total = pending["sum"][0].wait()
-                    mean = torch.empty_like(total)
-                    _native.check(_native.lib().texb_mean_from_sum(total.data_ptr(), counts.data_ptr(), total.shape[0],
-                                                                   total.shape[1], mean.data_ptr(), self._side.cuda_stream),
-                                  "texb_mean_from_sum")
-                    mean_ready = torch.cuda.Event()
-                    mean_ready.record(self._side)
-                mean.record_stream(main)
+                mean = torch.empty((self.layout.seg_total, feats.shape[1]), dtype=torch.float32, device=self.device)
+                self._side.wait_stream(main)   # `mean` may reuse a block that work queued on this stream still reads
+                total = pending["sum"][0].wait_on(self._side)
+                _native.check(_native.lib().texb_mean_from_sum(total.data_ptr(), counts.data_ptr(), total.shape[0],
+                                                               total.shape[1], mean.data_ptr(), self._side.cuda_stream),
+                              "texb_mean_from_sum")
+                mean_ready = torch.cuda.Event()
+                mean_ready.record(self._side)   # this stream waits for it below, before anything can be freed
                 out["mean"] = mean
         for op, parts in pending.items():
             done = tuple(p.wait() for p in parts)

@@ -59,20 +59,46 @@ class _RawCuda:
 
 class PendingPull:
     """Result of ``PeerRing.gather``: ``wait()`` makes the current stream wait for the
-    copies and returns the replicated tensor."""
+    copies and returns the replicated tensor.
 
-    def __init__(self, out: torch.Tensor, done, mean: Optional[torch.Tensor] = None):
+    The result tensors are allocated on the stream that called ``gather`` and written on side
+    streams.  They are deliberately NOT marked with ``record_stream`` for those: a block so
+    marked is not reusable until the allocator has seen the side streams' events pass, which
+    makes a steady loop allocate fresh device memory every now and then (milliseconds each
+    time, with peers mapped).  Instead the ordering is explicit: whoever uses or frees the
+    tensors has waited for the copies first (``wait``), so the allocating stream never
+    reuses a block that is still being written.  A result dropped without ``wait`` is marked
+    then, in ``__del__``."""
+
+    def __init__(self, out: torch.Tensor, done, mean: Optional[torch.Tensor] = None, alloc_stream=None, writers=()):
         self.out, self._done = out, list(done)
         self.mean = mean   # rows of means written beside rows of sums (``gather(..., mean_counts=...)``), valid after wait()
+        self._alloc_stream, self._writers, self._waited = alloc_stream, list(writers), False
+
+    def wait_on(self, stream) -> torch.Tensor:
+        """Makes ``stream`` wait for the copies; the caller keeps the tensors alive until the
+        allocating stream has waited too (``wait``)."""
+        for ev in self._done:
+            stream.wait_event(ev)
+        return self.out
 
     def wait(self) -> torch.Tensor:
         stream = torch.cuda.current_stream(self.out.device)
-        for ev in self._done:
-            stream.wait_event(ev)
-        self.out.record_stream(stream)
-        if self.mean is not None:
-            self.mean.record_stream(stream)
+        self.wait_on(stream)
+        if self._alloc_stream is not None and stream != self._alloc_stream:
+            self._alloc_stream.wait_stream(stream)   # frees and reuse happen there
+        self._waited = True
         return self.out
+
+    def __del__(self):
+        try:
+            if not self._waited:
+                for t in (self.out, self.mean):
+                    for st in self._writers:
+                        if t is not None:
+                            t.record_stream(st)
+        except Exception:  # interpreter shutdown
+            pass
 
 
 class PeerRing:
@@ -198,14 +224,14 @@ class PeerRing:
         dist.all_reduce(self._token, group=self.group)
         ready = torch.cuda.Event()
         ready.record(main)
-        done = []
+        done, writers = [], []
 
         def finished(stream):
             ev = torch.cuda.Event()
             ev.record(stream)
             done.append(ev)
             if stream is not main:
-                out.record_stream(stream)
+                writers.append(stream)
 
         if self.mode in ("sm", "sm-serial"):
             st = self._pull_streams[0] if self._pull_streams else main
@@ -224,8 +250,7 @@ class PeerRing:
                     _native.check(self._lib.texb_peer_pull_mean(srcs, dsts, means, sizes, rows, n, mean_counts.data_ptr(),
                                                                 self.channels, st.cuda_stream), "texb_peer_pull_mean")
                     if st is not main:
-                        mean.record_stream(st)
-                        mean_counts.record_stream(st)
+                        mean_counts.record_stream(st)   # a long-lived tensor of the caller; marked once per gather, freed rarely
             finished(st)
         else:
             own, pulls = self._pull_streams[0], self._pull_streams[1:]
@@ -249,7 +274,7 @@ class PeerRing:
                     _native.check(self._lib.texb_peer_copy(dst, src, nbytes, st.cuda_stream), "texb_peer_copy")
                 finished(st)
         self._history[k % self.slots] = list(done)
-        return PendingPull(out, done, mean)
+        return PendingPull(out, done, mean, main, writers)
 
     # ---- teardown --------------------------------------------------------------------
 
