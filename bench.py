@@ -723,6 +723,10 @@ def multi_frame_bench(args, rank, world, dev, barrier):
     # the transfers alone: one [seg_total, C] result replicated with no reduction beside it
     ring = shard._ring_for(c, None) if world > 1 else None
     if ring is not None:
+        res["pull_engine"] = {"sm": "one kernel loading from all peers (texb_peer_pull)",
+                              "sm-serial": "one kernel loading from all peers, on the reducing stream",
+                              "dma": "cudaMemcpyAsync on the copy engines (texb_peer_copy)"}[ring.mode]
+
         def move_only():
             return ring.gather(ring.acquire(), torch.float32, layout.seg_counts_all).wait()
         ms = timed(move_only)

@@ -79,6 +79,7 @@ def _worker(rank, world, port, frames, per_frame, channels, out_dir, gather):
         many = shard.scatter_many(("sum", "mean", "max"), feats, replicated=True)  # gathers overlapped, waited at the end
         res["many_sum"], res["many_mean"] = many["sum"], many["mean"]
         res["many_max"], res["many_arg"] = many["max"]
+        res["counts_all"] = shard._counts_everywhere(None)   # sizes of all segments on every rank (for derived means)
         torch.save({k: v.clone() for k, v in res.items()}, os.path.join(out_dir, f"rank{rank}.pt"))
     finally:
         dist.destroy_process_group()
@@ -112,3 +113,4 @@ def test_two_rank_shards_reproduce_the_single_process_result(tmp_path, gather):
         assert np.array_equal(out["many_sum"].numpy(), want_sum) and np.array_equal(out["many_mean"].numpy(), want_mean)
         assert np.array_equal(out["many_max"].numpy(), want_max) and np.array_equal(out["many_arg"].numpy(), want_arg)
         assert np.array_equal(out["sum_local"].numpy(), want_sum[seg_off[r]:seg_off[r + 1]])
+        assert out["counts_all"].dtype == torch.int32 and np.array_equal(out["counts_all"].numpy(), cnt)
