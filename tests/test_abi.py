@@ -58,6 +58,16 @@ def test_bad_arguments_are_rejected_without_a_gpu():
     assert lib.texb_scatter_sum(None, None, None, 4, 3, 1, 10, None, 0, None) == 1
     assert lib.texb_tune_set(b"no_such_knob", 1) == 1
     assert lib.texb_tune_set(b"rows_per_cta", 7) == 1
+    # the peer kernels: sizes and pointers are checked before anything is launched
+    assert lib.texb_peer_pull(None, None, None, 0, None) == 0          # nothing to copy
+    assert lib.texb_peer_pull(None, None, None, 2, None) == 1
+    assert lib.texb_peer_pull(None, None, None, -1, None) == 1
+    assert lib.texb_peer_pull_mean(None, None, None, None, None, 0, None, 8, None) == 1
+    assert "mean_dsts" in _native.last_error()
+    assert lib.texb_mean_from_sum(None, None, -1, 4, None, None) == 1
+    assert lib.texb_mean_from_sum(None, None, 3, 0, None, None) == 1
+    assert lib.texb_mean_from_sum(None, None, 0, 4, None, None) == 0   # no rows
+    assert lib.texb_mean_from_sum(None, None, 3, 4, None, None) == 1
 
 
 def test_workspace_queries_and_tuning_knobs():
