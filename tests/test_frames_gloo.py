@@ -31,6 +31,29 @@ def test_frame_blocks_and_layout():
     assert ids.tolist() == [0, 1, 1, 3, 2]
 
 
+def test_layouts_partition_any_batch():
+    """Random batches and world sizes: the shards tile the segments and the rows without gap or overlap."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=200, deadline=None)
+    @given(st.lists(st.tuples(st.integers(0, 50), st.integers(0, 500)), min_size=0, max_size=20), st.integers(1, 9))
+    def check(frames, world):
+        segs, pts = [f[0] for f in frames], [f[1] for f in frames]
+        lays = [F.shard_layout(segs, pts, r, world) for r in range(world)]
+        seg, row, frame = 0, 0, 0
+        for r, lay in enumerate(lays):
+            assert lay.frames[0] == frame and lay.seg_base == seg and lay.row_base == row
+            assert lay.seg_count == sum(segs[lay.frames[0]:lay.frames[1]])
+            assert lay.row_count == sum(pts[lay.frames[0]:lay.frames[1]])
+            assert lay.seg_counts_all == [x.seg_count for x in lays] and lay.seg_total == sum(segs)
+            frame, seg, row = lay.frames[1], seg + lay.seg_count, row + lay.row_count
+        assert frame == len(frames) and seg == sum(segs) and row == sum(pts)
+        sizes = [b - a for a, b in F.frame_blocks(len(frames), world)]
+        assert max(sizes) - min(sizes) <= 1
+
+    check()
+
+
 class _CpuData:
     def __init__(self, ids, cnts):
         self.ids, self.m = ids, cnts.numel()
